@@ -1,0 +1,106 @@
+// Decoder-layer API.
+//
+// Same shape as the reference's models/transformer_layer.h:12-69: a config struct, a coordinator
+// whose constructor allocates the intermediates, initialize_pipelines() that binds the projection
+// kernels through the registry's kernel names, and forward() that only *enqueues* the layer (the
+// caller synchronises), taking X_in, the seven weight buffers and X_out.  Metal objects become
+// CUDA ones: device -> device ordinal, queue / command buffer -> cudaStream_t, MTLBuffer ->
+// device pointer.
+//
+// Semantics follow the reference's CPU layer (bench_8b_engine.mm:74-225): QKV head-major
+// projections, causal attention, O projection with X_mid = fp16(X + O), fused SwiGLU, down
+// projection with X_out = fp16(X_mid + down).  The extra config fields default to that behaviour
+// (multi-head attention, no normalisation, no rotary embedding, fp16 KV, one GPU) and add what the
+// reference's Python block has (src/engine/model.py:181-270): RMSNorm, grouped-query attention,
+// rotary embedding; plus the Q8_0 KV cache of its benches and tensor parallelism.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+#include "quant_registry.h"
+
+typedef struct CUstream_st* cudaStream_t;
+
+namespace b200_llm {
+
+struct TransformerLayerConfig {
+    uint32_t M = 128;            // tokens
+    uint32_t K = 2048;           // hidden size
+    uint32_t H = 32;             // query heads (of the whole model, before tensor-parallel split)
+    uint32_t D = 64;             // head size
+    uint32_t N_mlp = 8192;       // MLP width (whole model)
+    float attn_scale = 0.125f;
+    QuantFormat weight_format = QUANT_Q4_0;
+    // ---- additions (defaults reproduce the reference layer) ----
+    uint32_t num_kv_heads = 0;   // 0 = H (multi-head attention)
+    float rms_eps = 0.0f;        // > 0 enables RMSNorm before attention and before the MLP
+    float rope_theta = 0.0f;     // > 0 enables rotary embedding on Q and K
+    bool kv_q8_0 = false;        // compress K and V to Q8_0 before attention
+    uint32_t tp_size = 1;        // tensor-parallel ranks; weights passed to forward() are this rank's shards
+};
+
+// Sum-reduce `count` fp32 values in place across the tensor-parallel group, ordered on `stream`.
+typedef void (*AllReduceFn)(void* ctx, float* buf, size_t count, cudaStream_t stream);
+
+class TransformerLayerCoordinator {
+public:
+    TransformerLayerCoordinator(int device, cudaStream_t stream, const TransformerLayerConfig& config);
+    ~TransformerLayerCoordinator();
+    TransformerLayerCoordinator(const TransformerLayerCoordinator&) = delete;
+    TransformerLayerCoordinator& operator=(const TransformerLayerCoordinator&) = delete;
+
+    // Resolve the registry's kernel names for config.weight_format.  `library` is ignored (kernels are
+    // compiled in).  False if the format has no projection kernel or allocation failed.
+    bool initialize_pipelines(const void* library = nullptr);
+
+    // fp16 [K] RMSNorm weights (device pointers); required when rms_eps > 0.
+    void set_norm_weights(const void* attn_norm, const void* mlp_norm);
+    // required when tp_size > 1
+    void set_allreduce(AllReduceFn fn, void* ctx);
+
+    // Enqueue one layer on `stream`.  All pointers are device pointers.  Weight shapes for rank r of
+    // tp_size: W_q [H/tp*D][K], W_k/W_v [Hkv/tp*D][K], W_o [K][H/tp*D], W_gate/W_up [N_mlp/tp][K],
+    // W_down [K][N_mlp/tp], each in weight_format with rows contiguous along the input dimension.
+    void forward(cudaStream_t stream, const void* X_in, const void* W_q, const void* W_k, const void* W_v,
+                 const void* W_o, const void* W_gate, const void* W_up, const void* W_down, void* X_out);
+
+    const TransformerLayerConfig& config() const { return config_; }
+    int last_status() const { return status_; }           // 0, or the first error of the last forward()
+    uint32_t kernels_per_forward() const { return launches_; }
+
+private:
+    struct Impl;
+    Impl* impl_;
+    TransformerLayerConfig config_;
+    int device_;
+    int status_ = 0;
+    uint32_t launches_ = 0;
+};
+
+}  // namespace b200_llm
+
+extern "C" {
+typedef struct {
+    uint32_t M, K, H, D, N_mlp;
+    float attn_scale;
+    int weight_format;
+    uint32_t num_kv_heads;
+    float rms_eps;
+    float rope_theta;
+    int kv_q8_0;
+    uint32_t tp_size;
+} b200_layer_config;
+
+/* Create on the bridge's device and stream (m4_bridge_init first).  NULL on failure. */
+void* b200_layer_create(const b200_layer_config* cfg);
+void b200_layer_destroy(void* layer);
+int b200_layer_set_norm_weights(void* layer, const void* attn_norm, const void* mlp_norm);
+/* fn(ctx, device fp32 buffer, count): called from forward() on the calling thread, between
+ * enqueued kernels; it must order its work on the bridge stream (b200_bridge_stream()). */
+int b200_layer_set_allreduce(void* layer, void (*fn)(void* ctx, void* buf, size_t count), void* ctx);
+/* X_in / X_out may be host or device pointers; weights must be device pointers or host buffers
+ * registered with b200_bridge_register_weights.  Returns 0 or a bridge error code. */
+int b200_layer_forward(void* layer, const void* X_in, const void* W_q, const void* W_k, const void* W_v,
+                       const void* W_o, const void* W_gate, const void* W_up, const void* W_down, void* X_out);
+uint32_t b200_layer_kernels_per_forward(void* layer);
+}

@@ -1,0 +1,283 @@
+// C ABI of the bridge (include/b200_bridge.h): argument validation in the reference's order
+// (core/bridge/m4_mlx_bridge.mm:194-230), host/device pointer resolution, staging, and dispatch
+// onto the kernels.  One internal stream; a mutex guards all state, as in the reference
+// (core/bridge/m4_mlx_bridge.mm:20,84,284-287).
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+
+#include "../../include/b200_bridge.h"
+#include "../../include/quant_router.h"
+#include "bridge_state.cuh"
+#include "qgemm.cuh"
+
+namespace bridge {
+
+State g;
+
+bool DevBuf::ensure(size_t n) {
+    if (n <= cap) return true;
+    if (p) cudaFree(p);        // implicit device sync: nothing in flight still uses the old block
+    p = nullptr; cap = 0;
+    size_t want = n + n / 4;
+    if (cudaMalloc(&p, want) != cudaSuccess) { cudaGetLastError(); p = nullptr; return false; }
+    cap = want;
+    return true;
+}
+void DevBuf::release() { if (p) cudaFree(p); p = nullptr; cap = 0; }
+
+void set_error(const std::string& s) { g.last_error = s; }
+
+bool is_device_ptr(const void* ptr) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, ptr) != cudaSuccess) { cudaGetLastError(); return false; }
+    return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+}
+
+// Device address for an input buffer: the pointer itself when it is device memory, the
+// registered device copy when it is a registered host weight buffer, else a staged copy.
+const void* resolve_in(const void* ptr, size_t bytes, DevBuf& stage, bool weights, int* rc) {
+    if (is_device_ptr(ptr)) return ptr;
+    if (weights) {
+        auto it = g.registered.find(ptr);
+        if (it != g.registered.end() && it->second.bytes >= bytes) return it->second.dev;
+    }
+    if (!stage.ensure(bytes)) { *rc = -5; return nullptr; }
+    if (cudaMemcpyAsync(stage.p, ptr, bytes, cudaMemcpyHostToDevice, g.stream) != cudaSuccess) {
+        cudaGetLastError(); *rc = -5; return nullptr;
+    }
+    g.h2d_bytes += bytes;
+    return stage.p;
+}
+
+// Device address to write an output into; `*host_dst` is set when a copy back is needed.
+void* resolve_out(void* ptr, size_t bytes, DevBuf& stage, void** host_dst, int* rc) {
+    *host_dst = nullptr;
+    if (is_device_ptr(ptr)) return ptr;
+    if (!stage.ensure(bytes)) { *rc = -5; return nullptr; }
+    *host_dst = ptr;
+    return stage.p;
+}
+
+bool ensure_workspace(size_t floats) {
+    if (floats == 0) return true;
+    if (!g.ws_partial.ensure(floats * sizeof(float))) return false;
+    return true;
+}
+
+int validate_gemm(const void* X, size_t Xb, const void* W, size_t Wb, const void* Y, size_t Yb, int format, bool extended,
+                  uint32_t M, uint32_t K, uint32_t N) {
+    if (!g.initialized) return -1;
+    if (!X || !W || !Y) return -2;
+    if (((uintptr_t)X % 2 != 0) || ((uintptr_t)Y % 2 != 0)) return -2;
+    const bool base_fmt = format >= 0 && format < 6;
+    const bool ext_fmt = extended && (format == QUANT_PRISM_Q2_0 || format == QUANT_MLX_4BIT_G64 || format == QUANT_TERNARY_ROW);
+    if (!base_fmt && !ext_fmt) return -3;
+    if (M == 0 || K == 0 || N == 0) return -4;
+    if ((K % 32) != 0) return -4;
+    if ((format == 2 || format == 4 || format == 5) && (K % 256) != 0) return -4;
+    if (format == QUANT_PRISM_Q2_0 && (K % 128) != 0) return -4;
+    if (format == QUANT_MLX_4BIT_G64 && (K % 64) != 0) return -4;
+    const size_t min_x = (size_t)M * K * 2, min_y = (size_t)M * N * 2;
+    const size_t min_w = compute_quant_matrix_bytes((QuantFormat)format, K, N);
+    if (Xb < min_x || Yb < min_y || Wb < min_w) return -2;
+    return 0;
+}
+
+int run_gemm(void* X, size_t Xb, void* W0, void* W1, size_t Wb, void* Y, size_t Yb, int format, uint32_t M, uint32_t K,
+             uint32_t N, int layout, uint32_t H, uint32_t D, void* residual) {
+    int rc = 0;
+    const size_t x_bytes = (size_t)M * K * 2, y_bytes = (size_t)M * N * 2;
+    const size_t w_bytes = compute_quant_matrix_bytes((QuantFormat)format, K, N);
+    qg::GemmArgs a;
+    memset(&a, 0, sizeof(a));
+    a.format = format;
+    a.X = resolve_in(X, x_bytes, g.stage_x, false, &rc);
+    if (rc) return rc;
+    a.W0 = resolve_in(W0, w_bytes, g.stage_w0, true, &rc);
+    if (rc) return rc;
+    if (W1) { a.W1 = resolve_in(W1, w_bytes, g.stage_w1, true, &rc); if (rc) return rc; }
+    if (residual) { a.residual = resolve_in(residual, y_bytes, g.stage_res, false, &rc); if (rc) return rc; }
+    void* host_dst = nullptr;
+    a.Y = resolve_out(Y, y_bytes, g.stage_y, &host_dst, &rc);
+    if (rc) return rc;
+    a.M = M; a.N = N; a.K = K; a.layout = layout; a.H = H; a.D = D;
+    a.force_generic = g.force_generic;
+    (void)Xb; (void)Wb; (void)Yb;
+    if (!ensure_workspace(qg::workspace_floats(a))) return -5;
+    qg::Workspace ws;
+    ws.partial = (float*)g.ws_partial.p; ws.partial_floats = g.ws_partial.cap / sizeof(float);
+    ws.counters = g.counters; ws.err = g.err_word;
+    cudaError_t e = qg::launch(a, ws, g.stream);
+    if (e != cudaSuccess) { set_error(std::string("kernel launch failed: ") + cudaGetErrorString(e)); return -6; }
+    g.launches += (uint64_t)qg::last_launch_count();
+    if (host_dst) {
+        if (cudaMemcpyAsync(host_dst, a.Y, y_bytes, cudaMemcpyDeviceToHost, g.stream) != cudaSuccess) { cudaGetLastError(); return -5; }
+        g.d2h_bytes += y_bytes;
+    }
+    return 0;
+}
+
+}  // namespace bridge
+
+using namespace bridge;
+
+extern "C" {
+
+bool m4_bridge_init(const char*) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (g.initialized) return true;
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+        cudaGetLastError();
+        set_error("no CUDA device: this library has no CPU path");
+        return false;
+    }
+    cudaGetDevice(&g.device);
+    cudaDeviceProp prop;
+    cudaGetDeviceProperties(&prop, g.device);
+    if (prop.major != 10) {
+        set_error("kernels are built for sm_100a only; found sm_" + std::to_string(prop.major) + std::to_string(prop.minor));
+        return false;
+    }
+    if (cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (cudaMalloc(&g.counters, 4096 * sizeof(uint32_t) + 64) != cudaSuccess) { cudaGetLastError(); return false; }
+    cudaMemsetAsync(g.counters, 0, 4096 * sizeof(uint32_t) + 64, g.stream);
+    g.err_word = reinterpret_cast<int*>(g.counters + 4096);
+    cudaStreamSynchronize(g.stream);
+    g.launches = 0; g.h2d_bytes = 0; g.d2h_bytes = 0;
+    g.initialized = true;
+    return true;
+}
+
+size_t m4_bridge_get_expected_weight_bytes(int format, uint32_t K, uint32_t N) {
+    if (format < 0 || format >= 6) return 0;
+    return compute_quant_matrix_bytes((QuantFormat)format, K, N);
+}
+
+size_t b200_bridge_weight_bytes(int format, uint32_t K, uint32_t N) {
+    if (!((format >= 0 && format < 6) || format == QUANT_PRISM_Q2_0 || format == QUANT_MLX_4BIT_G64 || format == QUANT_TERNARY_ROW))
+        return 0;
+    return compute_quant_matrix_bytes((QuantFormat)format, K, N);
+}
+
+int m4_bridge_dispatch_gemm(void* X, size_t Xb, void* W, size_t Wb, void* Y, size_t Yb, int format, uint32_t M, uint32_t K,
+                            uint32_t N) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    int rc = validate_gemm(X, Xb, W, Wb, Y, Yb, format, false, M, K, N);
+    if (rc) return rc;
+    return run_gemm(X, Xb, W, nullptr, Wb, Y, Yb, format, M, K, N, LAYOUT_STANDARD, 0, 0, nullptr);
+}
+
+int m4_bridge_dispatch_gemv(void* x, size_t xb, void* W, size_t Wb, void* y, size_t yb, int format, uint32_t K, uint32_t N) {
+    return m4_bridge_dispatch_gemm(x, xb, W, Wb, y, yb, format, 1, K, N);
+}
+
+int b200_bridge_dispatch_gemm_ex(void* X, size_t Xb, void* W, size_t Wb, void* Y, size_t Yb, int format, uint32_t M, uint32_t K,
+                                 uint32_t N, int layout, uint32_t H, uint32_t D, void* residual, size_t residual_bytes) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    int rc = validate_gemm(X, Xb, W, Wb, Y, Yb, format, true, M, K, N);
+    if (rc) return rc;
+    if (layout != LAYOUT_STANDARD && layout != LAYOUT_DIRECT_HEAD) return -4;
+    if (layout == LAYOUT_DIRECT_HEAD && (H == 0 || D == 0 || (uint64_t)H * D != N)) return -4;
+    if (residual) {
+        if (layout != LAYOUT_STANDARD) return -4;
+        if (((uintptr_t)residual % 2) != 0 || residual_bytes < (size_t)M * N * 2) return -2;
+    }
+    return run_gemm(X, Xb, W, nullptr, Wb, Y, Yb, format, M, K, N, layout, H, D, residual);
+}
+
+int b200_bridge_dispatch_swiglu(void* X, size_t Xb, void* Wg, void* Wu, size_t Wb, void* Out, size_t Ob, int format, uint32_t M,
+                                uint32_t K, uint32_t F) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (g.initialized && !Wu) return -2;
+    int rc = validate_gemm(X, Xb, Wg, Wb, Out, Ob, format, true, M, K, F);
+    if (rc) return rc;
+    return run_gemm(X, Xb, Wg, Wu, Wb, Out, Ob, format, M, K, F, LAYOUT_STANDARD, 0, 0, nullptr);
+}
+
+int b200_bridge_register_weights(const void* host_ptr, size_t bytes) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!host_ptr || bytes == 0) return -2;
+    if (is_device_ptr(host_ptr)) return 0;     // already resident
+    auto it = g.registered.find(host_ptr);
+    if (it != g.registered.end()) { cudaFree(it->second.dev); g.registered.erase(it); }
+    void* dev = nullptr;
+    if (cudaMalloc(&dev, bytes) != cudaSuccess) { cudaGetLastError(); return -5; }
+    if (cudaMemcpyAsync(dev, host_ptr, bytes, cudaMemcpyHostToDevice, g.stream) != cudaSuccess) { cudaGetLastError(); cudaFree(dev); return -5; }
+    cudaStreamSynchronize(g.stream);
+    g.registered[host_ptr] = Registered{dev, bytes};
+    return 0;
+}
+
+int b200_bridge_unregister_weights(const void* host_ptr) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    auto it = g.registered.find(host_ptr);
+    if (it == g.registered.end()) return -2;
+    cudaStreamSynchronize(g.stream);
+    cudaFree(it->second.dev);
+    g.registered.erase(it);
+    return 0;
+}
+
+void m4_bridge_synchronize(void) {
+    cudaStream_t s;
+    {
+        std::lock_guard<std::mutex> lock(g.mu);
+        if (!g.initialized) return;
+        s = g.stream;
+    }
+    cudaError_t e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) {
+        std::lock_guard<std::mutex> lock(g.mu);
+        set_error(std::string("stream error: ") + cudaGetErrorString(e));
+        fprintf(stderr, "[b200_bridge] %s\n", g.last_error.c_str());
+    }
+}
+
+double m4_bridge_get_uma_footprint_mb(void) {
+    size_t free_b = 0, total_b = 0;
+    if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) { cudaGetLastError(); return 0.0; }
+    return (double)(total_b - free_b) / (1024.0 * 1024.0);
+}
+
+bool m4_bridge_is_initialized(void) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    return g.initialized;
+}
+
+void m4_bridge_shutdown(void) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return;
+    cudaStreamSynchronize(g.stream);
+    g.stage_x.release(); g.stage_w0.release(); g.stage_w1.release(); g.stage_y.release(); g.stage_res.release();
+    g.stage_aux0.release(); g.stage_aux1.release(); g.stage_aux2.release();
+    g.ws_partial.release();
+    for (auto& kv : g.registered) cudaFree(kv.second.dev);
+    g.registered.clear();
+    cudaFree(g.counters); g.counters = nullptr; g.err_word = nullptr;
+    cudaStreamDestroy(g.stream); g.stream = nullptr;
+    g.initialized = false;
+}
+
+int b200_bridge_device_error(void) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    int v = 0;
+    cudaStreamSynchronize(g.stream);
+    cudaMemcpy(&v, g.err_word, sizeof(int), cudaMemcpyDeviceToHost);
+    return v;
+}
+
+const char* b200_bridge_last_error_string(void) { return g.last_error.c_str(); }
+uint64_t b200_bridge_kernel_launches(void) { return g.launches; }
+void* b200_bridge_stream(void) { return (void*)g.stream; }
+void b200_bridge_force_generic(int on) { g.force_generic = on; }
+
+}  // extern "C"

@@ -1,0 +1,312 @@
+// Per-format unpackers: packed weight bytes (held in registers) -> fp16 pairs.
+//
+// One thread owns one weight row.  For every 256-element K chunk it holds the row's packed
+// bytes (`ROW_BYTES`, a multiple of 16 for every format) in registers `r[]` and produces, for
+// each of the four 64-element sub-tiles `s`, 32 words `out[i]` = fp16 pair (k = 2i, 2i+1).  All
+// loops unroll so that register indices are compile-time constants.
+//
+// Arithmetic follows the reference's device unpackers (quant_router_kernels.metal:111-436): the
+// integer code is turned into an exact fp16 value and one fused fp16 multiply-add applies the
+// scale (and bias / minimum), so each weight is rounded once, exactly as `fma(half4(q), d, off)`
+// does there.  Integer -> fp16 uses the mantissa trick: 0x6400|q is the fp16 number 1024+q and
+// 0x5400|(q<<4) is 64+q, so a nibble never needs a convert instruction.
+//
+// The same code compiles for the host (tests/test_codecs_host.py builds it with g++ through
+// nvcc -x cu host pass) with `prmt` and the fp16 pair arithmetic emulated, which lets the unpack
+// logic be checked bit-for-bit against the CPU oracle without a GPU.
+#pragma once
+#include <cstdint>
+#include "../../include/quant_router.h"
+
+#if defined(__CUDACC__)
+#include <cuda_fp16.h>
+#define CDC_HD __host__ __device__ __forceinline__
+#else
+#define CDC_HD inline
+#endif
+
+namespace cdc {
+
+// ---- primitive helpers -------------------------------------------------------------------
+CDC_HD uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+#if defined(__CUDA_ARCH__)
+    return __byte_perm(a, b, sel);
+#else
+    uint64_t src = (uint64_t)a | ((uint64_t)b << 32);
+    uint32_t out = 0;
+    for (int i = 0; i < 4; i++) {
+        uint32_t n = (sel >> (4 * i)) & 7u;
+        out |= (uint32_t)((src >> (8 * n)) & 0xFF) << (8 * i);
+    }
+    return out;
+#endif
+}
+
+#if !defined(__CUDA_ARCH__)
+inline _Float16 bits2h(uint16_t b) { _Float16 h; __builtin_memcpy(&h, &b, 2); return h; }
+inline uint16_t h2bits(_Float16 h) { uint16_t b; __builtin_memcpy(&b, &h, 2); return b; }
+inline uint32_t pack2(_Float16 lo, _Float16 hi) { return (uint32_t)h2bits(lo) | ((uint32_t)h2bits(hi) << 16); }
+#endif
+
+// fp16x2 arithmetic on raw 32-bit words (each result rounded once, like the hardware)
+CDC_HD uint32_t h2sub(uint32_t a, uint32_t b) {
+#if defined(__CUDA_ARCH__)
+    __half2 r = __hsub2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+#else
+    return pack2((_Float16)((double)bits2h(a & 0xFFFF) - (double)bits2h(b & 0xFFFF)),
+                 (_Float16)((double)bits2h(a >> 16) - (double)bits2h(b >> 16)));
+#endif
+}
+CDC_HD uint32_t h2mul(uint32_t a, uint32_t b) {
+#if defined(__CUDA_ARCH__)
+    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+#else
+    return pack2((_Float16)((double)bits2h(a & 0xFFFF) * (double)bits2h(b & 0xFFFF)),
+                 (_Float16)((double)bits2h(a >> 16) * (double)bits2h(b >> 16)));
+#endif
+}
+CDC_HD uint32_t h2fma(uint32_t a, uint32_t b, uint32_t c) {
+#if defined(__CUDA_ARCH__)
+    __half2 r = __hfma2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b), *reinterpret_cast<__half2*>(&c));
+    return *reinterpret_cast<uint32_t*>(&r);
+#else
+    return pack2((_Float16)((double)bits2h(a & 0xFFFF) * (double)bits2h(b & 0xFFFF) + (double)bits2h(c & 0xFFFF)),
+                 (_Float16)((double)bits2h(a >> 16) * (double)bits2h(b >> 16) + (double)bits2h(c >> 16)));
+#endif
+}
+CDC_HD float h_lo_to_float(uint32_t w) {
+#if defined(__CUDA_ARCH__)
+    return __half2float(__ushort_as_half((unsigned short)(w & 0xFFFF)));
+#else
+    return (float)bits2h(w & 0xFFFF);
+#endif
+}
+CDC_HD float h_hi_to_float(uint32_t w) { return h_lo_to_float(w >> 16); }
+CDC_HD uint32_t float_to_h(float f) {  // fp16 bits in the low half
+#if defined(__CUDA_ARCH__)
+    return (uint32_t)__half_as_ushort(__float2half_rn(f));
+#else
+    return (uint32_t)h2bits((_Float16)f);
+#endif
+}
+CDC_HD uint32_t dup16(uint32_t h) { return (h & 0xFFFFu) | (h << 16); }
+
+// 16-bit field at (even) byte offset `o` of the register file, copied into both halves
+CDC_HD uint32_t bcast16(const uint32_t* r, int o) {
+    return (o & 2) ? prmt(r[o >> 2], 0u, 0x3232u) : prmt(r[o >> 2], 0u, 0x1010u);
+}
+// bytes o, o+1 (o even) -> byte o in bits 0-7, byte o+1 in bits 16-23
+CDC_HD uint32_t spread_pair(const uint32_t* r, int o) {
+    return (o & 2) ? prmt(r[o >> 2], 0u, 0x4342u) : prmt(r[o >> 2], 0u, 0x4140u);
+}
+CDC_HD uint32_t byte_at(const uint32_t* r, int o) { return (r[o >> 2] >> (8 * (o & 3))) & 0xFFu; }
+
+constexpr uint32_t H2_1024 = 0x64006400u, H2_64 = 0x54005400u;
+constexpr uint32_t H2_1032 = 0x64086408u, H2_72 = 0x54805480u;   // 1024+8, 64+8
+constexpr uint32_t H2_1025 = 0x64016401u;
+
+// two bytes spread by spread_pair -> (1024 + low nibbles) and (64 + high nibbles)
+CDC_HD void nib_pairs(uint32_t sp, uint32_t& lo, uint32_t& hi) {
+    lo = (sp & 0x000F000Fu) | H2_1024;
+    hi = (sp & 0x00F000F0u) | H2_64;
+}
+
+// 8-entry fp16 table in L[0..3] (entry e in half e&1 of word e>>1), looked up for two indices at once
+CDC_HD uint32_t lut8_pair(const uint32_t* L, uint32_t q0, uint32_t q1) {
+    uint32_t sel = 0x1010u + 0x22u * (q0 & 3u) + 0x2200u * (q1 & 3u);
+    uint32_t wa = prmt(L[0], L[1], sel), wb = prmt(L[2], L[3], sel);
+    uint32_t m = ((q0 & 4u) ? 0x0000FFFFu : 0u) | ((q1 & 4u) ? 0xFFFF0000u : 0u);
+    return (wa & ~m) | (wb & m);
+}
+
+template <int FMT> struct Codec;
+
+// ---- Q4_0: 18 B / 32 (quant_router_kernels.metal:111-146) ---------------------------------
+template <> struct Codec<QUANT_Q4_0> {
+    static constexpr int ROW_BYTES = 144;   // 8 blocks per 256 elements
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
+#pragma unroll
+        for (int bi = 0; bi < 2; bi++) {
+            const int o = 18 * (2 * s + bi);
+            const uint32_t d2 = bcast16(r, o);
+#pragma unroll
+            for (int p = 0; p < 8; p++) {
+                uint32_t lo, hi;
+                nib_pairs(spread_pair(r, o + 2 + 2 * p), lo, hi);
+                out[16 * bi + p] = h2mul(h2sub(lo, H2_1032), d2);       // elements 2p, 2p+1
+                out[16 * bi + 8 + p] = h2mul(h2sub(hi, H2_72), d2);     // elements 16+2p, 17+2p
+            }
+        }
+    }
+};
+
+// ---- MLX 4-bit affine, 20 B / 32 (quant_router_kernels.metal:149-185) -----------------------
+template <> struct Codec<QUANT_MLX_4BIT> {
+    static constexpr int ROW_BYTES = 160;
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
+#pragma unroll
+        for (int bi = 0; bi < 2; bi++) {
+            const int o = 20 * (2 * s + bi);
+            const uint32_t d2 = bcast16(r, o), b2 = bcast16(r, o + 2);
+#pragma unroll
+            for (int p = 0; p < 8; p++) {
+                uint32_t lo, hi;
+                nib_pairs(spread_pair(r, o + 4 + 2 * p), lo, hi);
+                out[16 * bi + p] = h2fma(h2sub(lo, H2_1024), d2, b2);
+                out[16 * bi + 8 + p] = h2fma(h2sub(hi, H2_64), d2, b2);
+            }
+        }
+    }
+};
+
+// ---- Q4_K, 144 B / 256 (quant_router_kernels.metal:188-238; gold cpu_gold_reference.h:116-146) --
+template <> struct Codec<QUANT_Q4_K> {
+    static constexpr int ROW_BYTES = 144;
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
+        const uint32_t d_dmin = r[0];   // (d, dmin) as an fp16 pair
+#pragma unroll
+        for (int bi = 0; bi < 2; bi++) {
+            const int j = 2 * s + bi;
+            const uint32_t sj = byte_at(r, 4 + j);
+            uint32_t sc = sj & 63u, mn;
+            if (j < 4) mn = (byte_at(r, 4 + j + 8) & 15u) | ((sj >> 6) << 4);
+            else       mn = (byte_at(r, 4 + j + 4) >> 4) | ((sj >> 6) << 4);
+            // (sc, mn) as exact fp16.  q*sc <= 945 is exact in fp16, so w = fma(q*sc, d, -m_sub) rounds the
+            // product once (tighter than the reference's fp16 d*sc, which rounds the sub-scale first);
+            // m_sub = dmin*mn is rounded once as in the reference.
+            const uint32_t scm = h2sub((sc | (mn << 16)) | H2_1024, H2_1024);
+            const uint32_t sc2 = prmt(scm, 0u, 0x1010u);
+            const uint32_t negm2 = prmt(h2mul(scm, d_dmin), 0u, 0x3232u) ^ 0x80008000u;
+            const uint32_t d2 = prmt(d_dmin, 0u, 0x1010u);
+#pragma unroll
+            for (int p = 0; p < 8; p++) {
+                uint32_t lo, hi;
+                nib_pairs(spread_pair(r, 16 + 16 * j + 2 * p), lo, hi);
+                out[16 * bi + p] = h2fma(h2mul(h2sub(lo, H2_1024), sc2), d2, negm2);
+                out[16 * bi + 8 + p] = h2fma(h2mul(h2sub(hi, H2_64), sc2), d2, negm2);
+            }
+        }
+    }
+};
+
+// ---- ternary, 12 B / 32 (gold cpu_gold_reference.h:176-189: value = (code-1)*d, code 3 -> +2d) --
+template <> struct Codec<QUANT_TERNARY_1_58> {
+    static constexpr int ROW_BYTES = 96;
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
+#pragma unroll
+        for (int bi = 0; bi < 2; bi++) {
+            const int w = 3 * (2 * s + bi);
+            const uint32_t d2 = prmt(r[w], 0u, 0x1010u);
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const uint32_t q = r[w + 1 + u];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    uint32_t t = q >> (4 * i);
+                    uint32_t x = (t & 3u) | ((t << 14) & 0x30000u) | H2_1024;
+                    out[16 * bi + 8 * u + i] = h2mul(h2sub(x, H2_1025), d2);
+                }
+            }
+        }
+    }
+};
+
+// ---- EXL3-style codebook, 144 B / 256 (quant_router_kernels.metal:368-411; gold :342-389) ---------
+template <> struct Codec<QUANT_EXL3> {
+    static constexpr int ROW_BYTES = 144;
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
+        const float d = h_lo_to_float(r[0]), bias = h_hi_to_float(r[0]);
+#pragma unroll
+        for (int bi = 0; bi < 2; bi++) {
+            const int j = 2 * s + bi;
+            const float sub_scale = d * (float)byte_at(r, 4 + j) * 0.015625f;
+            const float sub_res = d * ((float)byte_at(r, 12 + j) - 128.0f) * 0.0078125f;
+            uint32_t L[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                float c0 = (float)(int8_t)byte_at(r, 20 + 2 * e), r0 = (float)(int8_t)byte_at(r, 28 + 2 * e);
+                float c1 = (float)(int8_t)byte_at(r, 21 + 2 * e), r1 = (float)(int8_t)byte_at(r, 29 + 2 * e);
+                L[e] = float_to_h(bias + sub_scale * c0 + sub_res * r0) |
+                       (float_to_h(bias + sub_scale * c1 + sub_res * r1) << 16);
+            }
+            const int w = 12 + 3 * j;
+            const uint32_t w0 = r[w], w1 = r[w + 1], w2 = r[w + 2];
+            const uint32_t v[4] = {w0 & 0xFFFFFFu, ((w0 >> 24) | (w1 << 8)) & 0xFFFFFFu,
+                                   ((w1 >> 16) | (w2 << 16)) & 0xFFFFFFu, w2 >> 8};
+#pragma unroll
+            for (int g = 0; g < 4; g++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    uint32_t t = v[g] >> (6 * i);
+                    out[16 * bi + 4 * g + i] = lut8_pair(L, t & 7u, (t >> 3) & 7u);
+                }
+        }
+    }
+};
+
+// ---- variable-rate affine, 160 B / 256 (quant_router_kernels.metal:265-365; gold :214-311) ---------
+template <> struct Codec<QUANT_VAR_RATE_AFFINE> {
+    static constexpr int ROW_BYTES = 160;
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
+        const float d = h_lo_to_float(r[0]), bias = h_hi_to_float(r[0]);
+#pragma unroll
+        for (int bi = 0; bi < 2; bi++) {
+            const int j = 2 * s + bi;
+            const int offs[8] = {0, 12, 24, 40, 56, 72, 88, 108};
+            const int w = 8 + offs[j] / 4;
+            const uint32_t sc2 = dup16(float_to_h(d * (float)byte_at(r, 4 + j) * 0.0625f));
+            const uint32_t bs2 = dup16(float_to_h(bias + d * ((float)byte_at(r, 12 + j) - 128.0f) * 0.0625f));
+            const uint32_t mode = byte_at(r, 20 + j);
+            const uint32_t bits = mode & 7u, perm = (mode >> 3) & 3u;
+            uint32_t pk[16];   // source-order pairs (2i, 2i+1)
+            if (bits == 3u) {
+                const uint32_t w0 = r[w], w1 = r[w + 1], w2 = r[w + 2];
+                const uint32_t v[4] = {w0 & 0xFFFFFFu, ((w0 >> 24) | (w1 << 8)) & 0xFFFFFFu,
+                                       ((w1 >> 16) | (w2 << 16)) & 0xFFFFFFu, w2 >> 8};
+#pragma unroll
+                for (int g = 0; g < 4; g++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        uint32_t t = v[g] >> (6 * i);
+                        uint32_t x = (t & 7u) | ((t << 13) & 0x70000u) | H2_1024;
+                        pk[4 * g + i] = h2fma(h2sub(x, 0x64046404u), sc2, bs2);      // q - 4
+                    }
+            } else if (bits == 5u) {
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    // 40-bit group g starts at bit 40g of the 20-byte run = bit 8g of word g
+                    const uint32_t a = r[w + g], b = r[w + g + 1];
+                    const uint64_t v = (g == 0) ? ((uint64_t)a | ((uint64_t)(b & 0xFFu) << 32))
+                                                : (((((uint64_t)b << 32) | a) >> (8 * g)) & 0xFFFFFFFFFFull);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        uint32_t t = (uint32_t)(v >> (10 * i));
+                        uint32_t x = (t & 31u) | ((t << 11) & 0x1F0000u) | H2_1024;
+                        pk[4 * g + i] = h2fma(h2sub(x, 0x64106410u), sc2, bs2);      // q - 16
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int p = 0; p < 8; p++) {
+                    uint32_t lo, hi;
+                    nib_pairs(spread_pair(r, 4 * w + 2 * p), lo, hi);
+                    pk[p] = h2fma(h2sub(lo, H2_1032), sc2, bs2);
+                    pk[8 + p] = h2fma(h2sub(hi, H2_72), sc2, bs2);
+                }
+            }
+            // destination permutation: 0 identity; 1 even sources first, then odd; 2 reversed
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                uint32_t ident = pk[i];
+                uint32_t deint = (i < 8) ? prmt(pk[2 * i], pk[2 * i + 1], 0x5410u)
+                                         : prmt(pk[2 * (i - 8)], pk[2 * (i - 8) + 1], 0x7632u);
+                uint32_t rev = prmt(pk[15 - i], 0u, 0x1032u);
+                out[16 * bi + i] = (perm == 1u) ? deint : ((perm == 2u) ? rev : ident);
+            }
+        }
+    }
+};
+
+}  // namespace cdc

@@ -1,0 +1,158 @@
+// RMSNorm, rotary embedding and the fp32 residual add used by the decoder layer.
+//
+// The reference has these only in its Python block (src/engine/model.py:39-45 RMSNorm in its own
+// code; :112-116 rotary embedding through a third-party array library, non-interleaved form), so
+// the CPU oracle for them is a restatement (oracle/oracle.cpp: orc_rmsnorm, orc_rope).
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "../../include/b200_bridge.h"
+#include "bridge_state.cuh"
+#include "layer_ops.cuh"
+
+namespace lops {
+
+// one CTA of 256 threads per row; each thread walks 8-element vectors
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const __half* __restrict__ X, const __half* __restrict__ W,
+                                                      __half* __restrict__ Y, uint32_t K, float eps) {
+    const __half* x = X + (size_t)blockIdx.x * K;
+    __half* y = Y + (size_t)blockIdx.x * K;
+    float ss = 0.0f;
+    const bool vec = (K % 8 == 0) && ((((uintptr_t)x | (uintptr_t)y | (uintptr_t)W) & 15u) == 0);
+    if (vec) {
+        for (uint32_t i = threadIdx.x; i < K / 8; i += blockDim.x) {
+            uint4 v = reinterpret_cast<const uint4*>(x)[i];
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; j++) { float2 f = __half22float2(h[j]); ss += f.x * f.x + f.y * f.y; }
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) { float f = __half2float(x[i]); ss += f * f; }
+    }
+    __shared__ float red[8];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += red[i];
+    const float r = 1.0f / sqrtf(tot / (float)K + eps);
+    if (vec) {
+        for (uint32_t i = threadIdx.x; i < K / 8; i += blockDim.x) {
+            uint4 v = reinterpret_cast<const uint4*>(x)[i], w = reinterpret_cast<const uint4*>(W)[i], o;
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+            const __half2* wh = reinterpret_cast<const __half2*>(&w);
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float2 f = __half22float2(h[j]), g = __half22float2(wh[j]);
+                __half2 n = __floats2half2_rn(f.x * r, f.y * r);          // rounded to fp16 first, as the reference does
+                float2 nf = __half22float2(n);
+                oh[j] = __floats2half2_rn(nf.x * g.x, nf.y * g.y);
+            }
+            reinterpret_cast<uint4*>(y)[i] = o;
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) {
+            __half n = __float2half_rn(__half2float(x[i]) * r);
+            y[i] = __float2half_rn(__half2float(n) * __half2float(W[i]));
+        }
+    }
+}
+
+__global__ void rope_kernel(__half* __restrict__ X, uint32_t M, uint32_t D, float log2_theta, uint32_t pos0, size_t total_pairs) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total_pairs) return;
+    const uint32_t half = D / 2;
+    const uint32_t j = (uint32_t)(i % half);
+    const size_t row = i / half;                 // h*M + m
+    const uint32_t m = (uint32_t)(row % M);
+    const float inv_freq = exp2f(-2.0f * (float)j / (float)D * log2_theta);
+    const float ang = (float)(pos0 + m) * inv_freq;
+    float s, c;
+    sincosf(ang, &s, &c);
+    __half* x = X + row * D;
+    const float a = __half2float(x[j]), b = __half2float(x[j + half]);
+    x[j] = __float2half_rn(a * c - b * s);
+    x[j + half] = __float2half_rn(b * c + a * s);
+}
+
+__global__ void add_residual_f32_kernel(const __half* __restrict__ A, const float* __restrict__ B, __half* __restrict__ Y, size_t n) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i + 3 < n) {
+        const float4 b = *reinterpret_cast<const float4*>(B + i);
+        const __half2 a0 = *reinterpret_cast<const __half2*>(A + i), a1 = *reinterpret_cast<const __half2*>(A + i + 2);
+        *reinterpret_cast<__half2*>(Y + i) = __floats2half2_rn(__low2float(a0) + b.x, __high2float(a0) + b.y);
+        *reinterpret_cast<__half2*>(Y + i + 2) = __floats2half2_rn(__low2float(a1) + b.z, __high2float(a1) + b.w);
+    } else {
+        for (size_t k = i; k < n; k++) Y[k] = __float2half_rn(__half2float(A[k]) + B[k]);
+    }
+}
+
+cudaError_t rmsnorm(const void* X, const void* weight, void* Y, uint32_t M, uint32_t K, float eps, cudaStream_t s) {
+    rmsnorm_kernel<<<M, 256, 0, s>>>((const __half*)X, (const __half*)weight, (__half*)Y, K, eps);
+    return cudaGetLastError();
+}
+cudaError_t rope(void* X, uint32_t H, uint32_t M, uint32_t D, float theta, uint32_t pos0, cudaStream_t s) {
+    const size_t pairs = (size_t)H * M * (D / 2);
+    rope_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>((__half*)X, M, D, log2f(theta), pos0, pairs);
+    return cudaGetLastError();
+}
+cudaError_t add_residual_f32(const void* A, const float* B, void* Y, size_t n, cudaStream_t s) {
+    const size_t threads = (n + 3) / 4;
+    add_residual_f32_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>((const __half*)A, B, (__half*)Y, n);
+    return cudaGetLastError();
+}
+
+}  // namespace lops
+
+using namespace bridge;
+
+extern "C" {
+
+int b200_bridge_rmsnorm(void* X, void* weight, void* Y, uint32_t M, uint32_t K, float eps) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!X || !weight || !Y) return -2;
+    if (M == 0 || K == 0) return -4;
+    int rc = 0;
+    const size_t bytes = (size_t)M * K * 2;
+    const void* x = resolve_in(X, bytes, g.stage_x, false, &rc);
+    if (rc) return rc;
+    const void* w = resolve_in(weight, (size_t)K * 2, g.stage_aux0, false, &rc);
+    if (rc) return rc;
+    void* host_dst = nullptr;
+    void* y = resolve_out(Y, bytes, g.stage_y, &host_dst, &rc);
+    if (rc) return rc;
+    if (lops::rmsnorm(x, w, y, M, K, eps, g.stream) != cudaSuccess) return -6;
+    g.launches++;
+    if (host_dst) { cudaMemcpyAsync(host_dst, y, bytes, cudaMemcpyDeviceToHost, g.stream); g.d2h_bytes += bytes; }
+    return 0;
+}
+
+/* In-place rotary embedding on X [H][M][D] (device or host pointer). */
+int b200_bridge_rope(void* X, uint32_t H, uint32_t M, uint32_t D, float theta, uint32_t pos0) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!X) return -2;
+    if (H == 0 || M == 0 || D == 0 || (D % 2) != 0 || theta <= 0.0f) return -4;
+    const size_t bytes = (size_t)H * M * D * 2;
+    if (is_device_ptr(X)) {
+        if (lops::rope(X, H, M, D, theta, pos0, g.stream) != cudaSuccess) return -6;
+        g.launches++;
+        return 0;
+    }
+    int rc = 0;
+    void* x = const_cast<void*>(resolve_in(X, bytes, g.stage_x, false, &rc));
+    if (rc) return rc;
+    if (lops::rope(x, H, M, D, theta, pos0, g.stream) != cudaSuccess) return -6;
+    g.launches++;
+    cudaMemcpyAsync(X, x, bytes, cudaMemcpyDeviceToHost, g.stream);
+    g.d2h_bytes += bytes;
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,24 @@
+// Small per-layer kernels around the GEMMs and the attention kernel (internal interface).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+
+namespace lops {
+// Y[m][:] = fp16( fp16(x * rsqrt(mean(x^2) + eps)) * w ), sums in fp32.
+cudaError_t rmsnorm(const void* X, const void* weight, void* Y, uint32_t M, uint32_t K, float eps, cudaStream_t s);
+// Rotate-half rotary embedding in place on X [H][M][D]; positions pos0 .. pos0+M-1.
+cudaError_t rope(void* X, uint32_t H, uint32_t M, uint32_t D, float theta, uint32_t pos0, cudaStream_t s);
+// Y = fp16(float(A) + B) elementwise, A fp16, B fp32 (residual add after an fp32 all-reduce).
+cudaError_t add_residual_f32(const void* A_f16, const float* B_f32, void* Y_f16, size_t n, cudaStream_t s);
+}  // namespace lops
+
+namespace attn {
+struct Params;
+cudaError_t launch_quantize(const void* src, void* dst, size_t n_elements, cudaStream_t stream);
+cudaError_t launch_dequantize(const void* src, void* dst, size_t n_elements, cudaStream_t stream);
+// thin wrapper so other translation units need not see attn::Params
+cudaError_t launch_attention_simple(const void* Q, const void* K, const void* V, void* O, uint32_t Hq, uint32_t Hkv,
+                                    uint32_t M, uint32_t Mkv, uint32_t D, float scale, uint32_t pos0, int out_tokens_major,
+                                    int kv_fp16, cudaStream_t stream);
+}  // namespace attn

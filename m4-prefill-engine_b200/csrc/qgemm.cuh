@@ -1,0 +1,40 @@
+// Host-side interface of the dequant-fused projection kernels (internal to the library; the
+// public surface is include/b200_bridge.h).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+
+namespace qg {
+
+struct GemmArgs {
+    int format;               // QuantFormat id
+    const void* X;            // [M][K] fp16, device
+    const void* W0;           // packed weights [N][K/blk] (gate matrix for SwiGLU)
+    const void* W1;           // up matrix for SwiGLU, else nullptr
+    void* Y;                  // fp16 out: [M][N], or [H][M][D] when layout == 1
+    uint32_t M, N, K;
+    int layout;               // LayoutMode
+    uint32_t H, D;            // direct-head split of N
+    const void* residual;     // optional fp16 [M][N] added in the epilogue (standard layout only)
+    float* partial_out;       // optional fp32 [M][N]: write raw accumulators instead of fp16 Y
+    int force_generic;        // testing hook: use the CUDA-core fallback kernel
+};
+
+struct Workspace {            // split-K scratch, owned by the caller
+    float* partial = nullptr; // >= partial_floats
+    size_t partial_floats = 0;
+    uint32_t* counters = nullptr;  // >= 4096 zero-initialised words; the kernel leaves them zero
+    int* err = nullptr;       // device error word (0 = ok)
+};
+
+// True if (format, shape, pointers) can take the TMA + tcgen05 path.
+bool fast_path_ok(const GemmArgs& a);
+// Floats of split-K scratch the launch will use (0 when it does not split).
+size_t workspace_floats(const GemmArgs& a);
+// Enqueue on `stream`.  Returns cudaSuccess or the launch error.
+cudaError_t launch(const GemmArgs& a, const Workspace& ws, cudaStream_t stream);
+// Number of kernels the last launch() enqueued (1, or 2 with the generic tail) -- for launch accounting.
+int last_launch_count();
+
+}  // namespace qg

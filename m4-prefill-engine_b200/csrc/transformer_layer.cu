@@ -1,0 +1,269 @@
+// TransformerLayerCoordinator: composition of the hot-path kernels into one decoder layer
+// (reference: models/transformer_layer.mm:7-218 for the shape of the class,
+// bench_8b_engine.mm:74-225 for what the layer computes and where it rounds to fp16).
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/b200_bridge.h"
+#include "../../include/transformer_layer.h"
+#include "bridge_state.cuh"
+#include "layer_ops.cuh"
+#include "qgemm.cuh"
+
+namespace b200_llm {
+
+struct TransformerLayerCoordinator::Impl {
+    // intermediates (device)
+    void *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *kq = nullptr, *vq = nullptr;
+    void *attn = nullptr, *x_mid = nullptr, *act = nullptr;
+    float* partial = nullptr;        // tensor-parallel partial sums [M][K]
+    float* ws = nullptr;             // split-K scratch
+    size_t ws_floats = 0;
+    uint32_t* counters = nullptr;
+    int* err = nullptr;
+    const void *norm1 = nullptr, *norm2 = nullptr;
+    AllReduceFn allreduce = nullptr;
+    void* allreduce_ctx = nullptr;
+    KernelBinding gemm_binding, head_binding;
+    bool bound = false;
+    cudaStream_t stream = nullptr;
+};
+
+static bool dev_alloc(void** p, size_t bytes) {
+    if (cudaMalloc(p, bytes ? bytes : 16) != cudaSuccess) { cudaGetLastError(); *p = nullptr; return false; }
+    return true;
+}
+
+TransformerLayerCoordinator::TransformerLayerCoordinator(int device, cudaStream_t stream, const TransformerLayerConfig& config)
+    : impl_(new Impl), config_(config), device_(device) {
+    if (config_.num_kv_heads == 0) config_.num_kv_heads = config_.H;
+    if (config_.tp_size == 0) config_.tp_size = 1;
+    impl_->stream = stream;
+}
+
+TransformerLayerCoordinator::~TransformerLayerCoordinator() {
+    void* bufs[] = {impl_->xn, impl_->q, impl_->k, impl_->v, impl_->kq, impl_->vq, impl_->attn, impl_->x_mid, impl_->act,
+                    impl_->partial, impl_->ws, impl_->counters};
+    for (void* b : bufs) if (b) cudaFree(b);
+    delete impl_;
+}
+
+bool TransformerLayerCoordinator::initialize_pipelines(const void*) {
+    const TransformerLayerConfig& c = config_;
+    const QuantCodecDescriptor* d = QuantRegistry::instance().get(c.weight_format);
+    if (!d) { status_ = -3; return false; }
+    impl_->gemm_binding = QuantRegistry::instance().resolve_kernel(d->gemm_kernel_name);
+    impl_->head_binding = QuantRegistry::instance().resolve_kernel(d->head_gemm_kernel_name);
+    if (!impl_->gemm_binding.valid || !impl_->gemm_binding.implemented || !impl_->head_binding.valid ||
+        !impl_->head_binding.implemented) { status_ = -3; return false; }
+    if (c.M == 0 || c.K == 0 || c.H == 0 || c.D == 0 || c.N_mlp == 0) { status_ = -4; return false; }
+    if (c.H % c.tp_size || c.num_kv_heads % c.tp_size || c.N_mlp % c.tp_size || c.H % c.num_kv_heads) { status_ = -4; return false; }
+    if (c.D != 64 && c.D != 128) { status_ = -4; return false; }
+    const uint32_t hq = c.H / c.tp_size, hkv = c.num_kv_heads / c.tp_size, f = c.N_mlp / c.tp_size;
+    if (d->block_size && ((c.K % d->block_size) || ((hq * c.D) % d->block_size) || (f % d->block_size))) { status_ = -4; return false; }
+    cudaSetDevice(device_);
+    const size_t MK = (size_t)c.M * c.K * 2;
+    bool ok = dev_alloc(&impl_->xn, MK) && dev_alloc(&impl_->x_mid, MK) &&
+              dev_alloc(&impl_->q, (size_t)c.M * hq * c.D * 2) && dev_alloc(&impl_->k, (size_t)c.M * hkv * c.D * 2) &&
+              dev_alloc(&impl_->v, (size_t)c.M * hkv * c.D * 2) && dev_alloc(&impl_->attn, (size_t)c.M * hq * c.D * 2) &&
+              dev_alloc(&impl_->act, (size_t)c.M * f * 2);
+    if (ok && c.kv_q8_0) {
+        const size_t qb = (size_t)c.M * hkv * c.D / 32 * 34;
+        ok = dev_alloc(&impl_->kq, qb) && dev_alloc(&impl_->vq, qb);
+    }
+    if (ok && c.tp_size > 1) ok = dev_alloc((void**)&impl_->partial, (size_t)c.M * c.K * 4);
+    // split-K scratch: sized for the largest projection of this layer (tokens <= 256 per tile)
+    if (ok) {
+        size_t need = 0;
+        const uint32_t ns[4] = {hq * c.D, hkv * c.D, c.K, f};
+        const uint32_t ks[4] = {c.K, c.K, hq * c.D, c.K};
+        for (int i = 0; i < 4; i++) {
+            qg::GemmArgs a; memset(&a, 0, sizeof(a));
+            a.format = c.weight_format; a.M = c.M; a.N = ns[i]; a.K = ks[i];
+            a.X = (const void*)16; a.W0 = (const void*)16; a.Y = (void*)16;   // alignment probes only
+            size_t w = qg::workspace_floats(a);
+            if (w > need) need = w;
+        }
+        { qg::GemmArgs a; memset(&a, 0, sizeof(a)); a.format = c.weight_format; a.M = c.M; a.N = c.K; a.K = f;
+          a.X = (const void*)16; a.W0 = (const void*)16; a.Y = (void*)16; size_t w = qg::workspace_floats(a); if (w > need) need = w; }
+        impl_->ws_floats = need;
+        if (need) ok = dev_alloc((void**)&impl_->ws, need * 4);
+        if (ok) ok = dev_alloc((void**)&impl_->counters, 4096 * 4 + 64);
+        if (ok) {
+            cudaMemset(impl_->counters, 0, 4096 * 4 + 64);
+            impl_->err = reinterpret_cast<int*>(impl_->counters + 4096);
+        }
+    }
+    if (!ok) { status_ = -5; return false; }
+    impl_->bound = true;
+    status_ = 0;
+    return true;
+}
+
+void TransformerLayerCoordinator::set_norm_weights(const void* a, const void* m) { impl_->norm1 = a; impl_->norm2 = m; }
+void TransformerLayerCoordinator::set_allreduce(AllReduceFn fn, void* ctx) { impl_->allreduce = fn; impl_->allreduce_ctx = ctx; }
+
+void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in, const void* W_q, const void* W_k,
+                                          const void* W_v, const void* W_o, const void* W_gate, const void* W_up,
+                                          const void* W_down, void* X_out) {
+    const TransformerLayerConfig& c = config_;
+    Impl& im = *impl_;
+    launches_ = 0;
+    if (!im.bound) { status_ = -1; return; }
+    if (!X_in || !W_q || !W_k || !W_v || !W_o || !W_gate || !W_up || !W_down || !X_out) { status_ = -2; return; }
+    if (c.rms_eps > 0.0f && (!im.norm1 || !im.norm2)) { status_ = -2; return; }
+    if (c.tp_size > 1 && !im.allreduce) { status_ = -2; return; }
+    status_ = 0;
+    const uint32_t hq = c.H / c.tp_size, hkv = c.num_kv_heads / c.tp_size, f = c.N_mlp / c.tp_size;
+    qg::Workspace ws;
+    ws.partial = im.ws; ws.partial_floats = im.ws_floats; ws.counters = im.counters; ws.err = im.err;
+
+    auto gemm = [&](const KernelBinding& kb, const void* X, const void* W0, const void* W1, void* Y, uint32_t N, uint32_t K,
+                    uint32_t H, const void* residual, float* partial_out) {
+        if (status_) return;
+        qg::GemmArgs a; memset(&a, 0, sizeof(a));
+        a.format = kb.format; a.X = X; a.W0 = W0; a.W1 = W1; a.Y = Y; a.M = c.M; a.N = N; a.K = K;
+        a.layout = kb.layout; a.H = H; a.D = c.D; a.residual = residual; a.partial_out = partial_out;
+        if (qg::launch(a, ws, stream) != cudaSuccess) { status_ = -6; return; }
+        launches_ += (uint32_t)qg::last_launch_count();
+    };
+    auto check = [&](cudaError_t e) { if (e != cudaSuccess && !status_) status_ = -6; else launches_++; };
+
+    // 1. attention block
+    const void* x_attn = X_in;
+    if (c.rms_eps > 0.0f) { check(lops::rmsnorm(X_in, im.norm1, im.xn, c.M, c.K, c.rms_eps, stream)); x_attn = im.xn; }
+    gemm(im.head_binding, x_attn, W_q, nullptr, im.q, hq * c.D, c.K, hq, nullptr, nullptr);
+    gemm(im.head_binding, x_attn, W_k, nullptr, im.k, hkv * c.D, c.K, hkv, nullptr, nullptr);
+    gemm(im.head_binding, x_attn, W_v, nullptr, im.v, hkv * c.D, c.K, hkv, nullptr, nullptr);
+    if (c.rope_theta > 0.0f) {
+        check(lops::rope(im.q, hq, c.M, c.D, c.rope_theta, 0, stream));
+        check(lops::rope(im.k, hkv, c.M, c.D, c.rope_theta, 0, stream));
+    }
+    const void *kk = im.k, *vv = im.v;
+    if (c.kv_q8_0) {
+        check(attn::launch_quantize(im.k, im.kq, (size_t)hkv * c.M * c.D, stream));
+        check(attn::launch_quantize(im.v, im.vq, (size_t)hkv * c.M * c.D, stream));
+        kk = im.kq; vv = im.vq;
+    }
+    check(attn::launch_attention_simple(im.q, kk, vv, im.attn, hq, hkv, c.M, c.M, c.D, c.attn_scale, 0, 1, c.kv_q8_0 ? 0 : 1, stream));
+    // 2. O projection + first residual
+    if (c.tp_size == 1) {
+        gemm(im.gemm_binding, im.attn, W_o, nullptr, im.x_mid, c.K, hq * c.D, 0, X_in, nullptr);
+    } else {
+        gemm(im.gemm_binding, im.attn, W_o, nullptr, nullptr, c.K, hq * c.D, 0, nullptr, im.partial);
+        if (!status_) im.allreduce(im.allreduce_ctx, im.partial, (size_t)c.M * c.K, stream);
+        check(lops::add_residual_f32(X_in, im.partial, im.x_mid, (size_t)c.M * c.K, stream));
+    }
+    // 3. MLP
+    const void* x_mlp = im.x_mid;
+    if (c.rms_eps > 0.0f) { check(lops::rmsnorm(im.x_mid, im.norm2, im.xn, c.M, c.K, c.rms_eps, stream)); x_mlp = im.xn; }
+    gemm(im.gemm_binding, x_mlp, W_gate, W_up, im.act, f, c.K, 0, nullptr, nullptr);
+    if (c.tp_size == 1) {
+        gemm(im.gemm_binding, im.act, W_down, nullptr, X_out, c.K, f, 0, im.x_mid, nullptr);
+    } else {
+        gemm(im.gemm_binding, im.act, W_down, nullptr, nullptr, c.K, f, 0, nullptr, im.partial);
+        if (!status_) im.allreduce(im.allreduce_ctx, im.partial, (size_t)c.M * c.K, stream);
+        check(lops::add_residual_f32(im.x_mid, im.partial, X_out, (size_t)c.M * c.K, stream));
+    }
+}
+
+}  // namespace b200_llm
+
+// ---------------------------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------------------------
+using namespace bridge;
+using b200_llm::TransformerLayerCoordinator;
+
+namespace {
+struct LayerHandle {
+    TransformerLayerCoordinator* layer;
+    void (*py_fn)(void*, void*, size_t) = nullptr;
+    void* py_ctx = nullptr;
+    DevBuf stage_in, stage_out;
+};
+void allreduce_trampoline(void* ctx, float* buf, size_t count, cudaStream_t) {
+    LayerHandle* h = (LayerHandle*)ctx;
+    h->py_fn(h->py_ctx, buf, count);
+}
+}  // namespace
+
+extern "C" {
+
+void* b200_layer_create(const b200_layer_config* cfg) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized || !cfg) return nullptr;
+    b200_llm::TransformerLayerConfig c;
+    c.M = cfg->M; c.K = cfg->K; c.H = cfg->H; c.D = cfg->D; c.N_mlp = cfg->N_mlp; c.attn_scale = cfg->attn_scale;
+    c.weight_format = (QuantFormat)cfg->weight_format; c.num_kv_heads = cfg->num_kv_heads; c.rms_eps = cfg->rms_eps;
+    c.rope_theta = cfg->rope_theta; c.kv_q8_0 = cfg->kv_q8_0 != 0; c.tp_size = cfg->tp_size ? cfg->tp_size : 1;
+    LayerHandle* h = new LayerHandle;
+    h->layer = new TransformerLayerCoordinator(g.device, g.stream, c);
+    if (!h->layer->initialize_pipelines(nullptr)) {
+        set_error("layer: initialize_pipelines failed with status " + std::to_string(h->layer->last_status()));
+        delete h->layer; delete h;
+        return nullptr;
+    }
+    return h;
+}
+
+void b200_layer_destroy(void* layer) {
+    if (!layer) return;
+    std::lock_guard<std::mutex> lock(g.mu);
+    LayerHandle* h = (LayerHandle*)layer;
+    if (g.initialized) cudaStreamSynchronize(g.stream);
+    h->stage_in.release(); h->stage_out.release();
+    delete h->layer;
+    delete h;
+}
+
+int b200_layer_set_norm_weights(void* layer, const void* a, const void* m) {
+    if (!layer || !a || !m) return -2;
+    ((LayerHandle*)layer)->layer->set_norm_weights(a, m);
+    return 0;
+}
+
+int b200_layer_set_allreduce(void* layer, void (*fn)(void*, void*, size_t), void* ctx) {
+    if (!layer || !fn) return -2;
+    LayerHandle* h = (LayerHandle*)layer;
+    h->py_fn = fn; h->py_ctx = ctx;
+    h->layer->set_allreduce(allreduce_trampoline, h);
+    return 0;
+}
+
+int b200_layer_forward(void* layer, const void* X_in, const void* W_q, const void* W_k, const void* W_v, const void* W_o,
+                       const void* W_gate, const void* W_up, const void* W_down, void* X_out) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!layer || !X_in || !X_out) return -2;
+    LayerHandle* h = (LayerHandle*)layer;
+    const auto& c = h->layer->config();
+    const size_t bytes = (size_t)c.M * c.K * 2;
+    int rc = 0;
+    const void* x = resolve_in(X_in, bytes, h->stage_in, false, &rc);
+    if (rc) return rc;
+    void* host_dst = nullptr;
+    void* y = resolve_out(X_out, bytes, h->stage_out, &host_dst, &rc);
+    if (rc) return rc;
+    const void* w[7] = {W_q, W_k, W_v, W_o, W_gate, W_up, W_down};
+    for (int i = 0; i < 7; i++) {
+        if (!w[i]) return -2;
+        if (!is_device_ptr(w[i])) {
+            auto it = g.registered.find(w[i]);
+            if (it == g.registered.end()) { set_error("layer weights must be device pointers or registered host buffers"); return -2; }
+            w[i] = it->second.dev;
+        }
+    }
+    h->layer->forward(g.stream, x, w[0], w[1], w[2], w[3], w[4], w[5], w[6], y);
+    if (h->layer->last_status()) return h->layer->last_status();
+    g.launches += h->layer->kernels_per_forward();
+    if (host_dst) { cudaMemcpyAsync(host_dst, y, bytes, cudaMemcpyDeviceToHost, g.stream); g.d2h_bytes += bytes; }
+    return 0;
+}
+
+uint32_t b200_layer_kernels_per_forward(void* layer) { return layer ? ((LayerHandle*)layer)->layer->kernels_per_forward() : 0; }
+
+}  // extern "C"
