@@ -1,0 +1,180 @@
+"""Projection GEMM parity on the GPU, through the C ABI, against the CPU oracle.
+
+Test plan follows the reference's: tier-1 parity at 1/128 for every format at the M boundary set
+(tests/e2e/test_tier1_feature_coverage.mm:122-223), unit-weight known answers and shape/error probes
+of the bridge (tests/test_bridge_basic.py, tests/redteam_bridge.py:274-471), then the benchmark shapes."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import oracle as o
+from gpu_util import TOL, check, dev, run_gemm
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+BRIDGE_FORMATS = (o.Q4_0, o.MLX_4BIT, o.Q4_K, o.TERNARY_1_58, o.VAR_RATE_AFFINE, o.EXL3)
+
+
+@pytest.mark.parametrize("fmt", BRIDGE_FORMATS)
+@pytest.mark.parametrize("M", [33, 127, 128, 129, 512])
+def test_tier1_parity(bridge, fmt, M):
+    K, N = 512, 256
+    g = o.RefLcg(1337)
+    W = g.weights(fmt, K, N)
+    X = g.activations(M, K)
+    Y = run_gemm(bridge, fmt, X, W, N)
+    diff = np.abs(Y.astype(np.float64) - o.gemm_f64(fmt, X, W, N))
+    assert diff.max() <= TOL, f"max-abs {diff.max()}"
+
+
+@pytest.mark.parametrize("fmt", BRIDGE_FORMATS)
+def test_golden_fixture_and_direct_head(bridge, fmt):
+    z = np.load(GOLD / "gemm_tier1.npz")
+    X = z[f"X{fmt}"].view(np.float16)
+    W = z[f"W{fmt}"]
+    Y = run_gemm(bridge, fmt, X, W, 256)
+    assert np.abs(Y.astype(np.float32) - z[f"Y{fmt}"].view(np.float16).astype(np.float32)).max() <= TOL
+    Yh = run_gemm(bridge, fmt, X, W, 256, layout=1, H=4, D=64)
+    assert np.abs(Yh.astype(np.float32) - z[f"Yh{fmt}"].view(np.float16).astype(np.float32)).max() <= TOL
+    # the head-major result is the standard result re-laid out, bit for bit
+    assert np.array_equal(Yh.view(np.uint16), Y.reshape(33, 4, 64).transpose(1, 0, 2).copy().view(np.uint16))
+
+
+@pytest.mark.parametrize("fmt", [o.Q4_0, o.MLX_4BIT, o.TERNARY_1_58, o.Q4_K])
+@pytest.mark.parametrize("shape", [(33, 64, 64), (64, 64, 64), (128, 128, 128), (33, 256, 256), (1, 512, 128)])
+def test_unit_weights_give_k(bridge, pkg, fmt, shape):
+    from m4_prefill_engine_b200.modules import unit_weights
+    M, K, N = shape
+    if fmt == o.Q4_K and K % 256:
+        pytest.skip("super-block format needs K % 256 == 0")
+    W = unit_weights(fmt, K, N).numpy()
+    Y = run_gemm(bridge, fmt, np.ones((M, K), np.float16), W, N)
+    assert np.all(Y == np.float16(K))
+
+
+def test_error_codes(bridge):
+    L = bridge.lib
+    X = torch.zeros(64 * 256, dtype=torch.float16, device="cuda")
+    W = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    Y = torch.zeros(64 * 256, dtype=torch.float16, device="cuda")
+    xp, wp, yp = X.data_ptr(), W.data_ptr(), Y.data_ptr()
+    xb, wb, yb = X.numel() * 2, W.numel(), Y.numel() * 2
+    call = L.m4_bridge_dispatch_gemm
+    assert call(None, xb, wp, wb, yp, yb, 0, 4, 64, 64) == -2
+    assert call(xp + 1, xb - 1, wp, wb, yp, yb, 0, 4, 64, 64) == -2          # odd fp16 pointer
+    for bad in (-1, 6, 999, -999):
+        assert call(xp, xb, wp, wb, yp, yb, bad, 4, 64, 64) == -3
+    assert call(xp, xb, wp, wb, yp, yb, 0, 0, 64, 64) == -4
+    assert call(xp, xb, wp, wb, yp, yb, 0, 4, 48, 64) == -4                  # K % 32
+    for sb in (2, 4, 5):
+        assert call(xp, xb, wp, wb, yp, yb, sb, 4, 128, 64) == -4            # K % 256 for super-blocks
+    assert call(xp, 4 * 64 * 2 - 2, wp, wb, yp, yb, 0, 4, 64, 64) == -2      # X too small
+    assert call(xp, xb, wp, 64 * 2 * 18 - 1, yp, yb, 0, 4, 64, 64) == -2     # W too small
+    assert call(xp, xb, wp, wb, yp, 4 * 64 * 2 - 2, 0, 4, 64, 64) == -2      # Y too small
+    assert call(xp, xb, wp, wb, yp, yb, 0, 4, 64, 64) == 0
+    with pytest.raises(RuntimeError, match="status code -3"):
+        bridge.dispatch_gemm(X, W, Y, 6, 4, 64, 64)
+    bridge.synchronize()
+
+
+@pytest.mark.parametrize("shape", [(5, 64, 33), (9, 64, 65), (33, 256, 33), (70, 512, 65), (3, 96, 10), (40, 288, 130)])
+def test_ragged_shapes(bridge, shape):
+    M, K, N = shape
+    g = o.RefLcg(5)
+    W = g.weights(o.Q4_0, K, N)
+    X = g.activations(M, K)
+    Y = run_gemm(bridge, o.Q4_0, X, W, N)
+    assert np.abs(Y.astype(np.float64) - o.gemm_f64(o.Q4_0, X, W, N)).max() <= TOL
+
+
+def test_every_format_on_the_fallback_kernel(bridge):
+    M, K, N = 17, 512, 40
+    for fmt in BRIDGE_FORMATS + (o.PRISM_Q2_0,):
+        g = o.RefLcg(8)
+        W = g.weights(fmt, K, N)
+        X = g.activations(M, K)
+        bridge.lib.b200_bridge_force_generic(1)
+        try:
+            Y = run_gemm(bridge, fmt, X, W, N, ex=True)
+        finally:
+            bridge.lib.b200_bridge_force_generic(0)
+        assert np.abs(Y.astype(np.float64) - o.gemm_f64(fmt, X, W, N)).max() <= TOL
+
+
+@pytest.mark.parametrize("fmt", [o.MLX_4BIT_G64, o.TERNARY_ROW])
+def test_extension_layouts(bridge, fmt):
+    M, K, N = 33, 512, 96
+    X, W = o.baseline_inputs(fmt, M, K, N, 3)
+    check(run_gemm(bridge, fmt, X, W, N, ex=True), o.gemm_f64(fmt, X, W, N), f"fmt {fmt}")
+
+
+def test_host_pointers_and_gemv(bridge):
+    K, N = 512, 256
+    g = o.RefLcg(3)
+    W = g.weights(o.Q4_0, K, N)
+    X = g.activations(33, K)
+    a = run_gemm(bridge, o.Q4_0, X, W, N)
+    b = run_gemm(bridge, o.Q4_0, X, W, N, host=True)           # pageable host memory in and out
+    assert np.array_equal(a.view(np.uint16), b.view(np.uint16))
+    Wt = torch.from_numpy(W)
+    assert bridge.register_weights(Wt) == 0                     # resident copy keyed by the host pointer
+    Yh = torch.zeros(33, N, dtype=torch.float16)
+    bridge.dispatch_gemm(torch.from_numpy(X), Wt, Yh, o.Q4_0, 33, K, N)
+    bridge.synchronize()
+    assert np.array_equal(Yh.numpy().view(np.uint16), a.view(np.uint16))
+    assert bridge.lib.b200_bridge_unregister_weights(Wt.data_ptr()) == 0
+    y = torch.zeros(N, dtype=torch.float16, device="cuda")
+    bridge.dispatch_gemv(dev(X[0]), dev(W), y, o.Q4_0, K, N)
+    bridge.synchronize()
+    assert np.abs(y.cpu().numpy().astype(np.float64) - o.gemm_f64(o.Q4_0, X[:1], W, N)[0]).max() <= TOL
+
+
+def test_residual_epilogue(bridge):
+    M, K, N = 130, 512, 256
+    g = o.RefLcg(4)
+    W = g.weights(o.Q4_0, K, N)
+    X = g.activations(M, K)
+    R = g.activations(M, N)
+    Y = run_gemm(bridge, o.Q4_0, X, W, N, residual=R)
+    gold = o.gemm_f64(o.Q4_0, X, W, N) + R.astype(np.float64)
+    assert np.abs(Y.astype(np.float64) - gold).max() <= TOL
+
+
+# ---- benchmark shapes (K = N = 4096; the value distributions the benchmark contract names) ----
+@pytest.mark.parametrize("fmt", [o.Q4_0, o.MLX_4BIT, o.Q4_K, o.TERNARY_1_58, o.VAR_RATE_AFFINE, o.EXL3, o.MLX_4BIT_G64,
+                                 o.TERNARY_ROW])
+@pytest.mark.parametrize("M", [33, 128, 129])
+def test_8b_projection_small_m(bridge, fmt, M):
+    K = N = 4096
+    X, W = o.baseline_inputs(fmt, M, K, N, 100 + M)
+    check(run_gemm(bridge, fmt, X, W, N, ex=fmt > 5), o.gemm_f64(fmt, X, W, N), f"fmt {fmt} M {M}")
+
+
+@pytest.mark.parametrize("fmt", [o.Q4_0, o.MLX_4BIT, o.Q4_K, o.TERNARY_1_58])
+def test_8b_projection_m2048(bridge, fmt):
+    """Full size: sampled token rows (including both ragged ends of every 256-token tile) against the oracle,
+    plus two size-independent properties: runs are bit-reproducible, and permuting token rows permutes
+    output rows bit for bit (each output is an independent K-ordered sum)."""
+    M, K, N = 2048, 4096, 4096
+    X, W = o.baseline_inputs(fmt, M, K, N, 7)
+    Y = run_gemm(bridge, fmt, X, W, N)
+    rows = np.unique(np.concatenate([np.arange(0, M, 256), np.arange(255, M, 256), np.random.default_rng(0).integers(0, M, 40)]))
+    check(Y[rows], o.gemm_f64(fmt, X[rows], W, N), f"fmt {fmt}")
+    assert np.array_equal(Y.view(np.uint16), run_gemm(bridge, fmt, X, W, N).view(np.uint16))
+    perm = np.random.default_rng(1).permutation(M)
+    Yp = run_gemm(bridge, fmt, X[perm], W, N)
+    assert np.array_equal(Yp.view(np.uint16), Y[perm].view(np.uint16))
+
+
+def test_1b_reference_config_q4_0(bridge):
+    # the CPU-reference configuration: M=33, K=N=2048, d ~ U(0.005, 0.02), X ~ N(0,1)
+    X, W = o.baseline_inputs(o.Q4_0, 33, 2048, 2048, 42)
+    check(run_gemm(bridge, o.Q4_0, X, W, 2048), o.gemm_f64(o.Q4_0, X, W, 2048), "config 1")
+
+
+def test_ternary_n14336(bridge):
+    for fmt in (o.TERNARY_1_58, o.TERNARY_ROW):
+        X, W = o.baseline_inputs(fmt, 128, 4096, 14336, 9)
+        check(run_gemm(bridge, fmt, X, W, 14336, ex=fmt > 5), o.gemm_f64(fmt, X, W, 14336), f"ternary fmt {fmt}")

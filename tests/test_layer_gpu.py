@@ -1,0 +1,182 @@
+"""Decoder layer and the Linear wrapper on the GPU against the oracle's layer gold
+(bench_8b_engine.mm:376-705 verifies its pipeline against cpu_reference_prefill_layer the same way)."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import oracle as o
+from gpu_util import TOL, dev
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+
+
+SHRINK = {o.MLX_4BIT: 0.06, o.Q4_K: 0.03, o.TERNARY_1_58: 1.0}
+
+
+def layer_weights(fmt, K, H, Hkv, D, F, seed=1337):
+    g = o.RefLcg(seed)
+    shapes = {"q": (H * D, K), "k": (Hkv * D, K), "v": (Hkv * D, K), "o": (K, H * D), "gate": (F, K), "up": (F, K), "down": (K, F)}
+    if fmt == o.Q4_0:   # the reference layer's own scale range (bench_8b_engine.mm:44-53)
+        return {n: g.q4_0_bench(k, r, 0.003, 0.0003) for n, (r, k) in shapes.items()}, g
+    # other formats: the reference's generator ranges, with the fp16 scale fields shrunk so that a whole
+    # layer (two residual blocks deep) stays far inside the fp16 range
+    out = {}
+    for n, (r, k) in shapes.items():
+        be, bb = o.BLOCK[fmt]
+        blocks = g.weights(fmt, k, r).reshape(-1, bb)
+        nfields = 1 if fmt == o.TERNARY_1_58 else 2          # d (and bias / dmin)
+        hdr = blocks[:, :2 * nfields].copy().view(np.float16).astype(np.float32) * SHRINK[fmt]
+        blocks[:, :2 * nfields] = hdr.astype(np.float16).view(np.uint8)
+        out[n] = blocks.reshape(-1)
+    return out, g
+
+
+def run_layer(pkg, cfg_kwargs, X, w, norms=None, host_io=False):
+    from m4_prefill_engine_b200.layer import TransformerLayerConfig, TransformerLayerCoordinator
+    cfg = TransformerLayerConfig(**cfg_kwargs)
+    layer = TransformerLayerCoordinator(cfg)
+    assert layer.initialize_pipelines()
+    wd = {k: dev(v) for k, v in w.items()}
+    keep = []
+    if norms is not None:
+        keep = [dev(norms[0]), dev(norms[1])]
+        layer.set_norm_weights(*keep)
+    Xd = torch.from_numpy(X) if host_io else dev(X)
+    Yd = torch.zeros(X.shape, dtype=torch.float16, device="cpu" if host_io else "cuda")
+    layer.forward(Xd, wd["q"], wd["k"], wd["v"], wd["o"], wd["gate"], wd["up"], wd["down"], Yd)
+    layer.bridge.synchronize()
+    assert layer.bridge.device_error() == 0
+    n = layer.kernels_per_forward()
+    layer.close()
+    return Yd.cpu().numpy(), n
+
+
+def test_layer_reference_fixture(bridge, pkg):
+    z = np.load(GOLD / "layer_q4_0.npz")
+    X = z["X"].view(np.float16)
+    w = dict(zip(("q", "k", "v", "o", "gate", "up", "down"), (z[f"W{i}"] for i in range(7))))
+    Y, n = run_layer(pkg, dict(M=24, K=256, H=4, D=64, N_mlp=512, attn_scale=0.125), X, w)
+    # the reference's pipeline bench passes at 0.05 against this gold (bench_8b_engine.mm:694)
+    assert np.abs(Y.astype(np.float32) - z["Y"].view(np.float16).astype(np.float32)).max() <= TOL
+    assert n == 7      # q, k, v, attention, o(+residual), swiglu, down(+residual): residual adds and transposes are fused away
+
+
+@pytest.mark.parametrize("fmt", [o.Q4_0, o.MLX_4BIT, o.Q4_K, o.TERNARY_1_58])
+@pytest.mark.parametrize("M", [33, 129])
+def test_layer_reference_semantics(bridge, pkg, fmt, M):
+    K, H, D, F = 512, 8, 64, 768
+    w, g = layer_weights(fmt, K, H, H, D, F)
+    X = g.activations(M, K)
+    Y, _ = run_layer(pkg, dict(M=M, K=K, H=H, D=D, N_mlp=F, attn_scale=D ** -0.5, weight_format=fmt), X, w)
+    gold = o.layer(fmt, X, w["q"], w["k"], w["v"], w["o"], w["gate"], w["up"], w["down"], H, H, D, F, D ** -0.5)
+    diff = np.abs(Y.astype(np.float64) - gold.astype(np.float64))
+    rms = float(np.sqrt(np.mean(gold.astype(np.float64) ** 2)))
+    assert diff.max() <= max(TOL, 2.0 ** -7 * rms), f"max-abs {diff.max()} rms {rms}"
+
+
+@pytest.mark.parametrize("host_io", [False, True])
+def test_layer_llama_style(bridge, pkg, host_io):
+    """RMSNorm + grouped-query attention + rotary embedding + Q8_0 KV, the benchmark's layer (small shape)."""
+    M, K, H, Hkv, D, F = 100, 512, 4, 2, 128, 1024
+    w, g = layer_weights(o.Q4_0, K, H, Hkv, D, F)
+    X = g.activations(M, K)
+    rng = np.random.default_rng(1)
+    n1 = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    n2 = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    kw = dict(M=M, K=K, H=H, D=D, N_mlp=F, attn_scale=D ** -0.5, num_kv_heads=Hkv, rms_eps=1e-5, rope_theta=500000.0, kv_q8_0=True)
+    Y, _ = run_layer(pkg, kw, X, w, (n1, n2), host_io=host_io)
+    gold = o.layer(o.Q4_0, X, w["q"], w["k"], w["v"], w["o"], w["gate"], w["up"], w["down"], H, Hkv, D, F, D ** -0.5,
+                   rms_eps=1e-5, norm1=n1, norm2=n2, rope_theta=500000.0, kv_q8=True)
+    diff = np.abs(Y.astype(np.float64) - gold.astype(np.float64))
+    assert diff.max() <= 2 * TOL, f"max-abs {diff.max()}"
+
+
+def test_rmsnorm_and_rope_ops(bridge):
+    L = bridge.lib
+    import ctypes
+    g = o.RefLcg(12)
+    X = g.activations(37, 512)
+    wt = (1.0 + 0.2 * np.random.default_rng(2).standard_normal(512)).astype(np.float16)
+    Xd, wd = dev(X), dev(wt)
+    Yd = torch.zeros_like(Xd)
+    assert L.b200_bridge_rmsnorm(Xd.data_ptr(), wd.data_ptr(), Yd.data_ptr(), 37, 512, ctypes.c_float(1e-5)) == 0
+    bridge.synchronize()
+    gold = o.rmsnorm(X, wt, 1e-5).astype(np.float32)
+    assert np.abs(Yd.cpu().numpy().astype(np.float32) - gold).max() <= 2e-3     # two fp16 roundings, values ~3
+    Q = g.activations(3, 50, 128)
+    Qd = dev(Q)
+    assert L.b200_bridge_rope(Qd.data_ptr(), 3, 50, 128, ctypes.c_float(500000.0), 7) == 0
+    bridge.synchronize()
+    assert np.abs(Qd.cpu().numpy().astype(np.float32) - o.rope(Q, 500000.0, 7).astype(np.float32)).max() <= 2e-3
+
+
+def test_layer_tensor_parallel_emulated_on_one_gpu(bridge, pkg):
+    """Two tensor-parallel ranks emulated one after the other on a single GPU: the all-reduce hook of each
+    rank adds the other rank's partial sums, which were captured in an earlier pass.  Three passes make
+    both reductions consistent; the result must match the single-GPU layer and the oracle."""
+    from m4_prefill_engine_b200.layer import TransformerLayerConfig, TransformerLayerCoordinator, shard_layer_weights
+    M, K, H, Hkv, D, F, tp = 70, 512, 4, 2, 128, 1024, 2
+    w, g = layer_weights(o.Q4_0, K, H, Hkv, D, F)
+    X = g.activations(M, K)
+    base = dict(M=M, K=K, H=H, D=D, N_mlp=F, attn_scale=D ** -0.5, num_kv_heads=Hkv, kv_q8_0=True, rope_theta=10000.0)
+    single, _ = run_layer(pkg, base, X, w)
+    stream = torch.cuda.ExternalStream(bridge.lib.b200_bridge_stream())
+    cfg = TransformerLayerConfig(**base, tp_size=tp)
+    Xd = dev(X)
+    stash = [[None, None] for _ in range(tp)]       # stash[rank][call] = that rank's partial sums
+    outs = [None] * tp
+    for _pass in range(3):
+        new_stash = [[None, None] for _ in range(tp)]
+        for r in range(tp):
+            sw = {k: dev(v) for k, v in shard_layer_weights(o.Q4_0, w, cfg, r, tp).items()}
+            layer = TransformerLayerCoordinator(cfg)
+            calls = {"n": 0}
+
+            def hook(ptr, count, r=r, calls=calls, new_stash=new_stash):
+                class Raw:
+                    __cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 3}
+                t = torch.as_tensor(Raw(), device="cuda")
+                with torch.cuda.stream(stream):
+                    new_stash[r][calls["n"]] = t.clone()
+                    other = stash[1 - r][calls["n"]]
+                    if other is not None:
+                        t.add_(other)
+                calls["n"] += 1
+            layer.set_allreduce(hook)
+            Yd = torch.zeros_like(Xd)
+            layer.forward(Xd, sw["q"], sw["k"], sw["v"], sw["o"], sw["gate"], sw["up"], sw["down"], Yd)
+            bridge.synchronize()
+            outs[r] = Yd.cpu().numpy()
+            layer.close()
+        stash = new_stash
+    assert np.array_equal(outs[0].view(np.uint16), outs[1].view(np.uint16))       # both ranks hold the same result
+    assert np.abs(outs[0].astype(np.float32) - single.astype(np.float32)).max() <= 2e-3
+    gold = o.layer(o.Q4_0, X, w["q"], w["k"], w["v"], w["o"], w["gate"], w["up"], w["down"], H, Hkv, D, F, D ** -0.5,
+                   rope_theta=10000.0, kv_q8=True)
+    assert np.abs(outs[0].astype(np.float64) - gold.astype(np.float64)).max() <= 2 * TOL
+
+
+def test_linear_wrapper(bridge, pkg):
+    from m4_prefill_engine_b200.modules import M4QuantizedLinear
+    K, N = 512, 192
+    g = o.RefLcg(6)
+    W = g.weights(o.Q4_0, K, N)
+    lin = M4QuantizedLinear.from_quantized(W, "q4_0", K, N)
+    x = torch.from_numpy(g.activations(2, 3, 5, K)).cuda()
+    y = lin(x)
+    assert y.shape == (2, 3, 5, N) and y.dtype == torch.float16
+    gold = o.gemm_f64(o.Q4_0, x.reshape(-1, K).cpu().numpy(), W, N).reshape(2, 3, 5, N)
+    assert np.abs(y.cpu().numpy().astype(np.float64) - gold).max() <= TOL
+    assert lin(torch.zeros(0, K, device="cuda")).shape == (0, N)                     # empty input: no bridge call
+    assert lin(torch.zeros(4, 0, K)).shape == (4, 0, N)
+    y1 = lin(x[0, 0, 0].float())                                                     # 1-D, non-fp16 -> cast, GEMV
+    assert y1.shape == (N,) and np.abs(y1.cpu().numpy().astype(np.float64) - gold[0, 0, 0]).max() <= TOL
+    with pytest.raises(ValueError):
+        lin(torch.zeros(3, K + 32, device="cuda"))
+    lin.init_synthetic_weights()
+    assert torch.all(lin(torch.ones(7, K, device="cuda")) == K)
+    yc = lin(torch.ones(2, K), check_finite=True)                                    # host input, tripwire on
+    assert torch.all(yc.cpu() == K)
