@@ -45,17 +45,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` lives in shared memory: the first waiter that runs out of time
 // sets it (and the global error word) so every other waiter of the CTA leaves at once.
+// mbarrier.try_wait itself parks the thread for a hardware-defined interval, so the loop is
+// cheap; the clock and the abort flag are looked at only every 1024 failed tries so that waiting
+// warps do not take issue slots from the warps doing the unpacking.  SLEEP_NS > 0 adds a
+// nanosleep between tries for waits that are long by construction (a whole tile).
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           int* err_word, int code) {
     if (mbar_try_wait(bar, parity)) return true;
-    long long t0 = clock64();
-    while (true) {
+    long long t0 = 0;
+    for (uint32_t spin = 1;; ++spin) {
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-            *abort_flag = 1u;
-            if (err_word) atomicCAS(err_word, 0, code);
-            return false;
+        if ((spin & 1023u) == 0u) {
+            if (*abort_flag) return false;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1u;
+                if (err_word) atomicCAS(err_word, 0, code);
+                return false;
+            }
         }
     }
 }

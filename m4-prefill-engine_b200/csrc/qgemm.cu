@@ -48,8 +48,12 @@ template <int NW> struct Cfg {
     static constexpr int TOK_MAX = NW == 1 ? 256 : 128;
     static constexpr int A_STAGES = NW == 1 ? 3 : 2;
     static constexpr int B_STAGE_BYTES = TOK_MAX * 128;
-    static constexpr int DQ_THREADS = 128 * NW;
-    static constexpr int EPI_WARP0 = 4 + 4 * NW;
+    // Unpack warp groups per weight matrix: group g of G takes the 64-element sub-tiles s with s % G == g, so
+    // two warps per scheduler hide each other's latency.  SwiGLU already has two matrices' worth of warps.
+    static constexpr int DQ_GROUPS = NW == 1 ? 2 : 1;
+    static constexpr int DQ_THREADS = 128 * NW * DQ_GROUPS;   // arrivals that release a packed stage
+    static constexpr int FILL_THREADS = 128 * NW;             // arrivals that publish an unpacked stage
+    static constexpr int EPI_WARP0 = 4 + DQ_THREADS / 32;
     static constexpr int THREADS = 128 + DQ_THREADS + 128;
 };
 
@@ -123,7 +127,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < RAW_STAGES; i++) { ptx::mbar_init(&raw_full[i], 1); ptx::mbar_init(&raw_empty[i], C::DQ_THREADS); }
-        for (int i = 0; i < C::A_STAGES; i++) { ptx::mbar_init(&a_full[i], C::DQ_THREADS); ptx::mbar_init(&a_empty[i], 1); }
+        for (int i = 0; i < C::A_STAGES; i++) { ptx::mbar_init(&a_full[i], C::FILL_THREADS); ptx::mbar_init(&a_empty[i], 1); }
         for (int i = 0; i < B_STAGES; i++) { ptx::mbar_init(&b_full[i], 1); ptx::mbar_init(&b_empty[i], 1); }
         for (int i = 0; i < 2; i++) { ptx::mbar_init(&tm_full[i], 1); ptx::mbar_init(&tm_empty[i], 128); }
         *abort_flag = 0u;
@@ -149,7 +153,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
                 const Tile t = decode_tile(idx, p);
                 for (uint32_t kc = 0; kc < p.kchunks; kc++) {
-                    if (!ptx::mbar_wait(&raw_empty[rs], rph ^ 1u, abort_flag, p.err, 101)) { ok = false; break; }
+                    if (!ptx::mbar_wait<64>(&raw_empty[rs], rph ^ 1u, abort_flag, p.err, 101)) { ok = false; break; }
                     ptx::mbar_arrive_expect_tx(&raw_full[rs], NW * RAW_TILE_BYTES);
                     const int x = (int)((t.ks * p.kchunks + kc) * ROW_BYTES);
                     const int y = (int)(t.wt * W_TILE);
@@ -169,7 +173,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 const Tile t = decode_tile(idx, p);
                 const uint32_t k0 = t.ks * p.kchunks * KCHUNK;
                 for (uint32_t ks = 0; ks < ksteps; ks++) {
-                    if (!ptx::mbar_wait(&b_empty[bs], bph ^ 1u, abort_flag, p.err, 102)) { ok = false; break; }
+                    if (!ptx::mbar_wait<64>(&b_empty[bs], bph ^ 1u, abort_flag, p.err, 102)) { ok = false; break; }
                     ptx::mbar_arrive_expect_tx(&b_full[bs], p.T * 128u);
                     ptx::tma_load_2d(sB + bs * C::B_STAGE_BYTES, &tmX, &b_full[bs], (int)(k0 + ks * KSTEP), (int)(t.tt * p.T));
                     if (++bs == B_STAGES) { bs = 0; bph ^= 1u; }
@@ -209,10 +213,13 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         }
     } else if (warp >= 4 && warp < (uint32_t)C::EPI_WARP0) {
         // ---------------- unpack warps: packed bytes -> swizzled fp16 K-major tile ----------------
-        const uint32_t w = (warp - 4) >> 2;                   // which weight matrix
-        const uint32_t row = threadIdx.x - 128 - 128 * w;     // weight row inside the tile
+        constexpr int G = C::DQ_GROUPS;
+        const uint32_t dq = threadIdx.x - 128;                // 0 .. DQ_THREADS-1
+        const uint32_t grp = (dq >> 7) % G;                   // sub-tile phase this warp group unpacks
+        const uint32_t w = (dq >> 7) / G;                     // which weight matrix
+        const uint32_t row = dq & 127;                        // weight row inside the tile
         const uint32_t row_off = (row >> 3) * 1024 + (row & 7) * 128, xr = row & 7;
-        uint32_t rs = 0, rph = 0, as = 0, aph = 0;
+        uint32_t rs = 0, rph = 0, kn = 0;                     // kn: running 64-element step of this CTA
         bool ok = true;
         for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
             for (uint32_t kc = 0; ok && kc < p.kchunks; kc++) {
@@ -226,19 +233,22 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 }
 #pragma unroll
                 for (int s = 0; s < KCHUNK / KSTEP; s++) {
-                    uint32_t o[32];
-                    Cd::dequant64(r, s, o);
-                    if (ok && !ptx::mbar_wait(&a_empty[as], aph ^ 1u, abort_flag, p.err, 107)) ok = false;
-                    if (ok) {
-                        uint8_t* dst = sA + (as * NW + w) * A_TILE_BYTES + row_off;
+                    if ((uint32_t)(s % G) == grp) {
+                        uint32_t o[32];
+                        Cd::dequant64(r, s, o);
+                        const uint32_t step = kn + s, as = step % C::A_STAGES, aph = (step / C::A_STAGES) & 1u;
+                        if (ok && !ptx::mbar_wait(&a_empty[as], aph ^ 1u, abort_flag, p.err, 107)) ok = false;
+                        if (ok) {
+                            uint8_t* dst = sA + (as * NW + w) * A_TILE_BYTES + row_off;
 #pragma unroll
-                        for (int c = 0; c < 8; c++)
-                            *reinterpret_cast<uint4*>(dst + ((c ^ xr) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
-                        ptx::fence_proxy_async_smem();
-                        ptx::mbar_arrive(&a_full[as]);
-                        if (++as == (uint32_t)C::A_STAGES) { as = 0; aph ^= 1u; }
+                            for (int c = 0; c < 8; c++)
+                                *reinterpret_cast<uint4*>(dst + ((c ^ xr) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                            ptx::fence_proxy_async_smem();
+                            ptx::mbar_arrive(&a_full[as]);
+                        }
                     }
                 }
+                kn += KCHUNK / KSTEP;
                 // Release the packed stage only now: the stores above consumed every register loaded
                 // from it, so the loads have certainly returned.  (An arrive issued right after the
                 // loads let the next TMA write overtake reads that were still in flight.)
@@ -254,7 +264,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         for (uint32_t idx = blockIdx.x; idx < total_tiles; idx += gridDim.x, it++) {
             const Tile t = decode_tile(idx, p);
             const uint32_t buf = it & 1u;
-            if (!ptx::mbar_wait(&tm_full[buf], (it >> 1) & 1u, abort_flag, p.err, 108)) break;
+            if (!ptx::mbar_wait<256>(&tm_full[buf], (it >> 1) & 1u, abort_flag, p.err, 108)) break;
             ptx::tc_fence_after_sync();
             const uint32_t n = t.wt * W_TILE + q * 32 + lane;
             const bool n_ok = n < p.N;
