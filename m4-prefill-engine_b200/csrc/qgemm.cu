@@ -35,18 +35,29 @@
 
 namespace qg {
 
+// Development aid: with -DQG_TRACE one CTA records clock64() stamps at its synchronisation points
+// (role, step, tag) into a device array that a host harness reads back.  Compiled out otherwise.
+#ifdef QG_TRACE
+#ifndef QG_TRACE_CTA
+#define QG_TRACE_CTA 0
+#endif
+__device__ unsigned long long g_trace[8][256][4];
+#define QTR(role, step, tag) do { if (blockIdx.x == QG_TRACE_CTA && (step) < 256u) g_trace[role][step][tag] = clock64(); } while (0)
+#else
+#define QTR(role, step, tag) do { } while (0)
+#endif
+
 constexpr int W_TILE = 128;     // weight rows per tile = UMMA M
 constexpr int KSTEP = 64;       // fp16 elements per 128-byte swizzled row
 constexpr int KCHUNK = 256;     // K elements per packed-weight stage
 constexpr int RAW_STAGES = 2;
-constexpr int B_STAGES = 4;
+constexpr int STAGES = 3;       // operand ring: one stage = unpacked weight tile(s) + activation tile
 constexpr int A_TILE_BYTES = W_TILE * 128;
 constexpr int TMEM_COLS = 512;
 constexpr int ACC_STRIDE = 256; // tensor-memory columns per accumulator buffer
 
 template <int NW> struct Cfg {
     static constexpr int TOK_MAX = NW == 1 ? 256 : 128;
-    static constexpr int A_STAGES = NW == 1 ? 3 : 2;
     static constexpr int B_STAGE_BYTES = TOK_MAX * 128;
     // Unpack warp groups per weight matrix: group g of G takes the 64-element sub-tiles s with s % G == g, so
     // two warps per scheduler hide each other's latency.  SwiGLU already has two matrices' worth of warps.
@@ -72,7 +83,7 @@ struct Params {
 
 template <int FMT, int NW> constexpr size_t smem_bytes() {
     using C = Cfg<NW>;
-    return 1024 /*alignment slack*/ + (size_t)B_STAGES * C::B_STAGE_BYTES + (size_t)C::A_STAGES * NW * A_TILE_BYTES +
+    return 1024 /*alignment slack*/ + (size_t)STAGES * C::B_STAGE_BYTES + (size_t)STAGES * NW * A_TILE_BYTES +
            (size_t)RAW_STAGES * NW * cdc::Codec<FMT>::ROW_BYTES * W_TILE + 512 /*barriers*/;
 }
 
@@ -106,16 +117,17 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t pad = (1024u - (ptx::smem_u32(smem_dyn) & 1023u)) & 1023u;
     uint8_t* sB = smem_dyn + pad;
-    uint8_t* sA = sB + B_STAGES * C::B_STAGE_BYTES;
-    uint8_t* sRaw = sA + C::A_STAGES * NW * A_TILE_BYTES;
+    uint8_t* sA = sB + STAGES * C::B_STAGE_BYTES;
+    uint8_t* sRaw = sA + STAGES * NW * A_TILE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + RAW_STAGES * NW * RAW_TILE_BYTES);
     uint64_t* raw_full = bars;
     uint64_t* raw_empty = raw_full + RAW_STAGES;
-    uint64_t* a_full = raw_empty + RAW_STAGES;
-    uint64_t* a_empty = a_full + C::A_STAGES;
-    uint64_t* b_full = a_empty + C::A_STAGES;
-    uint64_t* b_empty = b_full + B_STAGES;
-    uint64_t* tm_full = b_empty + B_STAGES;
+    // One full/empty pair per operand stage: "full" collects the unpack threads' arrivals plus the
+    // activation TMA's byte count, "empty" is one tcgen05.commit -- so the MMA thread does one wait
+    // and one commit per 64-element step.
+    uint64_t* op_full = raw_empty + RAW_STAGES;
+    uint64_t* op_empty = op_full + STAGES;
+    uint64_t* tm_full = op_empty + STAGES;
     uint64_t* tm_empty = tm_full + 2;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tm_empty + 2);
     volatile uint32_t* abort_flag = tmem_holder + 1;
@@ -126,10 +138,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     const uint32_t ksteps = p.kchunks * (KCHUNK / KSTEP);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < RAW_STAGES; i++) { ptx::mbar_init(&raw_full[i], 1); ptx::mbar_init(&raw_empty[i], C::DQ_THREADS); }
-        for (int i = 0; i < C::A_STAGES; i++) { ptx::mbar_init(&a_full[i], C::FILL_THREADS); ptx::mbar_init(&a_empty[i], 1); }
-        for (int i = 0; i < B_STAGES; i++) { ptx::mbar_init(&b_full[i], 1); ptx::mbar_init(&b_empty[i], 1); }
-        for (int i = 0; i < 2; i++) { ptx::mbar_init(&tm_full[i], 1); ptx::mbar_init(&tm_empty[i], 128); }
+        for (int i = 0; i < RAW_STAGES; i++) { ptx::mbar_init(&raw_full[i], 1); ptx::mbar_init(&raw_empty[i], C::DQ_THREADS / 32); }
+        for (int i = 0; i < STAGES; i++) { ptx::mbar_init(&op_full[i], C::FILL_THREADS / 32 + 1); ptx::mbar_init(&op_empty[i], 1); }
+        for (int i = 0; i < 2; i++) { ptx::mbar_init(&tm_full[i], 1); ptx::mbar_init(&tm_empty[i], 4); }
         *abort_flag = 0u;
         *last_flag = 0u;
         ptx::fence_barrier_init();
@@ -142,74 +153,91 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    if (threadIdx.x == 0) QTR(7, 0u, 0);
 
     if (warp == 0) {
         // ---------------- packed-weight producer ----------------
-        if (lane == 0) {
-            ptx::prefetch_tensormap(&tmW0);
-            if (NW == 2) ptx::prefetch_tensormap(&tmW1);
-            uint32_t rs = 0, rph = 0;
-            bool ok = true;
-            for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
-                const Tile t = decode_tile(idx, p);
-                for (uint32_t kc = 0; kc < p.kchunks; kc++) {
-                    if (!ptx::mbar_wait<64>(&raw_empty[rs], rph ^ 1u, abort_flag, p.err, 101)) { ok = false; break; }
+        // The whole warp walks the loop (only lane 0 issues): a lone lane looping while its 31 siblings
+        // already sit at the final barrier gets scheduled far less often than a converged warp.
+        if (lane == 0) { ptx::prefetch_tensormap(&tmW0); if (NW == 2) ptx::prefetch_tensormap(&tmW1); }
+        uint32_t rs = 0, rph = 0, wtr = 0;
+        (void)wtr;
+        bool ok = true;
+        for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
+            const Tile t = decode_tile(idx, p);
+            for (uint32_t kc = 0; kc < p.kchunks; kc++) {
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait<64>(&raw_empty[rs], rph ^ 1u, abort_flag, p.err, 101));
+                if (!ok) break;
+                if (lane == 0) {
+                    QTR(0, wtr, 0);
                     ptx::mbar_arrive_expect_tx(&raw_full[rs], NW * RAW_TILE_BYTES);
                     const int x = (int)((t.ks * p.kchunks + kc) * ROW_BYTES);
                     const int y = (int)(t.wt * W_TILE);
                     ptx::tma_load_2d(sRaw + (rs * NW + 0) * RAW_TILE_BYTES, &tmW0, &raw_full[rs], x, y);
                     if (NW == 2) ptx::tma_load_2d(sRaw + (rs * NW + 1) * RAW_TILE_BYTES, &tmW1, &raw_full[rs], x, y);
-                    if (++rs == RAW_STAGES) { rs = 0; rph ^= 1u; }
+                    QTR(0, wtr, 1); wtr++;
                 }
+                __syncwarp();
+                if (++rs == RAW_STAGES) { rs = 0; rph ^= 1u; }
             }
         }
     } else if (warp == 1) {
         // ---------------- activation producer ----------------
-        if (lane == 0) {
-            ptx::prefetch_tensormap(&tmX);
-            uint32_t bs = 0, bph = 0;
-            bool ok = true;
-            for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
-                const Tile t = decode_tile(idx, p);
-                const uint32_t k0 = t.ks * p.kchunks * KCHUNK;
-                for (uint32_t ks = 0; ks < ksteps; ks++) {
-                    if (!ptx::mbar_wait<64>(&b_empty[bs], bph ^ 1u, abort_flag, p.err, 102)) { ok = false; break; }
-                    ptx::mbar_arrive_expect_tx(&b_full[bs], p.T * 128u);
-                    ptx::tma_load_2d(sB + bs * C::B_STAGE_BYTES, &tmX, &b_full[bs], (int)(k0 + ks * KSTEP), (int)(t.tt * p.T));
-                    if (++bs == B_STAGES) { bs = 0; bph ^= 1u; }
+        if (lane == 0) ptx::prefetch_tensormap(&tmX);
+        uint32_t bs = 0, bph = 0, xtr = 0;
+        (void)xtr;
+        bool ok = true;
+        for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
+            const Tile t = decode_tile(idx, p);
+            const uint32_t k0 = t.ks * p.kchunks * KCHUNK;
+            for (uint32_t ks = 0; ks < ksteps; ks++) {
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&op_empty[bs], bph ^ 1u, abort_flag, p.err, 102));
+                if (!ok) break;
+                if (lane == 0) {
+                    QTR(1, xtr, 0);
+                    ptx::mbar_arrive_expect_tx(&op_full[bs], p.T * 128u);
+                    ptx::tma_load_2d(sB + bs * C::B_STAGE_BYTES, &tmX, &op_full[bs], (int)(k0 + ks * KSTEP), (int)(t.tt * p.T));
+                    QTR(1, xtr, 1); xtr++;
                 }
+                __syncwarp();
+                if (++bs == STAGES) { bs = 0; bph ^= 1u; }
             }
         }
     } else if (warp == 2) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            const uint32_t idesc = ptx::umma_idesc_f16(W_TILE, p.T);
-            uint32_t as = 0, aph = 0, bs = 0, bph = 0, it = 0;
-            bool ok = true;
-            for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x, it++) {
-                const uint32_t buf = it & 1u;
-                if (!ptx::mbar_wait(&tm_empty[buf], ((it >> 1) & 1u) ^ 1u, abort_flag, p.err, 103)) { ok = false; break; }
+        const uint32_t idesc = ptx::umma_idesc_f16(W_TILE, p.T);
+        uint32_t st = 0, sph = 0, it = 0, mtr = 0;
+        (void)mtr;
+        bool ok = true;
+        for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x, it++) {
+            const uint32_t buf = it & 1u;
+            ok = __all_sync(0xffffffffu, ptx::mbar_wait(&tm_empty[buf], ((it >> 1) & 1u) ^ 1u, abort_flag, p.err, 103));
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            for (uint32_t ks = 0; ks < ksteps; ks++) {
+                if (lane == 0) QTR(2, mtr, 0);
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait(&op_full[st], sph, abort_flag, p.err, 104));
+                if (!ok) break;
                 ptx::tc_fence_after_sync();
-                for (uint32_t ks = 0; ks < ksteps; ks++) {
-                    if (!ptx::mbar_wait(&a_full[as], aph, abort_flag, p.err, 104)) { ok = false; break; }
-                    if (!ptx::mbar_wait(&b_full[bs], bph, abort_flag, p.err, 105)) { ok = false; break; }
-                    ptx::tc_fence_after_sync();
-                    const uint64_t bdesc = ptx::umma_desc_k_sw128(ptx::smem_u32(sB + bs * C::B_STAGE_BYTES));
+                if (lane == 0) {
+                    QTR(2, mtr, 2);
+                    const uint64_t bdesc = ptx::umma_desc_k_sw128(ptx::smem_u32(sB + st * C::B_STAGE_BYTES));
 #pragma unroll
                     for (int w = 0; w < NW; w++) {
-                        const uint64_t adesc = ptx::umma_desc_k_sw128(ptx::smem_u32(sA + (as * NW + w) * A_TILE_BYTES));
+                        const uint64_t adesc = ptx::umma_desc_k_sw128(ptx::smem_u32(sA + (st * NW + w) * A_TILE_BYTES));
                         const uint32_t dcol = tmem_base + buf * ACC_STRIDE + w * 128;
 #pragma unroll
                         for (int kk = 0; kk < KSTEP / 16; kk++)
                             ptx::umma_f16_ss(dcol, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | (uint32_t)kk) != 0u);
                     }
-                    ptx::umma_commit(&a_empty[as]);
-                    ptx::umma_commit(&b_empty[bs]);
-                    if (++as == (uint32_t)C::A_STAGES) { as = 0; aph ^= 1u; }
-                    if (++bs == B_STAGES) { bs = 0; bph ^= 1u; }
+                    ptx::umma_commit(&op_empty[st]);
+                    QTR(2, mtr, 3); mtr++;
                 }
-                if (ok) ptx::umma_commit(&tm_full[buf]);
+                __syncwarp();
+                if (++st == STAGES) { st = 0; sph ^= 1u; }
             }
+            if (ok && lane == 0) ptx::umma_commit(&tm_full[buf]);
+            __syncwarp();
         }
     } else if (warp >= 4 && warp < (uint32_t)C::EPI_WARP0) {
         // ---------------- unpack warps: packed bytes -> swizzled fp16 K-major tile ----------------
@@ -223,7 +251,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         bool ok = true;
         for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
             for (uint32_t kc = 0; ok && kc < p.kchunks; kc++) {
-                if (!ptx::mbar_wait(&raw_full[rs], rph, abort_flag, p.err, 106)) { ok = false; break; }
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&raw_full[rs], rph, abort_flag, p.err, 106));
+                if (!ok) break;
+                if (row == 0 && w == 0) QTR(3, (kn >> 2) * 2 + grp, 0);
                 uint32_t r[ROW_BYTES / 4];
                 const uint4* src = reinterpret_cast<const uint4*>(sRaw + (rs * NW + w) * RAW_TILE_BYTES + row * ROW_BYTES);
 #pragma unroll
@@ -235,16 +265,25 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 for (int s = 0; s < KCHUNK / KSTEP; s++) {
                     if ((uint32_t)(s % G) == grp) {
                         uint32_t o[32];
+#if defined(QG_EXP) && QG_EXP == 5
+#pragma unroll
+                        for (int z = 0; z < 32; z++) o[z] = r[z % (ROW_BYTES / 4)];     // experiment: no unpack arithmetic
+#else
                         Cd::dequant64(r, s, o);
-                        const uint32_t step = kn + s, as = step % C::A_STAGES, aph = (step / C::A_STAGES) & 1u;
-                        if (ok && !ptx::mbar_wait(&a_empty[as], aph ^ 1u, abort_flag, p.err, 107)) ok = false;
+#endif
+                        if (row == 0 && w == 0) QTR(4 + grp, kn + s, 0);
+                        const uint32_t step = kn + s, as = step % STAGES, aph = (step / STAGES) & 1u;
+                        ok = __all_sync(0xffffffffu, ok && ptx::mbar_wait<32>(&op_empty[as], aph ^ 1u, abort_flag, p.err, 107));
+                        if (row == 0 && w == 0) QTR(4 + grp, kn + s, 1);
                         if (ok) {
                             uint8_t* dst = sA + (as * NW + w) * A_TILE_BYTES + row_off;
 #pragma unroll
                             for (int c = 0; c < 8; c++)
                                 *reinterpret_cast<uint4*>(dst + ((c ^ xr) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
                             ptx::fence_proxy_async_smem();
-                            ptx::mbar_arrive(&a_full[as]);
+                            __syncwarp();                      // every lane's stores are fenced; one arrival per warp
+                            if (lane == 0) ptx::mbar_arrive(&op_full[as]);
+                            if (row == 0 && w == 0) QTR(4 + grp, kn + s, 2);
                         }
                     }
                 }
@@ -252,7 +291,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 // Release the packed stage only now: the stores above consumed every register loaded
                 // from it, so the loads have certainly returned.  (An arrive issued right after the
                 // loads let the next TMA write overtake reads that were still in flight.)
-                ptx::mbar_arrive(&raw_empty[rs]);
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&raw_empty[rs]);
+                if (row == 0 && w == 0) QTR(3, ((kn >> 2) - 1) * 2 + grp, 3);
                 if (++rs == RAW_STAGES) { rs = 0; rph ^= 1u; }
             }
         }
@@ -265,37 +306,60 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             const Tile t = decode_tile(idx, p);
             const uint32_t buf = it & 1u;
             if (!ptx::mbar_wait<256>(&tm_full[buf], (it >> 1) & 1u, abort_flag, p.err, 108)) break;
+            if (et == 0) QTR(6, it, 0);
             ptx::tc_fence_after_sync();
             const uint32_t n = t.wt * W_TILE + q * 32 + lane;
             const bool n_ok = n < p.N;
+            // output element (tok, n) lives at out_base + tok * out_stride in either layout; the head split
+            // (a division by a run-time D) is done once per tile here, never per element
+            const size_t out_stride = (p.layout == 1) ? (size_t)p.D : (size_t)p.N;
+            const size_t out_base = (p.layout == 1) ? ((size_t)(n / p.D) * p.M * p.D + (n % p.D)) : (size_t)n;
             const uint32_t taddr = tmem_base + ((q * 32u) << 16) + buf * ACC_STRIDE;
             const uint32_t tok0 = t.tt * p.T;
             float* ws = p.ws_partial + ((size_t)t.ks * (p.n_w_tiles * p.n_tok_tiles) + t.id) * p.T * W_TILE;
+            // The destination kind is fixed per launch; branching on it once per tile (not per element) keeps
+            // the inner loops to a convert, an address add and a store.
+            const uint32_t valid = tok0 < p.M ? min(p.T, p.M - tok0) : 0u;     // token columns of this tile that exist
+            const int mode = p.k_splits > 1 ? 0 : (p.partial_out ? 1 : (p.residual ? 2 : 3));
             for (uint32_t c0 = 0; c0 < p.T; c0 += 16) {
                 uint32_t v[16], u[16];
+                if (et == 0 && it == 0) QTR(7, 1 + c0 / 16, 0);
                 ptx::tmem_ld_x16(taddr + c0, v);
                 if (NW == 2) ptx::tmem_ld_x16(taddr + 128 + c0, u);
                 ptx::tmem_ld_wait();
+                if (et == 0 && it == 0) QTR(7, 1 + c0 / 16, 1);
+                float f[16];
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
-                    const uint32_t tok = tok0 + c0 + j;
-                    float acc = __uint_as_float(v[j]);
-                    if (NW == 2) acc = silu_mul(acc, __uint_as_float(u[j]));
-                    if (p.k_splits > 1) {
-                        ws[(size_t)(c0 + j) * W_TILE + q * 32 + lane] = acc;
-                    } else if (n_ok && tok < p.M) {
-                        if (p.partial_out) {
-                            p.partial_out[(size_t)tok * p.N + n] = acc;
-                        } else {
-                            const size_t o = out_index(p, tok, n);
-                            if (p.residual) acc += __half2float(p.residual[o]);
-                            p.Y[o] = __float2half_rn(acc);
-                        }
+                    f[j] = __uint_as_float(v[j]);
+                    if (NW == 2) f[j] = silu_mul(f[j], __uint_as_float(u[j]));
+                }
+                if (mode == 0) {
+                    float* dst = ws + (size_t)c0 * W_TILE + q * 32 + lane;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) dst[(size_t)j * W_TILE] = f[j];
+                } else if (n_ok && c0 < valid) {
+                    const uint32_t lim = valid - c0;                            // >= 1 columns of this batch exist
+                    if (mode == 1) {
+                        float* dst = p.partial_out + (size_t)(tok0 + c0) * p.N + n;
+#pragma unroll
+                        for (int j = 0; j < 16; j++) if ((uint32_t)j < lim) dst[(size_t)j * p.N] = f[j];
+                    } else if (mode == 2) {
+                        const size_t o = out_base + (size_t)(tok0 + c0) * out_stride;
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if ((uint32_t)j < lim) p.Y[o + j * out_stride] = __float2half_rn(f[j] + __half2float(p.residual[o + j * out_stride]));
+                    } else {
+                        __half* dst = p.Y + out_base + (size_t)(tok0 + c0) * out_stride;
+#pragma unroll
+                        for (int j = 0; j < 16; j++) if ((uint32_t)j < lim) dst[j * out_stride] = __float2half_rn(f[j]);
                     }
                 }
             }
             ptx::tc_fence_before_sync();
-            ptx::mbar_arrive(&tm_empty[buf]);
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tm_empty[buf]);
+            if (et == 0) QTR(6, it, 1);
             if (p.k_splits > 1) {
                 // the last CTA to finish a tile adds the partial tiles in split order
                 __threadfence();
@@ -326,7 +390,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                                 if (p.partial_out) {
                                     p.partial_out[(size_t)tok * p.N + n] = v;
                                 } else {
-                                    const size_t o = out_index(p, tok, n);
+                                    const size_t o = out_base + (size_t)tok * out_stride;
                                     if (p.residual) v += __half2float(p.residual[o]);
                                     p.Y[o] = __float2half_rn(v);
                                 }
@@ -343,6 +407,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     // ---------------- teardown ----------------
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if (threadIdx.x == 0) QTR(7, 0u, 1);
     if (*abort_flag) {
         // let copies that are still in flight land before the CTA gives its shared memory back
         const long long t0 = clock64();
