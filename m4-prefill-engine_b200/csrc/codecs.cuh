@@ -126,6 +126,7 @@ template <int FMT> struct Codec;
 // ---- Q4_0: 18 B / 32 (quant_router_kernels.metal:111-146) ---------------------------------
 template <> struct Codec<QUANT_Q4_0> {
     static constexpr int ROW_BYTES = 144;   // 8 blocks per 256 elements
+    static constexpr int GROUPS = 3;      // unpack warp groups per matrix in the projection kernel
     CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
 #pragma unroll
         for (int bi = 0; bi < 2; bi++) {
@@ -145,6 +146,7 @@ template <> struct Codec<QUANT_Q4_0> {
 // ---- MLX 4-bit affine, 20 B / 32 (quant_router_kernels.metal:149-185) -----------------------
 template <> struct Codec<QUANT_MLX_4BIT> {
     static constexpr int ROW_BYTES = 160;
+    static constexpr int GROUPS = 3;      // unpack warp groups per matrix in the projection kernel
     CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
 #pragma unroll
         for (int bi = 0; bi < 2; bi++) {
@@ -164,6 +166,7 @@ template <> struct Codec<QUANT_MLX_4BIT> {
 // ---- Q4_K, 144 B / 256 (quant_router_kernels.metal:188-238; gold cpu_gold_reference.h:116-146) --
 template <> struct Codec<QUANT_Q4_K> {
     static constexpr int ROW_BYTES = 144;
+    static constexpr int GROUPS = 3;      // unpack warp groups per matrix in the projection kernel
     CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
         const uint32_t d_dmin = r[0];   // (d, dmin) as an fp16 pair
 #pragma unroll
@@ -194,6 +197,7 @@ template <> struct Codec<QUANT_Q4_K> {
 // ---- ternary, 12 B / 32 (gold cpu_gold_reference.h:176-189: value = (code-1)*d, code 3 -> +2d) --
 template <> struct Codec<QUANT_TERNARY_1_58> {
     static constexpr int ROW_BYTES = 96;
+    static constexpr int GROUPS = 3;      // unpack warp groups per matrix in the projection kernel
     CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
 #pragma unroll
         for (int bi = 0; bi < 2; bi++) {
@@ -216,6 +220,7 @@ template <> struct Codec<QUANT_TERNARY_1_58> {
 // ---- EXL3-style codebook, 144 B / 256 (quant_router_kernels.metal:368-411; gold :342-389) ---------
 template <> struct Codec<QUANT_EXL3> {
     static constexpr int ROW_BYTES = 144;
+    static constexpr int GROUPS = 2;      // unpack warp groups per matrix in the projection kernel
     CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
         const float d = h_lo_to_float(r[0]), bias = h_hi_to_float(r[0]);
 #pragma unroll
@@ -249,6 +254,7 @@ template <> struct Codec<QUANT_EXL3> {
 // ---- variable-rate affine, 160 B / 256 (quant_router_kernels.metal:265-365; gold :214-311) ---------
 template <> struct Codec<QUANT_VAR_RATE_AFFINE> {
     static constexpr int ROW_BYTES = 160;
+    static constexpr int GROUPS = 2;      // unpack warp groups per matrix in the projection kernel
     CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
         const float d = h_lo_to_float(r[0]), bias = h_hi_to_float(r[0]);
 #pragma unroll

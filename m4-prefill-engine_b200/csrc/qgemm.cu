@@ -10,10 +10,12 @@
 //   * operands are swapped: the 128 weight rows of a tile are the UMMA "M" side, up to 256
 //     tokens are the "N" side, so one unpacked weight tile feeds a 128 x T x 16 MMA;
 //   * warp 0 streams packed weight bytes with TMA (2-D map over the raw byte matrix, one box =
-//     128 rows x the bytes of 256 K-elements, no swizzle); warp 1 streams fp16 activations with
-//     TMA into 128-byte-swizzled K-major tiles; warp 2 issues tcgen05.mma (fp16 x fp16 -> fp32 in
-//     tensor memory); 4 (8 for SwiGLU) unpack warps turn packed bytes into the swizzled fp16
-//     K-major layout the MMA reads; the last 4 warps drain tensor memory and write fp16;
+//     128 rows x the bytes of 256 K-elements, no swizzle, 2-stage ring); warp 1 streams fp16
+//     activations with TMA into 128-byte-swizzled K-major tiles; warp 2 issues tcgen05.mma (fp16 x
+//     fp16 -> fp32 in tensor memory); 8-16 unpack warps turn packed bytes into the swizzled fp16
+//     K-major layout the MMA reads; the last 4 warps drain tensor memory and write fp16.  Weight
+//     and activation tiles of one 64-element K step share a 3-deep operand ring with one
+//     full/empty mbarrier pair per stage;
 //   * two accumulator buffers in tensor memory overlap a tile's epilogue with the next tile;
 //   * for few tokens the K range is split across CTAs; partial tiles meet in a scratch buffer
 //     and the last CTA of a tile adds them in split order (deterministic) and writes Y.
@@ -42,9 +44,20 @@ namespace qg {
 #define QG_TRACE_CTA 0
 #endif
 __device__ unsigned long long g_trace[8][256][4];
-#define QTR(role, step, tag) do { if (blockIdx.x == QG_TRACE_CTA && (step) < 256u) g_trace[role][step][tag] = clock64(); } while (0)
+__device__ unsigned long long g_cta_ns[256][4];     // per CTA: entry, after set-up, before teardown, exit (globaltimer ns)
+__device__ __forceinline__ unsigned long long gtimer() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define QCTA(tag) do { if (threadIdx.x == 0 && blockIdx.x < 256u) g_cta_ns[blockIdx.x][tag] = gtimer(); } while (0)
+#define QTR_(role, step, tag) do { if (blockIdx.x == QG_TRACE_CTA && (step) < 256u) g_trace[role][step][tag] = clock64(); } while (0)
+#define QTRC(role, step, tag) QTR_(role, step, tag)            /* coarse: once per tile */
+#if QG_TRACE >= 2
+#define QTR(role, step, tag) QTR_(role, step, tag)             /* fine: once per 64-element step */
 #else
 #define QTR(role, step, tag) do { } while (0)
+#endif
+#else
+#define QTR(role, step, tag) do { } while (0)
+#define QTRC(role, step, tag) do { } while (0)
+#define QCTA(tag) do { } while (0)
 #endif
 
 constexpr int W_TILE = 128;     // weight rows per tile = UMMA M
@@ -56,12 +69,15 @@ constexpr int A_TILE_BYTES = W_TILE * 128;
 constexpr int TMEM_COLS = 512;
 constexpr int ACC_STRIDE = 256; // tensor-memory columns per accumulator buffer
 
-template <int NW> struct Cfg {
+template <int NW, int FMT = 0> struct Cfg {
     static constexpr int TOK_MAX = NW == 1 ? 256 : 128;
     static constexpr int B_STAGE_BYTES = TOK_MAX * 128;
-    // Unpack warp groups per weight matrix: group g of G takes the 64-element sub-tiles s with s % G == g, so
-    // two warps per scheduler hide each other's latency.  SwiGLU already has two matrices' worth of warps.
-    static constexpr int DQ_GROUPS = NW == 1 ? 2 : 1;
+    // Unpack warp groups per weight matrix.  With G == STAGES group g owns operand stage g (it unpacks every
+    // step with step % STAGES == g); with G < STAGES group g takes the sub-tiles s with s % G == g.  G must not
+    // exceed STAGES: the parity wait on a stage's "empty" barrier is only unambiguous if the waiting group is
+    // never two phases ahead, which holds when its own previous wait already implied the phase before.
+    static constexpr int DQ_GROUPS = NW == 1 ? cdc::Codec<FMT>::GROUPS : (cdc::Codec<FMT>::GROUPS + 1) / 2;
+    static_assert(DQ_GROUPS >= 1 && DQ_GROUPS <= STAGES, "unpack groups are bounded by the operand ring depth");
     static constexpr int DQ_THREADS = 128 * NW * DQ_GROUPS;   // arrivals that release a packed stage
     static constexpr int FILL_THREADS = 128 * NW;             // arrivals that publish an unpacked stage
     static constexpr int EPI_WARP0 = 4 + DQ_THREADS / 32;
@@ -82,7 +98,7 @@ struct Params {
 };
 
 template <int FMT, int NW> constexpr size_t smem_bytes() {
-    using C = Cfg<NW>;
+    using C = Cfg<NW, FMT>;
     return 1024 /*alignment slack*/ + (size_t)STAGES * C::B_STAGE_BYTES + (size_t)STAGES * NW * A_TILE_BYTES +
            (size_t)RAW_STAGES * NW * cdc::Codec<FMT>::ROW_BYTES * W_TILE + 512 /*barriers*/;
 }
@@ -106,15 +122,16 @@ __device__ __forceinline__ size_t out_index(const Params& p, uint32_t tok, uint3
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 template <int FMT, int NW>
-__global__ void __launch_bounds__(Cfg<NW>::THREADS, 1)
+__global__ void __launch_bounds__(Cfg<NW, FMT>::THREADS, 1)
 qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW0,
              const __grid_constant__ CUtensorMap tmW1, const Params p) {
-    using C = Cfg<NW>;
+    using C = Cfg<NW, FMT>;
     using Cd = cdc::Codec<FMT>;
     constexpr int ROW_BYTES = Cd::ROW_BYTES;
     constexpr int RAW_TILE_BYTES = ROW_BYTES * W_TILE;
 
     extern __shared__ uint8_t smem_dyn[];
+    QCTA(0);
     const uint32_t pad = (1024u - (ptx::smem_u32(smem_dyn) & 1023u)) & 1023u;
     uint8_t* sB = smem_dyn + pad;
     uint8_t* sA = sB + STAGES * C::B_STAGE_BYTES;
@@ -153,7 +170,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
-    if (threadIdx.x == 0) QTR(7, 0u, 0);
+    if (threadIdx.x == 0) QTRC(7, 0u, 0);
+    QCTA(1);
 
     if (warp == 0) {
         // ---------------- packed-weight producer ----------------
@@ -206,6 +224,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     } else if (warp == 2) {
         // ---------------- MMA issuer ----------------
         const uint32_t idesc = ptx::umma_idesc_f16(W_TILE, p.T);
+        // operand descriptors differ between stages only in the 14-bit start-address field
+        const uint64_t desc_hi = ptx::umma_desc_k_sw128(0u);
+        const uint32_t a_lo0 = (ptx::smem_u32(sA) & 0x3FFFFu) >> 4, b_lo0 = (ptx::smem_u32(sB) & 0x3FFFFu) >> 4;
         uint32_t st = 0, sph = 0, it = 0, mtr = 0;
         (void)mtr;
         bool ok = true;
@@ -214,17 +235,19 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             ok = __all_sync(0xffffffffu, ptx::mbar_wait(&tm_empty[buf], ((it >> 1) & 1u) ^ 1u, abort_flag, p.err, 103));
             if (!ok) break;
             ptx::tc_fence_after_sync();
+            if (lane == 0) QTRC(2, 200u + it, 0);
             for (uint32_t ks = 0; ks < ksteps; ks++) {
                 if (lane == 0) QTR(2, mtr, 0);
-                ok = __all_sync(0xffffffffu, ptx::mbar_wait(&op_full[st], sph, abort_flag, p.err, 104));
+                // (no tcgen05 fence here: the stage was written by TMA and by generic stores that were
+                // followed by fence.proxy.async; the mbarrier acquire orders them before the MMA's reads)
+                ok = ptx::mbar_wait(&op_full[st], sph, abort_flag, p.err, 104);
                 if (!ok) break;
-                ptx::tc_fence_after_sync();
                 if (lane == 0) {
                     QTR(2, mtr, 2);
-                    const uint64_t bdesc = ptx::umma_desc_k_sw128(ptx::smem_u32(sB + st * C::B_STAGE_BYTES));
+                    const uint64_t bdesc = desc_hi | (uint64_t)(b_lo0 + st * (C::B_STAGE_BYTES >> 4));
 #pragma unroll
                     for (int w = 0; w < NW; w++) {
-                        const uint64_t adesc = ptx::umma_desc_k_sw128(ptx::smem_u32(sA + (st * NW + w) * A_TILE_BYTES));
+                        const uint64_t adesc = desc_hi | (uint64_t)(a_lo0 + (st * NW + w) * (A_TILE_BYTES >> 4));
                         const uint32_t dcol = tmem_base + buf * ACC_STRIDE + w * 128;
 #pragma unroll
                         for (int kk = 0; kk < KSTEP / 16; kk++)
@@ -236,7 +259,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 __syncwarp();
                 if (++st == STAGES) { st = 0; sph ^= 1u; }
             }
-            if (ok && lane == 0) ptx::umma_commit(&tm_full[buf]);
+            if (ok && lane == 0) { ptx::umma_commit(&tm_full[buf]); QTRC(2, 200u + it, 1); }
             __syncwarp();
         }
     } else if (warp >= 4 && warp < (uint32_t)C::EPI_WARP0) {
@@ -263,14 +286,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 }
 #pragma unroll
                 for (int s = 0; s < KCHUNK / KSTEP; s++) {
-                    if ((uint32_t)(s % G) == grp) {
+                    if ((G == STAGES ? (kn + s) % STAGES : (uint32_t)(s % G)) == grp) {
                         uint32_t o[32];
-#if defined(QG_EXP) && QG_EXP == 5
-#pragma unroll
-                        for (int z = 0; z < 32; z++) o[z] = r[z % (ROW_BYTES / 4)];     // experiment: no unpack arithmetic
-#else
                         Cd::dequant64(r, s, o);
-#endif
                         if (row == 0 && w == 0) QTR(4 + grp, kn + s, 0);
                         const uint32_t step = kn + s, as = step % STAGES, aph = (step / STAGES) & 1u;
                         ok = __all_sync(0xffffffffu, ok && ptx::mbar_wait<32>(&op_empty[as], aph ^ 1u, abort_flag, p.err, 107));
@@ -306,7 +324,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             const Tile t = decode_tile(idx, p);
             const uint32_t buf = it & 1u;
             if (!ptx::mbar_wait<256>(&tm_full[buf], (it >> 1) & 1u, abort_flag, p.err, 108)) break;
-            if (et == 0) QTR(6, it, 0);
+            if (et == 0) QTRC(6, it, 0);
             ptx::tc_fence_after_sync();
             const uint32_t n = t.wt * W_TILE + q * 32 + lane;
             const bool n_ok = n < p.N;
@@ -359,7 +377,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&tm_empty[buf]);
-            if (et == 0) QTR(6, it, 1);
+            if (et == 0) QTRC(6, it, 1);
             if (p.k_splits > 1) {
                 // the last CTA to finish a tile adds the partial tiles in split order
                 __threadfence();
@@ -407,7 +425,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     // ---------------- teardown ----------------
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if (threadIdx.x == 0) QTR(7, 0u, 1);
+    if (threadIdx.x == 0) QTRC(7, 0u, 1);
+    QCTA(2);
     if (*abort_flag) {
         // let copies that are still in flight land before the CTA gives its shared memory back
         const long long t0 = clock64();
@@ -418,6 +437,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, TMEM_COLS);
     }
+    QCTA(3);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -622,7 +642,7 @@ Plan make_plan(const GemmArgs& a) {
 
 template <int FMT, int NW>
 cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t stream) {
-    using C = Cfg<NW>;
+    using C = Cfg<NW, FMT>;
     const Plan pl = make_plan(a);
     const int rb = cdc::Codec<FMT>::ROW_BYTES;
     const uint64_t w_row_bytes = (uint64_t)(a.K / KCHUNK) * rb;
