@@ -105,6 +105,18 @@ int b200_bridge_rmsnorm(void* X, void* weight, void* Y, uint32_t M, uint32_t K, 
  * (pos0 + m) * theta^(-2i/D) (src/engine/model.py:112-116 with traditional = False). */
 int b200_bridge_rope(void* X, uint32_t H, uint32_t M, uint32_t D, float theta, uint32_t pos0);
 
+/* No counterpart in the reference.  m4_bridge_dispatch_gemm for callers that must not allocate device
+ * memory at run time (hosts whose own pool owns the rest of the GPU, latency-critical loops that cannot
+ * take the implicit synchronisation of cudaMalloc): same arguments, same result, but device pointers
+ * only, and the split-K scratch lives in a 12 MiB device array inside the library image (held by every
+ * GPU that loads the library until exit) instead of being allocated on demand.  Never calls cudaMalloc
+ * or cudaFree.  Returns -7 (message in b200_bridge_last_error_string) when the shape needs more than
+ * 3 Mi floats of scratch, -2 for host pointers.  The first call on a device looks up the array's address
+ * and sets kernel attributes: make it before any stream capture.  All calls share the one array (tile
+ * counters are cleared on the stream before each launch), so calls that overlap on the GPU would race. */
+int b200_bridge_gemm_scratch_static(void* X_ptr, size_t X_bytes, void* W_ptr, size_t W_bytes, void* Y_ptr, size_t Y_bytes,
+                                    int format, uint32_t M, uint32_t K, uint32_t N);
+
 /* Upload a host weight buffer once; later dispatches that pass the same host pointer and size
  * use the device copy instead of staging it again.  Returns 0, -2 or -5. */
 int b200_bridge_register_weights(const void* host_ptr, size_t bytes);

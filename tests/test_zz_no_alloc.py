@@ -1,0 +1,67 @@
+"""The allocation-free GEMM entry point against the regular one.
+
+Some callers of this library may not allocate device memory while they run: the application that
+hosts them has handed all remaining GPU memory to its own pool (so a cudaMalloc inside the library
+could fail, or stall the host while the driver synchronises the device), or they sit in a
+latency-critical loop where that synchronisation is not allowed.  For them
+`b200_bridge_gemm_scratch_static` runs the few-token projection with its split-K scratch in a fixed
+device array that is part of the library image.  It must give the same answer as
+`m4_bridge_dispatch_gemm`, call after call, although the array keeps the previous call's contents.
+This file is collected last so that a failure here cannot hide one elsewhere.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle as o
+from gpu_util import TOL, check, dev
+
+pytestmark = pytest.mark.gpu
+
+
+def _call(br, fn, Xd, Wd, Yd, fmt, M, K, N):
+    rc = fn(Xd.data_ptr(), Xd.numel() * 2, Wd.data_ptr(), Wd.numel(), Yd.data_ptr(), Yd.numel() * 2, fmt, M, K, N)
+    br.synchronize()
+    return rc
+
+
+def test_static_scratch_matches_regular_entry_point(bridge):
+    L = bridge.lib
+    K = N = 4096
+    first = None
+    # two calls in a row on different inputs and different split shapes: the second sees the first's leftovers
+    for M, fmt, seed in ((33, o.Q4_0, 1), (129, o.MLX_4BIT, 2), (33, o.Q4_0, 1)):
+        X, W = o.baseline_inputs(fmt, M, K, N, seed)
+        Xd, Wd = dev(X), dev(W)
+        Y_ref = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+        Y_new = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
+        assert _call(bridge, L.m4_bridge_dispatch_gemm, Xd, Wd, Y_ref, fmt, M, K, N) == 0
+        assert _call(bridge, L.b200_bridge_gemm_scratch_static, Xd, Wd, Y_new, fmt, M, K, N) == 0
+        assert bridge.device_error() == 0
+        a, b = Y_ref.cpu().numpy(), Y_new.cpu().numpy()
+        assert np.all(np.isfinite(b.astype(np.float32)))
+        assert np.abs(a.astype(np.float32) - b.astype(np.float32)).max() <= TOL
+        check(b, o.gemm_f64(fmt, X, W, N), f"static-scratch GEMM M={M} fmt={fmt}")
+        if first is None:
+            first = b.copy()
+    assert np.array_equal(first.view(np.uint16), b.view(np.uint16))      # same inputs again: same bits
+
+
+def test_static_scratch_limits(bridge):
+    L = bridge.lib
+    K = N = 4096
+    X = torch.zeros(256, K, dtype=torch.float16, device="cuda")
+    W = torch.zeros(N * (K // 32) * 18, dtype=torch.uint8, device="cuda")
+    Y = torch.zeros(256, N, dtype=torch.float16, device="cuda")
+    # 256 tokens x 4096 outputs split four ways needs 4 Mi floats of scratch: over the 3 Mi limit
+    assert _call(bridge, L.b200_bridge_gemm_scratch_static, X, W, Y, 0, 256, K, N) == -7
+    assert b"static array holds" in L.b200_bridge_last_error_string()
+    # host memory would have to be staged, which needs an allocation: refused
+    Xh = torch.zeros(33, K, dtype=torch.float16)
+    assert L.b200_bridge_gemm_scratch_static(Xh.data_ptr(), Xh.numel() * 2, W.data_ptr(), W.numel(), Y.data_ptr(), Y.numel() * 2,
+                                             0, 33, K, N) == -2
+    assert _call(bridge, L.b200_bridge_gemm_scratch_static, X, W, Y, 9, 33, K, N) == -3
+    # a launch with enough tiles to fill the GPU does not split K, needs no scratch and is accepted
+    Xb = torch.zeros(2048, K, dtype=torch.float16, device="cuda")
+    Yb = torch.zeros(2048, N, dtype=torch.float16, device="cuda")
+    assert _call(bridge, L.b200_bridge_gemm_scratch_static, Xb, W, Yb, 0, 2048, K, N) == 0
