@@ -1,0 +1,70 @@
+"""Tensor-parallel decoder layer over NCCL on two GPUs (skipped where fewer are visible): both ranks must
+hold the same output, and it must match the CPU oracle's layer.  One process per GPU, 127.0.0.1 rendezvous."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+WORKER = r'''
+import os, sys, numpy as np, torch, torch.distributed as dist
+root = sys.argv[1]; sys.path.insert(0, root); sys.path.insert(0, os.path.join(root, "tests"))
+import oracle as o
+from __graft_entry__ import load_package
+load_package()
+from m4_prefill_engine_b200.bridge import B200Bridge
+from m4_prefill_engine_b200.layer import TransformerLayerConfig, TransformerLayerCoordinator, shard_layer_weights, torch_allreduce_hook
+rank, world = int(sys.argv[3]), int(sys.argv[4])
+torch.cuda.set_device(rank)
+os.environ["NCCL_NVLS_ENABLE"] = "0"
+dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{sys.argv[2]}", rank=rank, world_size=world,
+                        device_id=torch.device("cuda", rank))
+br = B200Bridge.get_instance(); assert br.init()
+M, K, H, Hkv, D, F = 70, 512, 4, 2, 128, 1024
+g = o.RefLcg(1337)
+shapes = {"q": (H * D, K), "k": (Hkv * D, K), "v": (Hkv * D, K), "o": (K, H * D), "gate": (F, K), "up": (F, K), "down": (K, F)}
+w = {n: g.q4_0_bench(k, r, 0.003, 0.0003) for n, (r, k) in shapes.items()}
+X = g.activations(M, K)
+cfg = TransformerLayerConfig(M=M, K=K, H=H, D=D, N_mlp=F, attn_scale=D ** -0.5, num_kv_heads=Hkv, kv_q8_0=True,
+                             rope_theta=10000.0, tp_size=world)
+sw = {k: torch.from_numpy(v).cuda() for k, v in shard_layer_weights(o.Q4_0, w, cfg, rank, world).items()}
+layer = TransformerLayerCoordinator(cfg, br)
+layer.set_allreduce(torch_allreduce_hook(br))
+Xd = torch.from_numpy(X).cuda(); Yd = torch.zeros_like(Xd)
+for _ in range(2):
+    layer.forward(Xd, sw["q"], sw["k"], sw["v"], sw["o"], sw["gate"], sw["up"], sw["down"], Yd)
+br.synchronize(); torch.cuda.synchronize()
+assert br.device_error() == 0
+Y = Yd.cpu().numpy()
+gold = o.layer(o.Q4_0, X, w["q"], w["k"], w["v"], w["o"], w["gate"], w["up"], w["down"], H, Hkv, D, F, D ** -0.5,
+               rope_theta=10000.0, kv_q8=True)
+diff = float(np.abs(Y.astype(np.float64) - gold.astype(np.float64)).max())
+assert diff <= 2 * 0.0078125, diff
+other = [torch.zeros_like(Yd) for _ in range(world)]
+dist.all_gather(other, Yd)
+assert all(torch.equal(other[0], t) for t in other), "ranks disagree"
+layer.close(); dist.barrier(); dist.destroy_process_group()
+print("rank", rank, "ok maxdiff", diff)
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_layer_tp2_nccl(tmp_path):
+    script = tmp_path / "tp_worker.py"
+    script.write_text(WORKER)
+    port = 29600 + (os.getpid() % 300)
+    procs = [subprocess.Popen([sys.executable, str(script), str(ROOT), str(port), str(r), "2"], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = []
+    for p in procs:
+        try:
+            outs.append(p.communicate(timeout=300)[0])
+        except subprocess.TimeoutExpired:
+            p.kill()
+            outs.append("timeout")
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)
