@@ -63,7 +63,8 @@ __device__ __forceinline__ unsigned long long gtimer() { unsigned long long t; a
 constexpr int W_TILE = 128;     // weight rows per tile = UMMA M
 constexpr int KSTEP = 64;       // fp16 elements per 128-byte swizzled row
 constexpr int KCHUNK = 256;     // K elements per packed-weight stage
-constexpr int RAW_STAGES = 2;
+constexpr int MAX_RAW_STAGES = 6;   // packed-weight ring depth is chosen per launch from the shared memory left over
+constexpr int SMEM_BYTES = 226 * 1024;  // dynamic shared memory of every launch
 constexpr int STAGES = 3;       // operand ring: one stage = unpacked weight tile(s) + activation tile
 constexpr int A_TILE_BYTES = W_TILE * 128;
 constexpr int TMEM_COLS = 512;
@@ -88,6 +89,7 @@ struct Params {
     uint32_t M, N, K;
     uint32_t T;                  // tokens per tile (multiple of 16)
     uint32_t n_tok_tiles, n_w_tiles, k_splits, kchunks;   // kchunks: 256-element chunks per split
+    uint32_t raw_stages, b_stage_bytes;                   // ring depth of packed weights; bytes of one activation stage (T*128)
     __half* Y;
     const __half* residual;
     float* partial_out;
@@ -97,10 +99,12 @@ struct Params {
     int* err;
 };
 
-template <int FMT, int NW> constexpr size_t smem_bytes() {
-    using C = Cfg<NW, FMT>;
-    return 1024 /*alignment slack*/ + (size_t)STAGES * C::B_STAGE_BYTES + (size_t)STAGES * NW * A_TILE_BYTES +
-           (size_t)RAW_STAGES * NW * cdc::Codec<FMT>::ROW_BYTES * W_TILE + 512 /*barriers*/;
+// Packed-weight stages that fit beside the operand ring for a given activation-tile height.
+template <int FMT, int NW> inline uint32_t raw_stages_for(uint32_t T) {
+    const long avail = (long)SMEM_BYTES - 1024 /*alignment slack*/ - 512 /*barriers*/ - (long)STAGES * NW * A_TILE_BYTES -
+                       (long)STAGES * T * 128;
+    long n = avail / ((long)NW * cdc::Codec<FMT>::ROW_BYTES * W_TILE);
+    return (uint32_t)(n < 2 ? 2 : (n > MAX_RAW_STAGES ? MAX_RAW_STAGES : n));
 }
 
 struct Tile { uint32_t wt, tt, ks, id; };
@@ -134,15 +138,15 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     QCTA(0);
     const uint32_t pad = (1024u - (ptx::smem_u32(smem_dyn) & 1023u)) & 1023u;
     uint8_t* sB = smem_dyn + pad;
-    uint8_t* sA = sB + STAGES * C::B_STAGE_BYTES;
+    uint8_t* sA = sB + STAGES * p.b_stage_bytes;
     uint8_t* sRaw = sA + STAGES * NW * A_TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + RAW_STAGES * NW * RAW_TILE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + p.raw_stages * NW * RAW_TILE_BYTES);
     uint64_t* raw_full = bars;
-    uint64_t* raw_empty = raw_full + RAW_STAGES;
+    uint64_t* raw_empty = raw_full + MAX_RAW_STAGES;
     // One full/empty pair per operand stage: "full" collects the unpack threads' arrivals plus the
     // activation TMA's byte count, "empty" is one tcgen05.commit -- so the MMA thread does one wait
     // and one commit per 64-element step.
-    uint64_t* op_full = raw_empty + RAW_STAGES;
+    uint64_t* op_full = raw_empty + MAX_RAW_STAGES;
     uint64_t* op_empty = op_full + STAGES;
     uint64_t* tm_full = op_empty + STAGES;
     uint64_t* tm_empty = tm_full + 2;
@@ -155,7 +159,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     const uint32_t ksteps = p.kchunks * (KCHUNK / KSTEP);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < RAW_STAGES; i++) { ptx::mbar_init(&raw_full[i], 1); ptx::mbar_init(&raw_empty[i], C::DQ_THREADS / 32); }
+        for (int i = 0; i < MAX_RAW_STAGES; i++) { ptx::mbar_init(&raw_full[i], 1); ptx::mbar_init(&raw_empty[i], C::DQ_THREADS / 32); }
         for (int i = 0; i < STAGES; i++) { ptx::mbar_init(&op_full[i], C::FILL_THREADS / 32 + 1); ptx::mbar_init(&op_empty[i], 1); }
         for (int i = 0; i < 2; i++) { ptx::mbar_init(&tm_full[i], 1); ptx::mbar_init(&tm_empty[i], 4); }
         *abort_flag = 0u;
@@ -196,7 +200,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                     QTR(0, wtr, 1); wtr++;
                 }
                 __syncwarp();
-                if (++rs == RAW_STAGES) { rs = 0; rph ^= 1u; }
+                if (++rs == p.raw_stages) { rs = 0; rph ^= 1u; }
             }
         }
     } else if (warp == 1) {
@@ -214,7 +218,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 if (lane == 0) {
                     QTR(1, xtr, 0);
                     ptx::mbar_arrive_expect_tx(&op_full[bs], p.T * 128u);
-                    ptx::tma_load_2d(sB + bs * C::B_STAGE_BYTES, &tmX, &op_full[bs], (int)(k0 + ks * KSTEP), (int)(t.tt * p.T));
+                    ptx::tma_load_2d(sB + bs * p.b_stage_bytes, &tmX, &op_full[bs], (int)(k0 + ks * KSTEP), (int)(t.tt * p.T));
                     QTR(1, xtr, 1); xtr++;
                 }
                 __syncwarp();
@@ -244,7 +248,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 if (!ok) break;
                 if (lane == 0) {
                     QTR(2, mtr, 2);
-                    const uint64_t bdesc = desc_hi | (uint64_t)(b_lo0 + st * (C::B_STAGE_BYTES >> 4));
+                    const uint64_t bdesc = desc_hi | (uint64_t)(b_lo0 + st * (p.b_stage_bytes >> 4));
 #pragma unroll
                     for (int w = 0; w < NW; w++) {
                         const uint64_t adesc = desc_hi | (uint64_t)(a_lo0 + (st * NW + w) * (A_TILE_BYTES >> 4));
@@ -312,7 +316,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&raw_empty[rs]);
                 if (row == 0 && w == 0) QTR(3, ((kn >> 2) - 1) * 2 + grp, 3);
-                if (++rs == RAW_STAGES) { rs = 0; rph ^= 1u; }
+                if (++rs == p.raw_stages) { rs = 0; rph ^= 1u; }
             }
         }
     } else if (warp >= (uint32_t)C::EPI_WARP0) {
@@ -369,8 +373,13 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                             if ((uint32_t)j < lim) p.Y[o + j * out_stride] = __float2half_rn(f[j] + __half2float(p.residual[o + j * out_stride]));
                     } else {
                         __half* dst = p.Y + out_base + (size_t)(tok0 + c0) * out_stride;
+                        if (lim >= 16u) {                                       // whole batch exists: no per-store predicate
 #pragma unroll
-                        for (int j = 0; j < 16; j++) if ((uint32_t)j < lim) dst[j * out_stride] = __float2half_rn(f[j]);
+                            for (int j = 0; j < 16; j++) dst[j * out_stride] = __float2half_rn(f[j]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; j++) if ((uint32_t)j < lim) dst[j * out_stride] = __float2half_rn(f[j]);
+                        }
                     }
                 }
             }
@@ -391,27 +400,39 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                     __threadfence();
                     const size_t split_stride = (size_t)(p.n_w_tiles * p.n_tok_tiles) * p.T * W_TILE;
                     const float* base = p.ws_partial + (size_t)t.id * p.T * W_TILE + q * 32 + lane;
-                    // 8 tokens x k_splits loads in flight per thread (T is a multiple of 16)
-                    for (uint32_t j0 = 0; j0 < p.T && tok0 + j0 < p.M; j0 += 8) {
-                        float acc[8];
+                    // 16 tokens x k_splits loads in flight per thread (T is a multiple of 16); the sum runs in
+                    // split order, so the result does not depend on which CTA arrived last
+                    const int fmode = p.partial_out ? 1 : (p.residual ? 2 : 3);
+                    for (uint32_t j0 = 0; j0 < valid; j0 += 16) {
+                        float acc[16];
 #pragma unroll
-                        for (int j = 0; j < 8; j++) acc[j] = 0.0f;
-                        for (uint32_t s = 0; s < p.k_splits; s++) {
+                        for (int j = 0; j < 16; j++) acc[j] = 0.0f;
+                        const float* b0 = base + (size_t)j0 * W_TILE;
+                        if (p.k_splits == 4) {
 #pragma unroll
-                            for (int j = 0; j < 8; j++) acc[j] += __ldcg(base + s * split_stride + (size_t)(j0 + j) * W_TILE);
+                            for (int s = 0; s < 4; s++)
+#pragma unroll
+                                for (int j = 0; j < 16; j++) acc[j] += __ldcg(b0 + s * split_stride + (size_t)j * W_TILE);
+                        } else {
+                            for (uint32_t s = 0; s < p.k_splits; s++)
+#pragma unroll
+                                for (int j = 0; j < 16; j++) acc[j] += __ldcg(b0 + s * split_stride + (size_t)j * W_TILE);
                         }
+                        if (n_ok) {
+                            const uint32_t lim = valid - j0;
+                            if (fmode == 1) {
+                                float* dst = p.partial_out + (size_t)(tok0 + j0) * p.N + n;
 #pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            const uint32_t tok = tok0 + j0 + j;
-                            if (n_ok && tok < p.M) {
-                                float v = acc[j];
-                                if (p.partial_out) {
-                                    p.partial_out[(size_t)tok * p.N + n] = v;
-                                } else {
-                                    const size_t o = out_base + (size_t)tok * out_stride;
-                                    if (p.residual) v += __half2float(p.residual[o]);
-                                    p.Y[o] = __float2half_rn(v);
-                                }
+                                for (int j = 0; j < 16; j++) if ((uint32_t)j < lim) dst[(size_t)j * p.N] = acc[j];
+                            } else if (fmode == 2) {
+                                const size_t o = out_base + (size_t)(tok0 + j0) * out_stride;
+#pragma unroll
+                                for (int j = 0; j < 16; j++)
+                                    if ((uint32_t)j < lim) p.Y[o + j * out_stride] = __float2half_rn(acc[j] + __half2float(p.residual[o + j * out_stride]));
+                            } else {
+                                __half* dst = p.Y + out_base + (size_t)(tok0 + j0) * out_stride;
+#pragma unroll
+                                for (int j = 0; j < 16; j++) if ((uint32_t)j < lim) dst[j * out_stride] = __float2half_rn(acc[j]);
                             }
                         }
                     }
@@ -660,6 +681,7 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     Params p;
     p.M = a.M; p.N = a.N; p.K = a.K;
     p.T = pl.T; p.n_tok_tiles = pl.n_tok_tiles; p.n_w_tiles = pl.n_w_tiles; p.k_splits = pl.k_splits; p.kchunks = pl.kchunks;
+    p.raw_stages = raw_stages_for<FMT, NW>(pl.T); p.b_stage_bytes = pl.T * 128u;
     p.Y = (__half*)a.Y; p.residual = (const __half*)a.residual; p.partial_out = a.partial_out;
     p.layout = (uint32_t)a.layout; p.H = a.H; p.D = a.D ? a.D : 1;
     p.ws_partial = ws.partial; p.ws_counters = ws.counters; p.err = ws.err;
@@ -668,7 +690,7 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
         if (!ws.partial || !ws.counters || ws.partial_floats < need) return cudaErrorInvalidValue;
     }
 
-    constexpr size_t smem = smem_bytes<FMT, NW>();
+    constexpr size_t smem = SMEM_BYTES;
     static int attr_device = -1;            // the attribute is per device; one device per process is the normal case
     int dev = 0;
     cudaGetDevice(&dev);
