@@ -47,9 +47,9 @@ M, K, N = 2048, 4096, 4096
 FLOPS_PER_STEP = 2.0 * M * N * K
 RING = 8
 FORMATS = {"q4_0": 0, "mlx_4bit": 1, "q4_k": 2, "ternary_1_58": 3, "var_rate_affine": 4, "exl3": 5}
-# dram__bytes_read.sum + dram__bytes_write.sum of one qgemm launch at this shape, from the ncu capture
-# summarised in profiles/ (None until a capture exists for the current kernel)
-NCU_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one qgemm launch (Q4_0), from the ncu captures summarised in
+# profiles/qgemm_q4_0_m2048.md and profiles/qgemm_q4_0_m33.md
+NCU_TRAFFIC_BYTES = {2048: 26.4e6, 33: 9.78e6}
 LAYER = dict(M=2048, K=4096, H=32, Hkv=8, D=128, F=14336)
 
 
@@ -279,10 +279,10 @@ def roofline(achieved_tflops, algo_bytes, ms_step, burst, sustained, hbm, src) -
     gbs = algo_bytes / (ms_step * 1e-3) / 1e9
     if M > 256:
         return {"bound": "tensor", "achieved": achieved_tflops, "peak": burst, "unit": "TFLOP/s", "frac": achieved_tflops / burst,
-                "traffic": NCU_TRAFFIC_BYTES if M == 2048 else None,
+                "traffic": NCU_TRAFFIC_BYTES.get(M),
                 "peak_source": f"{src}: dense bf16/fp16 cuBLAS burst (sustained {sustained})",
                 "algorithmic_flops_per_launch": FLOPS_PER_STEP, "algorithmic_bytes_per_launch": algo_bytes, "hbm_frac": gbs / hbm}
-    return {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "traffic": None,
+    return {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "traffic": NCU_TRAFFIC_BYTES.get(M),
             "peak_source": f"{src}: device copy bandwidth", "algorithmic_bytes_per_launch": algo_bytes,
             "algorithmic_flops_per_launch": FLOPS_PER_STEP, "tensor_frac": achieved_tflops / burst}
 
