@@ -274,6 +274,251 @@ __global__ void __launch_bounds__(THREADS) attn_q8kv_kernel(const Params p) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Grouped-head variant: one CTA = one kv head x a block of query positions x all G = Hq/Hkv query
+// heads that share that kv head (128 rows: 8 warps x 16 rows; each warp holds 16 consecutive
+// positions of one head).  A K/V tile is fetched and unpacked once for all G heads, int8 -> fp16
+// goes through the mantissa trick (no convert instructions: 0x6400 | (q ^ 0x80) is the fp16 number
+// 1024 + 128 + q), and the unpacked tiles are double-buffered so the unpack of key tile j+1
+// overlaps the MMAs of tile j across warps.
+// ---------------------------------------------------------------------------------------------
+constexpr int GQ_ROWS = 128, GQ_THREADS = 256;
+
+template <int D, int G>
+__global__ void __launch_bounds__(GQ_THREADS) attn_gqa_kernel(const Params p) {
+    constexpr int LD = D + 8;
+    constexpr int BP = GQ_ROWS / G;               // query positions per CTA
+    constexpr int ROW_RAW = (D / 32) * 34;
+    constexpr int RAW_TILE = BK * ROW_RAW;
+    constexpr int RAW_TILE_PAD = ((RAW_TILE + 15) & ~15) + 16;
+    constexpr int WPH = BP / 16;                  // warps per head
+    extern __shared__ __align__(16) uint8_t smem[];
+    __half* sQ = reinterpret_cast<__half*>(smem);
+    __half* sKV = sQ + GQ_ROWS * LD;              // [2 buffers][K, V][BK][LD]
+    uint8_t* sRaw = reinterpret_cast<uint8_t*>(sKV + 4 * BK * LD);   // [2 stages][K, V][RAW_TILE_PAD]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const uint32_t pb = gridDim.x - 1 - blockIdx.x;             // latest position blocks (longest) first
+    const uint32_t hk = blockIdx.y;
+    const uint32_t p0 = pb * BP;
+    const uint32_t last_pos = min(p.pos0 + min(p0 + BP, p.M) - 1, p.Mkv - 1);
+    const uint32_t n_ktiles = last_pos / BK + 1;
+
+    // ---- stage Q: row r = head (r / BP), position p0 + r % BP ----
+    for (int i = tid; i < GQ_ROWS * (D / 8); i += GQ_THREADS) {
+        const int r = i / (D / 8), c = i % (D / 8);
+        const uint32_t h = hk * G + r / BP, pos = p0 + r % BP;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (pos < p.M) v = *reinterpret_cast<const uint4*>(p.Q + ((size_t)h * p.M + pos) * D + c * 8);
+        *reinterpret_cast<uint4*>(sQ + r * LD + c * 8) = v;
+    }
+    const size_t kv_row_bytes = p.kv_fp16 ? (size_t)D * 2 : (size_t)ROW_RAW;
+    const uint8_t* Kh = p.K + (size_t)hk * p.Mkv * kv_row_bytes;
+    const uint8_t* Vh = p.V + (size_t)hk * p.Mkv * kv_row_bytes;
+
+    // async copy of key tile kt: packed bytes into raw stage kt&1, or fp16 rows straight into buffer kt&1
+    auto issue = [&](uint32_t kt) {
+        const uint32_t k0 = kt * BK, rows = min((uint32_t)BK, p.Mkv - k0);
+        const int st = kt & 1;
+        if (p.kv_fp16) {
+            __half* bK = sKV + (size_t)(st * 2 + 0) * BK * LD;
+            __half* bV = sKV + (size_t)(st * 2 + 1) * BK * LD;
+            for (int i = tid; i < BK * (D / 8); i += GQ_THREADS) {
+                const int r = i / (D / 8), c = i % (D / 8);
+                if ((uint32_t)r < rows) {
+                    cp_async16(bK + r * LD + c * 8, Kh + ((size_t)(k0 + r) * D + c * 8) * 2);
+                    cp_async16(bV + r * LD + c * 8, Vh + ((size_t)(k0 + r) * D + c * 8) * 2);
+                } else {
+                    *reinterpret_cast<uint4*>(bK + r * LD + c * 8) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(bV + r * LD + c * 8) = make_uint4(0, 0, 0, 0);
+                }
+            }
+        } else {
+            const uint32_t bytes = rows * ROW_RAW;
+#pragma unroll
+            for (int which = 0; which < 2; which++) {
+                const uint8_t* src = (which ? Vh : Kh) + (size_t)k0 * ROW_RAW;
+                const uint32_t ph = (uint32_t)((uintptr_t)src & 15u);
+                uint8_t* dst = sRaw + (size_t)(st * 2 + which) * RAW_TILE_PAD + ph;
+                const uint32_t head = min(bytes, (16u - ph) & 15u);
+                const uint32_t chunks = (bytes - head) / 16;
+                for (uint32_t i = tid * 2; i < head; i += GQ_THREADS * 2)
+                    *reinterpret_cast<uint16_t*>(dst + i) = *reinterpret_cast<const uint16_t*>(src + i);
+                for (uint32_t i = tid; i < chunks; i += GQ_THREADS) cp_async16(dst + head + i * 16, src + head + i * 16);
+                for (uint32_t i = head + chunks * 16 + tid * 2; i < bytes; i += GQ_THREADS * 2)
+                    *reinterpret_cast<uint16_t*>(dst + i) = *reinterpret_cast<const uint16_t*>(src + i);
+            }
+        }
+        cp_async_commit();
+    };
+
+    // raw stage kt&1 -> fp16 buffer kt&1; one thread per (row, 32-block); value = fp16(q * d) rounded once
+    auto unpack = [&](uint32_t kt) {
+        const uint32_t k0 = kt * BK, rows = min((uint32_t)BK, p.Mkv - k0);
+        const int st = kt & 1;
+        const uint8_t* kraw = sRaw + (size_t)(st * 2 + 0) * RAW_TILE_PAD + ((uintptr_t)(Kh + (size_t)k0 * ROW_RAW) & 15u);
+        const uint8_t* vraw = sRaw + (size_t)(st * 2 + 1) * RAW_TILE_PAD + ((uintptr_t)(Vh + (size_t)k0 * ROW_RAW) & 15u);
+        for (int i = tid; i < 2 * BK * (D / 32); i += GQ_THREADS) {
+            const int which = i / (BK * (D / 32));
+            const int j = i % (BK * (D / 32));
+            const int r = j / (D / 32), b = j % (D / 32);
+            __half* dst = sKV + (size_t)(st * 2 + which) * BK * LD + r * LD + b * 32;
+            if ((uint32_t)r < rows) {
+                const uint8_t* blk = (which ? vraw : kraw) + (size_t)r * ROW_RAW + b * 34;
+                const uint16_t* q16 = reinterpret_cast<const uint16_t*>(blk);
+                const uint32_t dd = q16[0];
+                const uint32_t d2 = dd | (dd << 16);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    uint32_t o[4];
+#pragma unroll
+                    for (int f = 0; f < 4; f++) {
+                        const uint32_t two = q16[1 + e * 4 + f];
+                        // bytes (b0, b1) -> lanes (bits 0-7, bits 16-23); flip the sign bit: unsigned q + 128
+                        const uint32_t x = (__byte_perm(two, 0u, 0x4140u) ^ 0x00800080u) | 0x64006400u;
+                        const __half2 qh = __hsub2(*reinterpret_cast<const __half2*>(&x), __half2half2(__float2half(1152.0f)));
+                        const __half2 w = __hmul2(qh, *reinterpret_cast<const __half2*>(&d2));
+                        o[f] = *reinterpret_cast<const uint32_t*>(&w);
+                    }
+                    *reinterpret_cast<uint4*>(dst + e * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; e++) *reinterpret_cast<uint4*>(dst + e * 8) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+
+    issue(0);
+    if (n_ktiles > 1 && !p.kv_fp16) { /* second tile is issued inside the loop, after the first unpack */ }
+    cp_async_wait<0>();
+    __syncthreads();                               // Q tile and key tile 0 are in shared memory
+    if (!p.kv_fp16) unpack(0);
+
+    const uint32_t head = hk * G + warp / WPH;
+    const uint32_t wpos = p0 + (warp % WPH) * 16;   // first query position of this warp
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < D / 16; kk++)
+        ldsm_x4(qf[kk], sQ + (warp * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8);
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.0f, 0.0f};
+    const uint32_t row_pos[2] = {p.pos0 + wpos + g, p.pos0 + wpos + g + 8};
+
+    if (n_ktiles > 1) issue(1);
+    for (uint32_t kt = 0; kt < n_ktiles; kt++) {
+        // tile kt is unpacked (or landed, fp16 KV) in buffer kt&1 once every thread passes this barrier;
+        // the packed bytes of tile kt+1 are waited for first
+        cp_async_wait<0>();
+        __syncthreads();
+        if (kt + 1 < n_ktiles && !p.kv_fp16) unpack(kt + 1);            // raw stage (kt+1)&1 -> buffer (kt+1)&1
+        const __half* sK = sKV + (size_t)((kt & 1) * 2 + 0) * BK * LD;
+        const __half* sV = sKV + (size_t)((kt & 1) * 2 + 1) * BK * LD;
+        const uint32_t k0 = kt * BK;
+        if (k0 <= p.pos0 + wpos + 15) {
+            float s[BK / 8][4];
+#pragma unroll
+            for (int i = 0; i < BK / 8; i++) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
+#pragma unroll
+            for (int kk = 0; kk < D / 16; kk++) {
+#pragma unroll
+                for (int nt = 0; nt < BK / 16; nt++) {
+                    uint32_t b[4];
+                    ldsm_x4(b, sK + (nt * 16 + (lane >> 4) * 8 + (lane & 7)) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
+                    mma16816(s[2 * nt], qf[kk], b[0], b[1]);
+                    mma16816(s[2 * nt + 1], qf[kk], b[2], b[3]);
+                }
+            }
+            float mx[2] = {m_run[0], m_run[1]};
+#pragma unroll
+            for (int nt = 0; nt < BK / 8; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const uint32_t key = k0 + nt * 8 + t4 * 2 + (e & 1);
+                    const int rr = e >> 1;
+                    float v = s[nt][e] * p.scale_log2e;
+                    if (key > row_pos[rr] || key >= p.Mkv) v = -1e30f;
+                    s[nt][e] = v;
+                    mx[rr] = fmaxf(mx[rr], v);
+                }
+#pragma unroll
+            for (int rr = 0; rr < 2; rr++) {
+                mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+                mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+            }
+            float corr[2], rs[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int rr = 0; rr < 2; rr++) { corr[rr] = exp2f(m_run[rr] - mx[rr]); m_run[rr] = mx[rr]; }
+            uint32_t pf[BK / 16][4];
+#pragma unroll
+            for (int nt = 0; nt < BK / 8; nt++) {
+                float e0 = exp2f(s[nt][0] - mx[0]), e1 = exp2f(s[nt][1] - mx[0]);
+                float e2 = exp2f(s[nt][2] - mx[1]), e3 = exp2f(s[nt][3] - mx[1]);
+                if (s[nt][0] <= -1e30f) e0 = 0.0f;
+                if (s[nt][1] <= -1e30f) e1 = 0.0f;
+                if (s[nt][2] <= -1e30f) e2 = 0.0f;
+                if (s[nt][3] <= -1e30f) e3 = 0.0f;
+                rs[0] += e0 + e1; rs[1] += e2 + e3;
+                pf[nt >> 1][(nt & 1) * 2 + 0] = pack_h2(e0, e1);
+                pf[nt >> 1][(nt & 1) * 2 + 1] = pack_h2(e2, e3);
+            }
+#pragma unroll
+            for (int rr = 0; rr < 2; rr++) l_run[rr] = l_run[rr] * corr[rr] + rs[rr];
+#pragma unroll
+            for (int i = 0; i < D / 8; i++) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; kk++) {
+#pragma unroll
+                for (int dt = 0; dt < D / 16; dt++) {
+                    uint32_t b[4];
+                    ldsm_x4_t(b, sV + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + dt * 16 + (lane >> 4) * 8);
+                    mma16816(o[2 * dt], pf[kk], b[0], b[1]);
+                    mma16816(o[2 * dt + 1], pf[kk], b[2], b[3]);
+                }
+            }
+        }
+        // The copy of tile kt+2 reuses raw stage kt&1 (unpacked before this iteration's barrier) or, for
+        // fp16 KV, buffer kt&1 -- which this iteration's MMAs still read, hence the barrier in that case.
+        if (kt + 2 < n_ktiles) {
+            if (p.kv_fp16) __syncthreads();
+            issue(kt + 2);
+        }
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int rr = 0; rr < 2; rr++) {
+        l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 1);
+        l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 2);
+    }
+    const float inv[2] = {l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f, l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f};
+#pragma unroll
+    for (int rr = 0; rr < 2; rr++) {
+        const uint32_t pos = wpos + g + rr * 8;
+        if (pos >= p.M) continue;
+        __half* dst = p.out_tokens_major ? p.O + ((size_t)pos * p.Hq + head) * D : p.O + ((size_t)head * p.M + pos) * D;
+#pragma unroll
+        for (int i = 0; i < D / 8; i++)
+            *reinterpret_cast<uint32_t*>(dst + i * 8 + t4 * 2) = pack_h2(o[i][rr * 2] * inv[rr], o[i][rr * 2 + 1] * inv[rr]);
+    }
+}
+
+template <int D> size_t gqa_smem_bytes() {
+    constexpr int LD = D + 8;
+    constexpr int RAW_TILE_PAD = (((BK * (D / 32) * 34) + 15) & ~15) + 16;
+    return (size_t)(GQ_ROWS + 4 * BK) * LD * 2 + 4 * (size_t)RAW_TILE_PAD;
+}
+
+template <int D, int G> cudaError_t launch_gqa(const Params& p, cudaStream_t stream) {
+    constexpr int BP = GQ_ROWS / G;
+    dim3 grid((p.M + BP - 1) / BP, p.Hkv);
+    cudaFuncSetAttribute(attn_gqa_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gqa_smem_bytes<D>());
+    attn_gqa_kernel<D, G><<<grid, GQ_THREADS, gqa_smem_bytes<D>(), stream>>>(p);
+    return cudaGetLastError();
+}
+
 // Q8_0 compression, one thread per 32-value block.  Bit-exact with the reference: the scale is
 // amax/127 in fp32, stored rounded to fp16, while the quantisation step uses the reciprocal of
 // the *unrounded* fp32 scale; rounding is half away from zero; codes are clamped to [-128, 127].
@@ -312,6 +557,19 @@ template <int D> size_t smem_bytes() {
 }
 
 cudaError_t launch_attention(const Params& p, uint32_t D, cudaStream_t stream) {
+    // grouped-head kernel when the group size divides its 128-row tile into whole warps
+    const uint32_t G = p.Hq / p.Hkv;
+    if (D == 128) {
+        if (G == 1) return launch_gqa<128, 1>(p, stream);
+        if (G == 2) return launch_gqa<128, 2>(p, stream);
+        if (G == 4) return launch_gqa<128, 4>(p, stream);
+        if (G == 8) return launch_gqa<128, 8>(p, stream);
+    } else if (D == 64) {
+        if (G == 1) return launch_gqa<64, 1>(p, stream);
+        if (G == 2) return launch_gqa<64, 2>(p, stream);
+        if (G == 4) return launch_gqa<64, 4>(p, stream);
+        if (G == 8) return launch_gqa<64, 8>(p, stream);
+    }
     dim3 grid((p.M + BQ - 1) / BQ, p.Hq);
     if (D == 128) {
         cudaFuncSetAttribute(attn_q8kv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<128>());

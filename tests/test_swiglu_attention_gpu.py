@@ -123,6 +123,8 @@ def test_attention_fixture(bridge):
     dict(Hq=8, Hkv=2, M=129, D=128), dict(Hq=8, Hkv=2, M=200, D=128, tokens_major=True),
     dict(Hq=3, Hkv=3, M=1, D=64), dict(Hq=4, Hkv=1, M=100, D=128, kv_fp16=True), dict(Hq=4, Hkv=4, M=64, D=64, kv_fp16=True),
     dict(Hq=4, Hkv=2, M=31, D=128, Mkv=95, pos0=64), dict(Hq=32, Hkv=8, M=512, D=128),
+    dict(Hq=8, Hkv=1, M=77, D=64), dict(Hq=16, Hkv=2, M=130, D=128, tokens_major=True), dict(Hq=6, Hkv=2, M=90, D=128),
+    dict(Hq=2, Hkv=2, M=300, D=128, kv_fp16=True), dict(Hq=8, Hkv=4, M=257, D=64, Mkv=300, pos0=43),
 ])
 def test_attention_cases(bridge, case):
     Hq, Hkv, M, D = case["Hq"], case["Hkv"], case["M"], case["D"]
