@@ -121,13 +121,22 @@ CDC_HD uint32_t lut8_pair(const uint32_t* L, uint32_t q0, uint32_t q1) {
     return (wa & ~m) | (wb & m);
 }
 
+// Traits every codec may override: META_WORDS 32-bit words of per-chunk metadata that live outside the packed
+// row (fetched from global memory by the unpack thread), ROW_SCALE when the weights are unpacked to exact small
+// integers and one fp16 scale per output row is applied to the fp32 accumulator instead.
+struct CodecDefaults {
+    static constexpr int META_WORDS = 0;
+    static constexpr bool ROW_SCALE = false;
+    static constexpr bool RAW_SWIZZLE_128 = false;   // packed tile staged with the 128-byte swizzle (ROW_BYTES == 128 only)
+};
+
 template <int FMT> struct Codec;
 
 // ---- Q4_0: 18 B / 32 (quant_router_kernels.metal:111-146) ---------------------------------
-template <> struct Codec<QUANT_Q4_0> {
+template <> struct Codec<QUANT_Q4_0> : CodecDefaults {
     static constexpr int ROW_BYTES = 144;   // 8 blocks per 256 elements
     static constexpr int GROUPS = 3;      // unpack warp groups per matrix in the projection kernel
-    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
 #pragma unroll
         for (int bi = 0; bi < 2; bi++) {
             const int o = 18 * (2 * s + bi);
@@ -144,10 +153,10 @@ template <> struct Codec<QUANT_Q4_0> {
 };
 
 // ---- MLX 4-bit affine, 20 B / 32 (quant_router_kernels.metal:149-185) -----------------------
-template <> struct Codec<QUANT_MLX_4BIT> {
+template <> struct Codec<QUANT_MLX_4BIT> : CodecDefaults {
     static constexpr int ROW_BYTES = 160;
     static constexpr int GROUPS = 3;      // unpack warp groups per matrix in the projection kernel
-    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
 #pragma unroll
         for (int bi = 0; bi < 2; bi++) {
             const int o = 20 * (2 * s + bi);
@@ -164,10 +173,10 @@ template <> struct Codec<QUANT_MLX_4BIT> {
 };
 
 // ---- Q4_K, 144 B / 256 (quant_router_kernels.metal:188-238; gold cpu_gold_reference.h:116-146) --
-template <> struct Codec<QUANT_Q4_K> {
+template <> struct Codec<QUANT_Q4_K> : CodecDefaults {
     static constexpr int ROW_BYTES = 144;
     static constexpr int GROUPS = 3;      // unpack warp groups per matrix in the projection kernel
-    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
         const uint32_t d_dmin = r[0];   // (d, dmin) as an fp16 pair
 #pragma unroll
         for (int bi = 0; bi < 2; bi++) {
@@ -195,10 +204,10 @@ template <> struct Codec<QUANT_Q4_K> {
 };
 
 // ---- ternary, 12 B / 32 (gold cpu_gold_reference.h:176-189: value = (code-1)*d, code 3 -> +2d) --
-template <> struct Codec<QUANT_TERNARY_1_58> {
+template <> struct Codec<QUANT_TERNARY_1_58> : CodecDefaults {
     static constexpr int ROW_BYTES = 96;
     static constexpr int GROUPS = 3;      // unpack warp groups per matrix in the projection kernel
-    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
 #pragma unroll
         for (int bi = 0; bi < 2; bi++) {
             const int w = 3 * (2 * s + bi);
@@ -218,10 +227,10 @@ template <> struct Codec<QUANT_TERNARY_1_58> {
 };
 
 // ---- EXL3-style codebook, 144 B / 256 (quant_router_kernels.metal:368-411; gold :342-389) ---------
-template <> struct Codec<QUANT_EXL3> {
+template <> struct Codec<QUANT_EXL3> : CodecDefaults {
     static constexpr int ROW_BYTES = 144;
     static constexpr int GROUPS = 2;      // unpack warp groups per matrix in the projection kernel
-    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
         const float d = h_lo_to_float(r[0]), bias = h_hi_to_float(r[0]);
 #pragma unroll
         for (int bi = 0; bi < 2; bi++) {
@@ -252,10 +261,10 @@ template <> struct Codec<QUANT_EXL3> {
 };
 
 // ---- variable-rate affine, 160 B / 256 (quant_router_kernels.metal:265-365; gold :214-311) ---------
-template <> struct Codec<QUANT_VAR_RATE_AFFINE> {
+template <> struct Codec<QUANT_VAR_RATE_AFFINE> : CodecDefaults {
     static constexpr int ROW_BYTES = 160;
     static constexpr int GROUPS = 2;      // unpack warp groups per matrix in the projection kernel
-    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out) {
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
         const float d = h_lo_to_float(r[0]), bias = h_hi_to_float(r[0]);
 #pragma unroll
         for (int bi = 0; bi < 2; bi++) {
@@ -310,6 +319,55 @@ template <> struct Codec<QUANT_VAR_RATE_AFFINE> {
                                          : prmt(pk[2 * (i - 8)], pk[2 * (i - 8) + 1], 0x7632u);
                 uint32_t rev = prmt(pk[15 - i], 0u, 0x1032u);
                 out[16 * bi + i] = (perm == 1u) ? deint : ((perm == 2u) ? rev : ident);
+            }
+        }
+    }
+};
+
+// ---- MLX 4-bit, group 64, sequential nibbles, planar (extension layout 100) --------------------------
+// Packed row: u32 words of 8 nibbles, nibble t of word i is k = 8i + t; 128 bytes per 256 elements.  Per 64
+// elements one fp16 scale and one fp16 bias in two planes behind the nibble plane; meta[0..1] hold the four
+// scales of the chunk, meta[2..3] the four biases.  w = q*s + b, one fused fp16 multiply-add.
+template <> struct Codec<QUANT_MLX_4BIT_G64> : CodecDefaults {
+    static constexpr int ROW_BYTES = 128;
+    static constexpr int GROUPS = 3;
+    static constexpr int META_WORDS = 4;
+    static constexpr bool RAW_SWIZZLE_128 = true;
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* meta) {
+        const uint32_t d2 = bcast16(meta, 2 * s), b2 = bcast16(meta + 2, 2 * s);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t w = r[8 * s + i], w8 = w >> 8;
+            // nibble pairs (n0,n4) (n1,n5) (n2,n6) (n3,n7) as (1024+n) or (64+n) halves, then back to k order
+            const uint32_t a04 = h2fma(h2sub((w & 0x000F000Fu) | H2_1024, H2_1024), d2, b2);
+            const uint32_t a15 = h2fma(h2sub((w & 0x00F000F0u) | H2_64, H2_64), d2, b2);
+            const uint32_t a26 = h2fma(h2sub((w8 & 0x000F000Fu) | H2_1024, H2_1024), d2, b2);
+            const uint32_t a37 = h2fma(h2sub((w8 & 0x00F000F0u) | H2_64, H2_64), d2, b2);
+            out[4 * i + 0] = prmt(a04, a15, 0x5410u);
+            out[4 * i + 1] = prmt(a26, a37, 0x5410u);
+            out[4 * i + 2] = prmt(a04, a15, 0x7632u);
+            out[4 * i + 3] = prmt(a26, a37, 0x7632u);
+        }
+    }
+};
+
+// ---- ternary with one scale per output row, planar (extension layout 101) -------------------------------
+// Packed row: u32 words of 16 two-bit codes, code t of word i is k = 16i + t; 64 bytes per 256 elements.  The
+// weights go to the tensor core as the exact integers code - 1; the row's fp16 scale multiplies the fp32
+// accumulator in the epilogue, so the result is rounded once.
+template <> struct Codec<QUANT_TERNARY_ROW> : CodecDefaults {
+    static constexpr int ROW_BYTES = 64;
+    static constexpr int GROUPS = 3;
+    static constexpr bool ROW_SCALE = true;
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
+#pragma unroll
+        for (int wi = 0; wi < 4; wi++) {
+            const uint32_t q = r[4 * s + wi];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t t = q >> (4 * i);
+                const uint32_t x = (t & 3u) | ((t << 14) & 0x30000u) | H2_1024;
+                out[8 * wi + i] = h2sub(x, H2_1025);
             }
         }
     }

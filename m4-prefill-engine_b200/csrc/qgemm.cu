@@ -97,6 +97,11 @@ struct Params {
     float* ws_partial;
     uint32_t* ws_counters;
     int* err;
+    // planar layouts: per-64 scale plane followed by the bias plane (meta), or one fp16 scale per row
+    const uint8_t* meta0;
+    const uint8_t* meta1;
+    const __half* row_scale0;
+    const __half* row_scale1;
 };
 
 // Packed-weight stages that fit beside the operand ring for a given activation-tile height.
@@ -277,7 +282,29 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         uint32_t rs = 0, rph = 0, kn = 0;                     // kn: running 64-element step of this CTA
         bool ok = true;
         for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
+            const Tile t = decode_tile(idx, p);
+            uint32_t meta_next[4] = {0u, 0u, 0u, 0u};
+            auto load_meta = [&](uint32_t kc, uint32_t (&m)[4]) {
+                const uint32_t n = t.wt * W_TILE + row;
+                if (n < p.N) {
+                    const uint32_t g64 = p.K / 64;
+                    const uint8_t* mp = (w == 0 ? p.meta0 : p.meta1) + ((size_t)n * g64 + (size_t)(t.ks * p.kchunks + kc) * 4) * 2;
+                    const uint2 sc = __ldg(reinterpret_cast<const uint2*>(mp));
+                    const uint2 bi = __ldg(reinterpret_cast<const uint2*>(mp + (size_t)p.N * g64 * 2));
+                    m[0] = sc.x; m[1] = sc.y; m[2] = bi.x; m[3] = bi.y;
+                }
+            };
+            (void)load_meta; (void)meta_next;
             for (uint32_t kc = 0; ok && kc < p.kchunks; kc++) {
+                // scales and biases kept outside the packed rows come straight from global memory, one chunk
+                // ahead of their use so the latency hides behind the unpacking of the current chunk
+                uint32_t meta[4] = {0u, 0u, 0u, 0u};
+                if (Cd::META_WORDS == 4) {
+                    if (kc == 0) load_meta(0u, meta_next);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) meta[i] = meta_next[i];
+                    if (kc + 1 < p.kchunks) load_meta(kc + 1, meta_next);
+                }
                 ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&raw_full[rs], rph, abort_flag, p.err, 106));
                 if (!ok) break;
                 if (row == 0 && w == 0) QTR(3, (kn >> 2) * 2 + grp, 0);
@@ -285,14 +312,16 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 const uint4* src = reinterpret_cast<const uint4*>(sRaw + (rs * NW + w) * RAW_TILE_BYTES + row * ROW_BYTES);
 #pragma unroll
                 for (int i = 0; i < ROW_BYTES / 16; i++) {
-                    uint4 v = src[i];
+                    // rows of exactly 128 bytes would put every lane on the same banks: those tiles are loaded
+                    // with the 128-byte TMA swizzle (16-byte chunk index ^ row % 8) and read back through it
+                    uint4 v = src[Cd::RAW_SWIZZLE_128 ? (i ^ (int)(row & 7u)) : i];
                     r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
                 }
 #pragma unroll
                 for (int s = 0; s < KCHUNK / KSTEP; s++) {
                     if ((G == STAGES ? (kn + s) % STAGES : (uint32_t)(s % G)) == grp) {
                         uint32_t o[32];
-                        Cd::dequant64(r, s, o);
+                        Cd::dequant64(r, s, o, meta);
                         if (row == 0 && w == 0) QTR(4 + grp, kn + s, 0);
                         const uint32_t step = kn + s, as = step % STAGES, aph = (step / STAGES) & 1u;
                         ok = __all_sync(0xffffffffu, ok && ptx::mbar_wait<32>(&op_empty[as], aph ^ 1u, abort_flag, p.err, 107));
@@ -343,6 +372,12 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             // the inner loops to a convert, an address add and a store.
             const uint32_t valid = tok0 < p.M ? min(p.T, p.M - tok0) : 0u;     // token columns of this tile that exist
             const int mode = p.k_splits > 1 ? 0 : (p.partial_out ? 1 : (p.residual ? 2 : 3));
+            // integer-valued codecs: the row's scale multiplies the fp32 accumulator (before SiLU, before split-K sums)
+            float rsc0 = 1.0f, rsc1 = 1.0f;
+            if (Cd::ROW_SCALE) {
+                rsc0 = n_ok ? __half2float(p.row_scale0[n]) : 0.0f;
+                if (NW == 2) rsc1 = n_ok ? __half2float(p.row_scale1[n]) : 0.0f;
+            }
             for (uint32_t c0 = 0; c0 < p.T; c0 += 16) {
                 uint32_t v[16], u[16];
                 if (et == 0 && it == 0) QTR(7, 1 + c0 / 16, 0);
@@ -354,7 +389,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     f[j] = __uint_as_float(v[j]);
-                    if (NW == 2) f[j] = silu_mul(f[j], __uint_as_float(u[j]));
+                    if (Cd::ROW_SCALE) f[j] *= rsc0;
+                    if (NW == 2) f[j] = silu_mul(f[j], Cd::ROW_SCALE ? __uint_as_float(u[j]) * rsc1 : __uint_as_float(u[j]));
                 }
                 if (mode == 0) {
                     float* dst = ws + (size_t)c0 * W_TILE + q * 32 + lane;
@@ -621,6 +657,8 @@ int row_bytes_256(int fmt) {
         case QUANT_TERNARY_1_58: return 96;
         case QUANT_VAR_RATE_AFFINE: return 160;
         case QUANT_EXL3: return 144;
+        case QUANT_MLX_4BIT_G64: return 128;     // nibble plane only; scales and biases sit in planes behind it
+        case QUANT_TERNARY_ROW: return 64;       // 2-bit plane only; one fp16 scale per row behind it
         default: return 0;
     }
 }
@@ -671,11 +709,10 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     if (!make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.X, a.K, a.M, (uint64_t)a.K * 2, KSTEP, pl.T,
                      CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
-    if (!make_map_2d(&tmW0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.W0, w_row_bytes, a.N, w_row_bytes, rb, W_TILE,
-                     CU_TENSOR_MAP_SWIZZLE_NONE))
+    const CUtensorMapSwizzle wsw = cdc::Codec<FMT>::RAW_SWIZZLE_128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;
+    if (!make_map_2d(&tmW0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.W0, w_row_bytes, a.N, w_row_bytes, rb, W_TILE, wsw))
         return cudaErrorInvalidValue;
-    if (!make_map_2d(&tmW1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.W1 ? a.W1 : a.W0, w_row_bytes, a.N, w_row_bytes, rb, W_TILE,
-                     CU_TENSOR_MAP_SWIZZLE_NONE))
+    if (!make_map_2d(&tmW1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.W1 ? a.W1 : a.W0, w_row_bytes, a.N, w_row_bytes, rb, W_TILE, wsw))
         return cudaErrorInvalidValue;
 
     Params p;
@@ -685,6 +722,12 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     p.Y = (__half*)a.Y; p.residual = (const __half*)a.residual; p.partial_out = a.partial_out;
     p.layout = (uint32_t)a.layout; p.H = a.H; p.D = a.D ? a.D : 1;
     p.ws_partial = ws.partial; p.ws_counters = ws.counters; p.err = ws.err;
+    // planar layouts: everything behind the N x (K/256 * ROW_BYTES) plane of packed values
+    const size_t plane = (size_t)a.N * w_row_bytes;
+    p.meta0 = (const uint8_t*)a.W0 + plane;
+    p.meta1 = a.W1 ? (const uint8_t*)a.W1 + plane : p.meta0;
+    p.row_scale0 = (const __half*)p.meta0;
+    p.row_scale1 = (const __half*)p.meta1;
     if (pl.k_splits > 1) {
         const size_t need = (size_t)pl.k_splits * pl.n_tok_tiles * pl.n_w_tiles * pl.T * W_TILE;
         if (!ws.partial || !ws.counters || ws.partial_floats < need) return cudaErrorInvalidValue;
@@ -714,6 +757,8 @@ cudaError_t dispatch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t s
         case QUANT_TERNARY_1_58: return launch_fast<QUANT_TERNARY_1_58, NW>(a, ws, s);
         case QUANT_VAR_RATE_AFFINE: return launch_fast<QUANT_VAR_RATE_AFFINE, NW>(a, ws, s);
         case QUANT_EXL3: return launch_fast<QUANT_EXL3, NW>(a, ws, s);
+        case QUANT_MLX_4BIT_G64: return launch_fast<QUANT_MLX_4BIT_G64, NW>(a, ws, s);
+        case QUANT_TERNARY_ROW: return launch_fast<QUANT_TERNARY_ROW, NW>(a, ws, s);
         default: return cudaErrorInvalidValue;
     }
 }

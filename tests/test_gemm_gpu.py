@@ -104,10 +104,33 @@ def test_every_format_on_the_fallback_kernel(bridge):
 
 
 @pytest.mark.parametrize("fmt", [o.MLX_4BIT_G64, o.TERNARY_ROW])
-def test_extension_layouts(bridge, fmt):
-    M, K, N = 33, 512, 96
+@pytest.mark.parametrize("shape", [(33, 512, 96), (1, 4096, 200), (129, 4096, 1000), (300, 1024, 130), (40, 192, 70)])
+def test_extension_layouts(bridge, fmt, shape):
+    """Planar layouts 100 / 101: tensor-core path (K % 256 == 0; the K = 4096 cases split K and cut ragged
+    row and token tiles) and the CUDA-core path (K = 192), which must agree with each other as well."""
+    M, K, N = shape
     X, W = o.baseline_inputs(fmt, M, K, N, 3)
-    check(run_gemm(bridge, fmt, X, W, N, ex=True), o.gemm_f64(fmt, X, W, N), f"fmt {fmt}")
+    gold = o.gemm_f64(fmt, X, W, N)
+    Y = run_gemm(bridge, fmt, X, W, N, ex=True)
+    check(Y, gold, f"fmt {fmt} {shape}")
+    bridge.lib.b200_bridge_force_generic(1)
+    try:
+        Yg = run_gemm(bridge, fmt, X, W, N, ex=True)
+    finally:
+        bridge.lib.b200_bridge_force_generic(0)
+    check(Yg, gold, f"fmt {fmt} {shape} generic")
+
+
+@pytest.mark.parametrize("fmt", [o.MLX_4BIT_G64, o.TERNARY_ROW])
+def test_extension_layouts_swiglu(bridge, fmt):
+    from gpu_util import check_swiglu
+    from test_swiglu_attention_gpu import run_swiglu
+    M, K, F = 130, 512, 300
+    X, Wg = o.baseline_inputs(fmt, M, K, F, 8)
+    _, Wu = o.baseline_inputs(fmt, M, K, F, 9)
+    X = (X.astype(np.float32) * 0.25).astype(np.float16)
+    out = run_swiglu(bridge, fmt, X, Wg, Wu, F)
+    check_swiglu(out, o.gemm_f64(fmt, X, Wg, F), o.gemm_f64(fmt, X, Wu, F), f"swiglu fmt {fmt}")
 
 
 def test_host_pointers_and_gemv(bridge):

@@ -145,6 +145,23 @@ def test_unpackers_baseline_distribution(codec_lib):
         assert np.array_equal(out.view(np.float16).astype(np.float64), ref.astype(np.float16).astype(np.float64))
 
 
+def test_planar_unpackers_match_oracle(codec_lib):
+    """The two planar extension layouts: nibble / 2-bit plane through the tensor-core codec, metadata planes beside it."""
+    K, N = 1024, 40
+    for fmt in (o.MLX_4BIT_G64, o.TERNARY_ROW):
+        _, W = o.baseline_inputs(fmt, 1, K, N, 5)
+        out = np.empty((N, K), np.uint16)
+        assert codec_lib.codec_host_dequant(fmt, o._ptr(W), o._ptr(out), N, K) == 0
+        got = out.view(np.float16).astype(np.float64)
+        ref = o.dequant_matrix(fmt, W, N, K)
+        if fmt == o.TERNARY_ROW:            # the codec yields the integers code-1; the row scale is applied to the accumulator
+            assert set(np.unique(got)) <= {-1.0, 0.0, 1.0}
+            got = got * W[N * K // 4:].view(np.float16).astype(np.float64)[:, None]
+            assert np.array_equal(got, ref)
+        else:
+            assert np.array_equal(got, ref.astype(np.float16).astype(np.float64))
+
+
 # ---- Linear wrapper argument contract (tests/redteam_modules.py:122-176) ----
 def test_linear_wrapper_rejects_bad_shapes(pkg):
     from m4_prefill_engine_b200.modules import M4QuantizedLinear, compute_quantized_weight_bytes, normalize_format
