@@ -1,7 +1,7 @@
 // Dequant-fused projection GEMM and dual gate/up SwiGLU for sm_100a.
 //
-//   Y[m][n] = sum_k X[m][k] * dequant(W)[n][k]            (NW == 1)
-//   Y[m][n] = silu(X.Wg^T)[m][n] * (X.Wu^T)[m][n]         (NW == 2)
+//   Y[m][n] = sum_k X[m][k] * dequant(W)[n][k]
+//   Y[m][n] = silu(X.Wg^T)[m][n] * (X.Wu^T)[m][n]         (SwiGLU: tiles of 64 gate rows + their 64 up rows)
 //
 // Replaces the reference's 64x64 simdgroup-matrix engine and its 14 entry points
 // (quant_router_kernels.metal:442-927) and the Brick-3 fused SwiGLU
@@ -9,13 +9,16 @@
 //
 //   * operands are swapped: the 128 weight rows of a tile are the UMMA "M" side, up to 256
 //     tokens are the "N" side, so one unpacked weight tile feeds a 128 x T x 16 MMA;
-//   * warp 0 streams packed weight bytes with TMA (2-D map over the raw byte matrix, one box =
-//     128 rows x the bytes of 256 K-elements, no swizzle, 2-stage ring); warp 1 streams fp16
-//     activations with TMA into 128-byte-swizzled K-major tiles; warp 2 issues tcgen05.mma (fp16 x
-//     fp16 -> fp32 in tensor memory); 8-16 unpack warps turn packed bytes into the swizzled fp16
-//     K-major layout the MMA reads; the last 4 warps drain tensor memory and write fp16.  Weight
-//     and activation tiles of one 64-element K step share a 3-deep operand ring with one
-//     full/empty mbarrier pair per stage;
+//   * one warp streams packed weight bytes with TMA (2-D map over the raw byte matrix, one box =
+//     128 rows x the bytes of 256 K-elements, ring of 2-6 stages sized from the shared memory left
+//     over); one warp streams fp16 activations with TMA into 128-byte-swizzled K-major tiles; one
+//     warp issues tcgen05.mma (fp16 x fp16 -> fp32 in tensor memory); 8-12 unpack warps turn packed
+//     bytes into the swizzled fp16 K-major layout the MMA reads; the last 4 warps drain tensor
+//     memory and write fp16.  Weight and activation tiles of one 64-element K step share a 3-deep
+//     operand ring with one full/empty mbarrier pair per stage;
+//   * a SwiGLU tile is 64 rows of the gate matrix plus the same 64 rows of the up matrix (two TMA
+//     boxes into one packed stage), so unpacking, MMA shape and tile width are those of the plain
+//     projection; the epilogue pairs each gate lane with its up lane through shared memory;
 //   * two accumulator buffers in tensor memory overlap a tile's epilogue with the next tile;
 //   * for few tokens the K range is split across CTAs; partial tiles meet in a scratch buffer
 //     and the last CTA of a tile adds them in split order (deterministic) and writes Y.
@@ -70,19 +73,29 @@ constexpr int A_TILE_BYTES = W_TILE * 128;
 constexpr int TMEM_COLS = 512;
 constexpr int ACC_STRIDE = 256; // tensor-memory columns per accumulator buffer
 
-template <int NW, int FMT = 0> struct Cfg {
-    static constexpr int TOK_MAX = NW == 1 ? 256 : 128;
-    static constexpr int B_STAGE_BYTES = TOK_MAX * 128;
-    // Unpack warp groups per weight matrix.  With G == STAGES group g owns operand stage g (it unpacks every
-    // step with step % STAGES == g); with G < STAGES group g takes the sub-tiles s with s % G == g.  G must not
-    // exceed STAGES: the parity wait on a stage's "empty" barrier is only unambiguous if the waiting group is
-    // never two phases ahead, which holds when its own previous wait already implied the phase before.
-    static constexpr int DQ_GROUPS = NW == 1 ? cdc::Codec<FMT>::GROUPS : (cdc::Codec<FMT>::GROUPS + 1) / 2;
+constexpr int XCHG_BYTES = 2 * 128 * 32;   // SwiGLU epilogue: two buffers of 8 floats per epilogue thread
+constexpr int GATE_ROWS = W_TILE / 2;      // SwiGLU tile: 64 gate rows on TMEM lanes 0..63, their 64 up rows on lanes 64..127
+
+template <int FMT> struct Cfg {
+    // Unpack warp groups.  With G == STAGES group g owns operand stage g (it unpacks every step with
+    // step % STAGES == g); with G < STAGES group g takes the sub-tiles s with s % G == g.  G must not exceed
+    // STAGES: the parity wait on a stage's "empty" barrier is only unambiguous if the waiting group is never
+    // two phases ahead, which holds when its own previous wait already implied the phase before.
+    static constexpr int DQ_GROUPS = cdc::Codec<FMT>::GROUPS;
     static_assert(DQ_GROUPS >= 1 && DQ_GROUPS <= STAGES, "unpack groups are bounded by the operand ring depth");
-    static constexpr int DQ_THREADS = 128 * NW * DQ_GROUPS;   // arrivals that release a packed stage
-    static constexpr int FILL_THREADS = 128 * NW;             // arrivals that publish an unpacked stage
-    static constexpr int EPI_WARP0 = 4 + DQ_THREADS / 32;
-    static constexpr int THREADS = 128 + DQ_THREADS + 128;
+    static constexpr int DQ_THREADS = 128 * DQ_GROUPS;   // arrivals that release a packed stage
+    static constexpr int FILL_THREADS = 128;             // arrivals that publish an unpacked stage
+    // Warp placement.  A warp's scheduler is warp % 4.  The MMA-issuing thread is back-pressured by the tensor
+    // pipe with next to no queueing, so every cycle one of its few instructions waits for an issue slot is idle
+    // tensor time: measured on B200, three ALU-busy warps on its scheduler stretch a 64-element step from about
+    // 575 to 700 cycles, the same warps on the other schedulers cost nothing.  Scheduler 2 therefore hosts only
+    // the light warps (MMA issuer = warp 2, packed-weight producer = warp 6, activation producer = warp 10, idle
+    // warps behind them, and the one epilogue warp that must sit there for its TMEM lane quadrant); the unpack
+    // warps take the ids with warp % 4 != 2, three per group of four ids.
+    static constexpr int DQ_WARPS = DQ_THREADS / 32;
+    static constexpr int QUADS = (DQ_WARPS + 2) / 3 < 3 ? 3 : (DQ_WARPS + 2) / 3;
+    static constexpr int EPI_WARP0 = 4 * QUADS;
+    static constexpr int THREADS = (EPI_WARP0 + 4) * 32;
 };
 
 struct Params {
@@ -98,6 +111,7 @@ struct Params {
     uint32_t* ws_counters;
     int* err;
     // planar layouts: per-64 scale plane followed by the bias plane (meta), or one fp16 scale per row
+    uint32_t swiglu;             // 1: tiles are 64 gate rows (matrix 0) + their 64 up rows (matrix 1); output = silu(g) * u
     const uint8_t* meta0;
     const uint8_t* meta1;
     const __half* row_scale0;
@@ -105,10 +119,10 @@ struct Params {
 };
 
 // Packed-weight stages that fit beside the operand ring for a given activation-tile height.
-template <int FMT, int NW> inline uint32_t raw_stages_for(uint32_t T) {
-    const long avail = (long)SMEM_BYTES - 1024 /*alignment slack*/ - 512 /*barriers*/ - (long)STAGES * NW * A_TILE_BYTES -
-                       (long)STAGES * T * 128;
-    long n = avail / ((long)NW * cdc::Codec<FMT>::ROW_BYTES * W_TILE);
+template <int FMT> inline uint32_t raw_stages_for(uint32_t T, bool swiglu) {
+    const long avail = (long)SMEM_BYTES - 1024 /*alignment slack*/ - 512 /*barriers*/ - (swiglu ? XCHG_BYTES : 0) -
+                       (long)STAGES * A_TILE_BYTES - (long)STAGES * T * 128;
+    long n = avail / ((long)cdc::Codec<FMT>::ROW_BYTES * W_TILE);
     return (uint32_t)(n < 2 ? 2 : (n > MAX_RAW_STAGES ? MAX_RAW_STAGES : n));
 }
 
@@ -130,11 +144,11 @@ __device__ __forceinline__ size_t out_index(const Params& p, uint32_t tok, uint3
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
-template <int FMT, int NW>
-__global__ void __launch_bounds__(Cfg<NW, FMT>::THREADS, 1)
+template <int FMT>
+__global__ void __launch_bounds__(Cfg<FMT>::THREADS, 1)
 qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW0,
              const __grid_constant__ CUtensorMap tmW1, const Params p) {
-    using C = Cfg<NW, FMT>;
+    using C = Cfg<FMT>;
     using Cd = cdc::Codec<FMT>;
     constexpr int ROW_BYTES = Cd::ROW_BYTES;
     constexpr int RAW_TILE_BYTES = ROW_BYTES * W_TILE;
@@ -144,8 +158,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     const uint32_t pad = (1024u - (ptx::smem_u32(smem_dyn) & 1023u)) & 1023u;
     uint8_t* sB = smem_dyn + pad;
     uint8_t* sA = sB + STAGES * p.b_stage_bytes;
-    uint8_t* sRaw = sA + STAGES * NW * A_TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + p.raw_stages * NW * RAW_TILE_BYTES);
+    uint8_t* sRaw = sA + STAGES * A_TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + p.raw_stages * RAW_TILE_BYTES);
     uint64_t* raw_full = bars;
     uint64_t* raw_empty = raw_full + MAX_RAW_STAGES;
     // One full/empty pair per operand stage: "full" collects the unpack threads' arrivals plus the
@@ -158,6 +172,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tm_empty + 2);
     volatile uint32_t* abort_flag = tmem_holder + 1;
     volatile uint32_t* last_flag = tmem_holder + 2;
+    float4* xchg = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(bars) + 512);   // SwiGLU launches only
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t total_tiles = p.n_w_tiles * p.n_tok_tiles * p.k_splits;
@@ -182,11 +197,15 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     if (threadIdx.x == 0) QTRC(7, 0u, 0);
     QCTA(1);
 
-    if (warp == 0) {
+    const uint32_t wq = warp & 3u, wg = warp >> 2;
+    const bool pre_epi = warp < (uint32_t)C::EPI_WARP0;
+    // unpack warp index among the ids with warp % 4 != 2 (meaningless for the others)
+    const uint32_t uw = wg * 3u + (wq == 3u ? 2u : wq);
+    if (pre_epi && wq == 2u && wg == 1u) {
         // ---------------- packed-weight producer ----------------
         // The whole warp walks the loop (only lane 0 issues): a lone lane looping while its 31 siblings
         // already sit at the final barrier gets scheduled far less often than a converged warp.
-        if (lane == 0) { ptx::prefetch_tensormap(&tmW0); if (NW == 2) ptx::prefetch_tensormap(&tmW1); }
+        if (lane == 0) { ptx::prefetch_tensormap(&tmW0); if (p.swiglu) ptx::prefetch_tensormap(&tmW1); }
         uint32_t rs = 0, rph = 0, wtr = 0;
         (void)wtr;
         bool ok = true;
@@ -197,18 +216,22 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 if (!ok) break;
                 if (lane == 0) {
                     QTR(0, wtr, 0);
-                    ptx::mbar_arrive_expect_tx(&raw_full[rs], NW * RAW_TILE_BYTES);
+                    ptx::mbar_arrive_expect_tx(&raw_full[rs], RAW_TILE_BYTES);
                     const int x = (int)((t.ks * p.kchunks + kc) * ROW_BYTES);
-                    const int y = (int)(t.wt * W_TILE);
-                    ptx::tma_load_2d(sRaw + (rs * NW + 0) * RAW_TILE_BYTES, &tmW0, &raw_full[rs], x, y);
-                    if (NW == 2) ptx::tma_load_2d(sRaw + (rs * NW + 1) * RAW_TILE_BYTES, &tmW1, &raw_full[rs], x, y);
+                    if (p.swiglu) {     // the maps of a SwiGLU launch have 64-row boxes: gate rows, then the same rows of up
+                        const int y = (int)(t.wt * GATE_ROWS);
+                        ptx::tma_load_2d(sRaw + rs * RAW_TILE_BYTES, &tmW0, &raw_full[rs], x, y);
+                        ptx::tma_load_2d(sRaw + rs * RAW_TILE_BYTES + GATE_ROWS * ROW_BYTES, &tmW1, &raw_full[rs], x, y);
+                    } else {
+                        ptx::tma_load_2d(sRaw + rs * RAW_TILE_BYTES, &tmW0, &raw_full[rs], x, (int)(t.wt * W_TILE));
+                    }
                     QTR(0, wtr, 1); wtr++;
                 }
                 __syncwarp();
                 if (++rs == p.raw_stages) { rs = 0; rph ^= 1u; }
             }
         }
-    } else if (warp == 1) {
+    } else if (pre_epi && wq == 2u && wg == 2u) {
         // ---------------- activation producer ----------------
         if (lane == 0) ptx::prefetch_tensormap(&tmX);
         uint32_t bs = 0, bph = 0, xtr = 0;
@@ -254,14 +277,11 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 if (lane == 0) {
                     QTR(2, mtr, 2);
                     const uint64_t bdesc = desc_hi | (uint64_t)(b_lo0 + st * (p.b_stage_bytes >> 4));
+                    const uint64_t adesc = desc_hi | (uint64_t)(a_lo0 + st * (A_TILE_BYTES >> 4));
+                    const uint32_t dcol = tmem_base + buf * ACC_STRIDE;
 #pragma unroll
-                    for (int w = 0; w < NW; w++) {
-                        const uint64_t adesc = desc_hi | (uint64_t)(a_lo0 + (st * NW + w) * (A_TILE_BYTES >> 4));
-                        const uint32_t dcol = tmem_base + buf * ACC_STRIDE + w * 128;
-#pragma unroll
-                        for (int kk = 0; kk < KSTEP / 16; kk++)
-                            ptx::umma_f16_ss(dcol, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | (uint32_t)kk) != 0u);
-                    }
+                    for (int kk = 0; kk < KSTEP / 16; kk++)
+                        ptx::umma_f16_ss(dcol, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | (uint32_t)kk) != 0u);
                     ptx::umma_commit(&op_empty[st]);
                     QTR(2, mtr, 3); mtr++;
                 }
@@ -271,13 +291,15 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             if (ok && lane == 0) { ptx::umma_commit(&tm_full[buf]); QTRC(2, 200u + it, 1); }
             __syncwarp();
         }
-    } else if (warp >= 4 && warp < (uint32_t)C::EPI_WARP0) {
+    } else if (pre_epi && wq != 2u && uw < (uint32_t)C::DQ_WARPS) {
         // ---------------- unpack warps: packed bytes -> swizzled fp16 K-major tile ----------------
         constexpr int G = C::DQ_GROUPS;
-        const uint32_t dq = threadIdx.x - 128;                // 0 .. DQ_THREADS-1
-        const uint32_t grp = (dq >> 7) % G;                   // sub-tile phase this warp group unpacks
-        const uint32_t w = (dq >> 7) / G;                     // which weight matrix
+        const uint32_t dq = uw * 32u + lane;                  // 0 .. DQ_THREADS-1
+        const uint32_t grp = dq >> 7;                         // sub-tile phase this warp group unpacks
         const uint32_t row = dq & 127;                        // weight row inside the tile
+        // which matrix the row comes from, and its row there (SwiGLU tiles hold 64 rows of each)
+        const uint32_t mat = p.swiglu ? (row >> 6) : 0u;
+        const uint32_t mrow_in_tile = p.swiglu ? (row & 63u) : row;
         const uint32_t row_off = (row >> 3) * 1024 + (row & 7) * 128, xr = row & 7;
         uint32_t rs = 0, rph = 0, kn = 0;                     // kn: running 64-element step of this CTA
         bool ok = true;
@@ -285,10 +307,10 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             const Tile t = decode_tile(idx, p);
             uint32_t meta_next[4] = {0u, 0u, 0u, 0u};
             auto load_meta = [&](uint32_t kc, uint32_t (&m)[4]) {
-                const uint32_t n = t.wt * W_TILE + row;
+                const uint32_t n = t.wt * (p.swiglu ? GATE_ROWS : W_TILE) + mrow_in_tile;
                 if (n < p.N) {
                     const uint32_t g64 = p.K / 64;
-                    const uint8_t* mp = (w == 0 ? p.meta0 : p.meta1) + ((size_t)n * g64 + (size_t)(t.ks * p.kchunks + kc) * 4) * 2;
+                    const uint8_t* mp = (mat == 0 ? p.meta0 : p.meta1) + ((size_t)n * g64 + (size_t)(t.ks * p.kchunks + kc) * 4) * 2;
                     const uint2 sc = __ldg(reinterpret_cast<const uint2*>(mp));
                     const uint2 bi = __ldg(reinterpret_cast<const uint2*>(mp + (size_t)p.N * g64 * 2));
                     m[0] = sc.x; m[1] = sc.y; m[2] = bi.x; m[3] = bi.y;
@@ -307,9 +329,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 }
                 ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&raw_full[rs], rph, abort_flag, p.err, 106));
                 if (!ok) break;
-                if (row == 0 && w == 0) QTR(3, (kn >> 2) * 2 + grp, 0);
+                if (row == 0) QTR(3, (kn >> 2) * 2 + grp, 0);
                 uint32_t r[ROW_BYTES / 4];
-                const uint4* src = reinterpret_cast<const uint4*>(sRaw + (rs * NW + w) * RAW_TILE_BYTES + row * ROW_BYTES);
+                const uint4* src = reinterpret_cast<const uint4*>(sRaw + rs * RAW_TILE_BYTES + row * ROW_BYTES);
 #pragma unroll
                 for (int i = 0; i < ROW_BYTES / 16; i++) {
                     // rows of exactly 128 bytes would put every lane on the same banks: those tiles are loaded
@@ -322,19 +344,19 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                     if ((G == STAGES ? (kn + s) % STAGES : (uint32_t)(s % G)) == grp) {
                         uint32_t o[32];
                         Cd::dequant64(r, s, o, meta);
-                        if (row == 0 && w == 0) QTR(4 + grp, kn + s, 0);
+                        if (row == 0) QTR(4 + grp, kn + s, 0);
                         const uint32_t step = kn + s, as = step % STAGES, aph = (step / STAGES) & 1u;
                         ok = __all_sync(0xffffffffu, ok && ptx::mbar_wait<32>(&op_empty[as], aph ^ 1u, abort_flag, p.err, 107));
-                        if (row == 0 && w == 0) QTR(4 + grp, kn + s, 1);
+                        if (row == 0) QTR(4 + grp, kn + s, 1);
                         if (ok) {
-                            uint8_t* dst = sA + (as * NW + w) * A_TILE_BYTES + row_off;
+                            uint8_t* dst = sA + as * A_TILE_BYTES + row_off;
 #pragma unroll
                             for (int c = 0; c < 8; c++)
                                 *reinterpret_cast<uint4*>(dst + ((c ^ xr) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
                             ptx::fence_proxy_async_smem();
                             __syncwarp();                      // every lane's stores are fenced; one arrival per warp
                             if (lane == 0) ptx::mbar_arrive(&op_full[as]);
-                            if (row == 0 && w == 0) QTR(4 + grp, kn + s, 2);
+                            if (row == 0) QTR(4 + grp, kn + s, 2);
                         }
                     }
                 }
@@ -344,7 +366,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 // loads let the next TMA write overtake reads that were still in flight.)
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&raw_empty[rs]);
-                if (row == 0 && w == 0) QTR(3, ((kn >> 2) - 1) * 2 + grp, 3);
+                if (row == 0) QTR(3, ((kn >> 2) - 1) * 2 + grp, 3);
                 if (++rs == p.raw_stages) { rs = 0; rph ^= 1u; }
             }
         }
@@ -352,7 +374,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         // ---------------- epilogue: tensor memory -> fp16 (or fp32 partials) ----------------
         const uint32_t q = warp - C::EPI_WARP0;               // == warp % 4: the TMEM lane quadrant
         const uint32_t et = threadIdx.x - C::EPI_WARP0 * 32;  // 0..127
-        uint32_t it = 0;
+        uint32_t it = 0, xb_i = 0;
         for (uint32_t idx = blockIdx.x; idx < total_tiles; idx += gridDim.x, it++) {
             const Tile t = decode_tile(idx, p);
             const uint32_t buf = it & 1u;
@@ -373,16 +395,54 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             const uint32_t valid = tok0 < p.M ? min(p.T, p.M - tok0) : 0u;     // token columns of this tile that exist
             const int mode = p.k_splits > 1 ? 0 : (p.partial_out ? 1 : (p.residual ? 2 : 3));
             // integer-valued codecs: the row's scale multiplies the fp32 accumulator (before SiLU, before split-K sums)
-            float rsc0 = 1.0f, rsc1 = 1.0f;
-            if (Cd::ROW_SCALE) {
-                rsc0 = n_ok ? __half2float(p.row_scale0[n]) : 0.0f;
-                if (NW == 2) rsc1 = n_ok ? __half2float(p.row_scale1[n]) : 0.0f;
-            }
+            float rsc0 = 1.0f;
+            if (Cd::ROW_SCALE && !p.swiglu) rsc0 = n_ok ? __half2float(p.row_scale0[n]) : 0.0f;
+            if (p.swiglu) {
+                // SwiGLU tile: lanes 0..63 (warps 0,1) hold the gate projection of 64 features, lanes 64..127
+                // (warps 2,3) the up projection of the same features.  Thread et and thread et ^ 64 own the two
+                // halves of one feature: per batch of 16 token columns they swap 8 values through shared memory,
+                // the gate thread finishes columns 0..7, the up thread columns 8..15.
+                const uint32_t nf = t.wt * GATE_ROWS + (q & 1u) * 32u + lane;
+                const bool nf_ok = nf < p.N;
+                const bool up_side = q >= 2u;
+                float rsc = 1.0f;
+                if (Cd::ROW_SCALE) rsc = nf_ok ? __half2float((up_side ? p.row_scale1 : p.row_scale0)[nf]) : 0.0f;
+                __half* dstb = p.Y + nf + (size_t)(tok0 + (up_side ? 8u : 0u)) * p.N;
+                const uint32_t vlim = valid > (up_side ? 8u : 0u) ? valid - (up_side ? 8u : 0u) : 0u;   // columns left from this thread's first
+                for (uint32_t c0 = 0; c0 < p.T; c0 += 16, xb_i++) {
+                    uint32_t v[16];
+                    ptx::tmem_ld_x16(taddr + c0, v);
+                    ptx::tmem_ld_wait();
+                    float f[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) f[j] = Cd::ROW_SCALE ? __uint_as_float(v[j]) * rsc : __uint_as_float(v[j]);
+                    float4* xb = xchg + (xb_i & 1u) * 256u;
+                    // send the half the partner finishes: gate values of columns 8..15, up values of columns 0..7
+                    xb[et] = up_side ? make_float4(f[0], f[1], f[2], f[3]) : make_float4(f[8], f[9], f[10], f[11]);
+                    xb[128 + et] = up_side ? make_float4(f[4], f[5], f[6], f[7]) : make_float4(f[12], f[13], f[14], f[15]);
+                    ptx::bar_sync(2, 128);
+                    const float4 r0 = xb[et ^ 64u], r1 = xb[128 + (et ^ 64u)];
+                    const float rv[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+                    float o8[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) o8[j] = up_side ? silu_mul(rv[j], f[8 + j]) : silu_mul(f[j], rv[j]);
+                    if (nf_ok && c0 < vlim) {
+                        const uint32_t lim = vlim - c0;
+                        __half* dst = dstb + (size_t)c0 * p.N;
+                        if (lim >= 8u) {
+#pragma unroll
+                            for (int j = 0; j < 8; j++) dst[(size_t)j * p.N] = __float2half_rn(o8[j]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; j++) if ((uint32_t)j < lim) dst[(size_t)j * p.N] = __float2half_rn(o8[j]);
+                        }
+                    }
+                }
+            } else
             for (uint32_t c0 = 0; c0 < p.T; c0 += 16) {
-                uint32_t v[16], u[16];
+                uint32_t v[16];
                 if (et == 0 && it == 0) QTR(7, 1 + c0 / 16, 0);
                 ptx::tmem_ld_x16(taddr + c0, v);
-                if (NW == 2) ptx::tmem_ld_x16(taddr + 128 + c0, u);
                 ptx::tmem_ld_wait();
                 if (et == 0 && it == 0) QTR(7, 1 + c0 / 16, 1);
                 float f[16];
@@ -390,7 +450,6 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 for (int j = 0; j < 16; j++) {
                     f[j] = __uint_as_float(v[j]);
                     if (Cd::ROW_SCALE) f[j] *= rsc0;
-                    if (NW == 2) f[j] = silu_mul(f[j], Cd::ROW_SCALE ? __uint_as_float(u[j]) * rsc1 : __uint_as_float(u[j]));
                 }
                 if (mode == 0) {
                     float* dst = ws + (size_t)c0 * W_TILE + q * 32 + lane;
@@ -677,12 +736,13 @@ int sm_count() {
 struct Plan { uint32_t T, n_tok_tiles, n_w_tiles, k_splits, kchunks; };
 
 Plan make_plan(const GemmArgs& a) {
-    const uint32_t tok_max = a.W1 ? 128u : 256u;
+    const uint32_t tok_max = 256u;
     Plan pl;
     pl.n_tok_tiles = (a.M + tok_max - 1) / tok_max;
     uint32_t per = (a.M + pl.n_tok_tiles - 1) / pl.n_tok_tiles;
     pl.T = (per + 15u) & ~15u;
-    pl.n_w_tiles = (a.N + W_TILE - 1) / W_TILE;
+    const uint32_t rows_per_tile = a.W1 ? GATE_ROWS : W_TILE;    // output features per tile
+    pl.n_w_tiles = (a.N + rows_per_tile - 1) / rows_per_tile;
     const uint32_t chunks = a.K / KCHUNK;
     pl.k_splits = 1;
     if (!a.W1) {
@@ -699,9 +759,9 @@ Plan make_plan(const GemmArgs& a) {
     return pl;
 }
 
-template <int FMT, int NW>
+template <int FMT>
 cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t stream) {
-    using C = Cfg<NW, FMT>;
+    using C = Cfg<FMT>;
     const Plan pl = make_plan(a);
     const int rb = cdc::Codec<FMT>::ROW_BYTES;
     const uint64_t w_row_bytes = (uint64_t)(a.K / KCHUNK) * rb;
@@ -710,15 +770,17 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
                      CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
     const CUtensorMapSwizzle wsw = cdc::Codec<FMT>::RAW_SWIZZLE_128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;
-    if (!make_map_2d(&tmW0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.W0, w_row_bytes, a.N, w_row_bytes, rb, W_TILE, wsw))
+    const uint32_t box_rows = a.W1 ? GATE_ROWS : W_TILE;
+    if (!make_map_2d(&tmW0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.W0, w_row_bytes, a.N, w_row_bytes, rb, box_rows, wsw))
         return cudaErrorInvalidValue;
-    if (!make_map_2d(&tmW1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.W1 ? a.W1 : a.W0, w_row_bytes, a.N, w_row_bytes, rb, W_TILE, wsw))
+    if (!make_map_2d(&tmW1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.W1 ? a.W1 : a.W0, w_row_bytes, a.N, w_row_bytes, rb, box_rows, wsw))
         return cudaErrorInvalidValue;
 
     Params p;
     p.M = a.M; p.N = a.N; p.K = a.K;
     p.T = pl.T; p.n_tok_tiles = pl.n_tok_tiles; p.n_w_tiles = pl.n_w_tiles; p.k_splits = pl.k_splits; p.kchunks = pl.kchunks;
-    p.raw_stages = raw_stages_for<FMT, NW>(pl.T); p.b_stage_bytes = pl.T * 128u;
+    p.swiglu = a.W1 ? 1u : 0u;
+    p.raw_stages = raw_stages_for<FMT>(pl.T, a.W1 != nullptr); p.b_stage_bytes = pl.T * 128u;
     p.Y = (__half*)a.Y; p.residual = (const __half*)a.residual; p.partial_out = a.partial_out;
     p.layout = (uint32_t)a.layout; p.H = a.H; p.D = a.D ? a.D : 1;
     p.ws_partial = ws.partial; p.ws_counters = ws.counters; p.err = ws.err;
@@ -738,27 +800,26 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     int dev = 0;
     cudaGetDevice(&dev);
     if (attr_device != dev) {
-        cudaError_t e = cudaFuncSetAttribute(qgemm_kernel<FMT, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(qgemm_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         attr_device = dev;
     }
     const uint32_t total = pl.n_tok_tiles * pl.n_w_tiles * pl.k_splits;
     const uint32_t grid = total < (uint32_t)sm_count() ? total : (uint32_t)sm_count();
-    qgemm_kernel<FMT, NW><<<grid, C::THREADS, smem, stream>>>(tmX, tmW0, tmW1, p);
+    qgemm_kernel<FMT><<<grid, C::THREADS, smem, stream>>>(tmX, tmW0, tmW1, p);
     return cudaGetLastError();
 }
 
-template <int NW>
 cudaError_t dispatch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t s) {
     switch (a.format) {
-        case QUANT_Q4_0: return launch_fast<QUANT_Q4_0, NW>(a, ws, s);
-        case QUANT_MLX_4BIT: return launch_fast<QUANT_MLX_4BIT, NW>(a, ws, s);
-        case QUANT_Q4_K: return launch_fast<QUANT_Q4_K, NW>(a, ws, s);
-        case QUANT_TERNARY_1_58: return launch_fast<QUANT_TERNARY_1_58, NW>(a, ws, s);
-        case QUANT_VAR_RATE_AFFINE: return launch_fast<QUANT_VAR_RATE_AFFINE, NW>(a, ws, s);
-        case QUANT_EXL3: return launch_fast<QUANT_EXL3, NW>(a, ws, s);
-        case QUANT_MLX_4BIT_G64: return launch_fast<QUANT_MLX_4BIT_G64, NW>(a, ws, s);
-        case QUANT_TERNARY_ROW: return launch_fast<QUANT_TERNARY_ROW, NW>(a, ws, s);
+        case QUANT_Q4_0: return launch_fast<QUANT_Q4_0>(a, ws, s);
+        case QUANT_MLX_4BIT: return launch_fast<QUANT_MLX_4BIT>(a, ws, s);
+        case QUANT_Q4_K: return launch_fast<QUANT_Q4_K>(a, ws, s);
+        case QUANT_TERNARY_1_58: return launch_fast<QUANT_TERNARY_1_58>(a, ws, s);
+        case QUANT_VAR_RATE_AFFINE: return launch_fast<QUANT_VAR_RATE_AFFINE>(a, ws, s);
+        case QUANT_EXL3: return launch_fast<QUANT_EXL3>(a, ws, s);
+        case QUANT_MLX_4BIT_G64: return launch_fast<QUANT_MLX_4BIT_G64>(a, ws, s);
+        case QUANT_TERNARY_ROW: return launch_fast<QUANT_TERNARY_ROW>(a, ws, s);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -785,7 +846,7 @@ size_t workspace_floats(const GemmArgs& a) {
 
 cudaError_t launch(const GemmArgs& a, const Workspace& ws, cudaStream_t stream) {
     g_last_launches = 1;
-    if (fast_path_ok(a)) return a.W1 ? dispatch_fast<2>(a, ws, stream) : dispatch_fast<1>(a, ws, stream);
+    if (fast_path_ok(a)) return dispatch_fast(a, ws, stream);
     Params p;
     memset(&p, 0, sizeof(p));
     p.M = a.M; p.N = a.N; p.K = a.K;
