@@ -630,7 +630,7 @@ int b200_bridge_quantize_kv_q8_0(void* src, size_t src_bytes, void* dst, size_t 
     if (rc) return rc;
     if (attn::launch_quantize(s, d, n_elements, g.stream) != cudaSuccess) return -6;
     g.launches++;
-    if (host_dst) { cudaMemcpyAsync(host_dst, d, out_bytes, cudaMemcpyDeviceToHost, g.stream); g.d2h_bytes += out_bytes; }
+    if (host_dst && copy_back(host_dst, d, out_bytes) != 0) return -5;
     return 0;
 }
 
@@ -649,7 +649,7 @@ int b200_bridge_dequantize_q8_0(void* src, size_t src_bytes, void* dst, size_t d
     if (rc) return rc;
     if (attn::launch_dequantize(s, d, n_elements, g.stream) != cudaSuccess) return -6;
     g.launches++;
-    if (host_dst) { cudaMemcpyAsync(host_dst, d, n_elements * 2, cudaMemcpyDeviceToHost, g.stream); g.d2h_bytes += n_elements * 2; }
+    if (host_dst && copy_back(host_dst, d, n_elements * 2) != 0) return -5;
     return 0;
 }
 
@@ -682,7 +682,7 @@ int b200_bridge_dispatch_attention_q8kv(void* Q, void* K, void* V, void* O, uint
     p.out_tokens_major = out_tokens_major; p.kv_fp16 = kv_fp16;
     if (attn::launch_attention(p, D, g.stream) != cudaSuccess) { set_error("attention launch failed"); return -6; }
     g.launches++;
-    if (host_dst) { cudaMemcpyAsync(host_dst, p.O, q_bytes, cudaMemcpyDeviceToHost, g.stream); g.d2h_bytes += q_bytes; }
+    if (host_dst && copy_back(host_dst, p.O, q_bytes) != 0) return -5;
     return 0;
 }
 

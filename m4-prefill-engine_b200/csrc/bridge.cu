@@ -1,6 +1,6 @@
 // C ABI of the bridge (include/b200_bridge.h): argument validation in the reference's order
 // (core/bridge/m4_mlx_bridge.mm:194-230), host/device pointer resolution, staging, and dispatch
-// onto the kernels.  One internal stream; a mutex guards all state, as in the reference
+// onto the kernels.  One compute stream plus two copy streams for host buffers; a mutex guards all state, as in the reference
 // (core/bridge/m4_mlx_bridge.mm:20,84,284-287).
 #include <cuda_runtime.h>
 
@@ -47,6 +47,9 @@ const void* resolve_in(const void* ptr, size_t bytes, DevBuf& stage, bool weight
         auto it = g.registered.find(ptr);
         if (it != g.registered.end() && it->second.bytes >= bytes) return it->second.dev;
     }
+    // a projection's copy back may still be writing the host buffer this call reads
+    for (StageSlot& sl : g.slots)
+        if (sl.out_pending) cudaStreamWaitEvent(g.stream, sl.ev_out, 0);
     if (!stage.ensure(bytes)) { *rc = -5; return nullptr; }
     if (cudaMemcpyAsync(stage.p, ptr, bytes, cudaMemcpyHostToDevice, g.stream) != cudaSuccess) {
         cudaGetLastError(); *rc = -5; return nullptr;
@@ -63,6 +66,44 @@ void* resolve_out(void* ptr, size_t bytes, DevBuf& stage, void** host_dst, int* 
     *host_dst = ptr;
     return stage.p;
 }
+
+int copy_back(void* host_dst, const void* dev_src, size_t bytes) {
+    if (cudaMemcpyAsync(host_dst, dev_src, bytes, cudaMemcpyDeviceToHost, g.stream) != cudaSuccess) { cudaGetLastError(); return -5; }
+    g.d2h_bytes += bytes;
+    cudaEventRecord(g.ev_main_d2h, g.stream);
+    g.main_d2h_pending = true;
+    return 0;
+}
+
+namespace {
+
+inline bool overlaps(const void* a, size_t an, const char* b, size_t bn) {
+    const char* ac = static_cast<const char*>(a);
+    return b && ac < b + bn && b < ac + an;
+}
+
+// Host input of a pipelined projection call: staged on the copy-in stream into the slot's buffer.
+const void* stage_in(const void* ptr, size_t bytes, StageSlot& sl, DevBuf& buf, bool weights, bool* staged, int* rc) {
+    if (is_device_ptr(ptr)) return ptr;
+    if (weights) {
+        auto it = g.registered.find(ptr);
+        if (it != g.registered.end() && it->second.bytes >= bytes) return it->second.dev;
+    }
+    // ordering through host memory: an earlier call's result may still be on its way into this buffer
+    for (StageSlot& o : g.slots)
+        if (o.out_pending && overlaps(ptr, bytes, o.out_ptr, o.out_bytes)) cudaStreamWaitEvent(g.stream_in, o.ev_out, 0);
+    if (!*staged) {     // first upload of this call: the slot's buffers must be free, earlier host results complete
+        if (sl.used) cudaStreamWaitEvent(g.stream_in, sl.ev_kernel, 0);
+        if (g.main_d2h_pending) cudaStreamWaitEvent(g.stream_in, g.ev_main_d2h, 0);
+    }
+    if (!buf.ensure(bytes)) { *rc = -5; return nullptr; }
+    if (cudaMemcpyAsync(buf.p, ptr, bytes, cudaMemcpyHostToDevice, g.stream_in) != cudaSuccess) { cudaGetLastError(); *rc = -5; return nullptr; }
+    g.h2d_bytes += bytes;
+    *staged = true;
+    return buf.p;
+}
+
+}  // namespace
 
 bool ensure_workspace(size_t floats) {
     if (floats == 0) return true;
@@ -97,30 +138,62 @@ int run_gemm(void* X, size_t Xb, void* W0, void* W1, size_t Wb, void* Y, size_t 
     qg::GemmArgs a;
     memset(&a, 0, sizeof(a));
     a.format = format;
-    a.X = resolve_in(X, x_bytes, g.stage_x, false, &rc);
+    // Host buffers go through one of two staging sets, uploads on the copy-in stream, the download on the
+    // copy-out stream; consecutive calls alternate sets, so call i+1 uploads while call i computes and downloads.
+    // The slot's buffers are reused two calls later: its uploads wait for the kernel that last read them, its
+    // kernel waits for the download that last read its output buffer.
+    StageSlot& sl = g.slots[g.slot_seq & 1u];
+    bool staged_in = false;
+    a.X = stage_in(X, x_bytes, sl, sl.x, false, &staged_in, &rc);
     if (rc) return rc;
-    a.W0 = resolve_in(W0, w_bytes, g.stage_w0, true, &rc);
+    a.W0 = stage_in(W0, w_bytes, sl, sl.w0, true, &staged_in, &rc);
     if (rc) return rc;
-    if (W1) { a.W1 = resolve_in(W1, w_bytes, g.stage_w1, true, &rc); if (rc) return rc; }
-    if (residual) { a.residual = resolve_in(residual, y_bytes, g.stage_res, false, &rc); if (rc) return rc; }
+    if (W1) { a.W1 = stage_in(W1, w_bytes, sl, sl.w1, true, &staged_in, &rc); if (rc) return rc; }
+    if (residual) { a.residual = stage_in(residual, y_bytes, sl, sl.res, false, &staged_in, &rc); if (rc) return rc; }
     void* host_dst = nullptr;
-    a.Y = resolve_out(Y, y_bytes, g.stage_y, &host_dst, &rc);
-    if (rc) return rc;
+    if (is_device_ptr(Y)) {
+        a.Y = Y;
+    } else {
+        if (!sl.y.ensure(y_bytes)) return -5;
+        a.Y = sl.y.p;
+        host_dst = Y;
+    }
     a.M = M; a.N = N; a.K = K; a.layout = layout; a.H = H; a.D = D;
     a.force_generic = g.force_generic;
     (void)Xb; (void)Wb; (void)Yb;
     if (!ensure_workspace(qg::workspace_floats(a))) return -5;
+    if (staged_in) {
+        cudaEventRecord(sl.ev_in, g.stream_in);
+        cudaStreamWaitEvent(g.stream, sl.ev_in, 0);
+    }
+    if (host_dst && sl.out_pending) cudaStreamWaitEvent(g.stream, sl.ev_out, 0);
     qg::Workspace ws;
     ws.partial = (float*)g.ws_partial.p; ws.partial_floats = g.ws_partial.cap / sizeof(float);
     ws.counters = g.counters; ws.err = g.err_word;
     cudaError_t e = qg::launch(a, ws, g.stream);
     if (e != cudaSuccess) { set_error(std::string("kernel launch failed: ") + cudaGetErrorString(e)); return -6; }
     g.launches += (uint64_t)qg::last_launch_count();
+    if (staged_in || host_dst) {
+        cudaEventRecord(sl.ev_kernel, g.stream);
+        sl.used = true;
+        g.slot_seq++;
+    }
     if (host_dst) {
-        if (cudaMemcpyAsync(host_dst, a.Y, y_bytes, cudaMemcpyDeviceToHost, g.stream) != cudaSuccess) { cudaGetLastError(); return -5; }
+        cudaStreamWaitEvent(g.stream_out, sl.ev_kernel, 0);
+        if (cudaMemcpyAsync(host_dst, a.Y, y_bytes, cudaMemcpyDeviceToHost, g.stream_out) != cudaSuccess) { cudaGetLastError(); return -5; }
+        cudaEventRecord(sl.ev_out, g.stream_out);
+        sl.out_pending = true; sl.out_ptr = static_cast<const char*>(host_dst); sl.out_bytes = y_bytes;
         g.d2h_bytes += y_bytes;
     }
     return 0;
+}
+
+// Everything the bridge has enqueued, on all three streams (caller holds no lock-protected references).
+cudaError_t sync_all_streams(cudaStream_t main, cudaStream_t in, cudaStream_t out) {
+    cudaError_t e = cudaStreamSynchronize(in);
+    cudaError_t e2 = cudaStreamSynchronize(main);
+    cudaError_t e3 = cudaStreamSynchronize(out);
+    return e != cudaSuccess ? e : (e2 != cudaSuccess ? e2 : e3);
 }
 
 }  // namespace bridge
@@ -145,7 +218,18 @@ bool m4_bridge_init(const char*) {
         set_error("kernels are built for sm_100a only; found sm_" + std::to_string(prop.major) + std::to_string(prop.minor));
         return false;
     }
-    if (cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&g.stream_in, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&g.stream_out, cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); return false; }
+    bool ev_ok = cudaEventCreateWithFlags(&g.ev_main_d2h, cudaEventDisableTiming) == cudaSuccess;
+    for (StageSlot& sl : g.slots) {
+        ev_ok = ev_ok && cudaEventCreateWithFlags(&sl.ev_in, cudaEventDisableTiming) == cudaSuccess &&
+                cudaEventCreateWithFlags(&sl.ev_kernel, cudaEventDisableTiming) == cudaSuccess &&
+                cudaEventCreateWithFlags(&sl.ev_out, cudaEventDisableTiming) == cudaSuccess;
+        sl.used = false; sl.out_pending = false; sl.out_ptr = nullptr; sl.out_bytes = 0;
+    }
+    if (!ev_ok) { cudaGetLastError(); return false; }
+    g.slot_seq = 0; g.main_d2h_pending = false;
     if (cudaMalloc(&g.counters, 4096 * sizeof(uint32_t) + 64) != cudaSuccess) { cudaGetLastError(); return false; }
     cudaMemsetAsync(g.counters, 0, 4096 * sizeof(uint32_t) + 64, g.stream);
     g.err_word = reinterpret_cast<int*>(g.counters + 4096);
@@ -220,20 +304,25 @@ int b200_bridge_unregister_weights(const void* host_ptr) {
     std::lock_guard<std::mutex> lock(g.mu);
     auto it = g.registered.find(host_ptr);
     if (it == g.registered.end()) return -2;
-    cudaStreamSynchronize(g.stream);
+    sync_all_streams(g.stream, g.stream_in, g.stream_out);
     cudaFree(it->second.dev);
     g.registered.erase(it);
     return 0;
 }
 
 void m4_bridge_synchronize(void) {
-    cudaStream_t s;
+    cudaStream_t s, si, so;
     {
         std::lock_guard<std::mutex> lock(g.mu);
         if (!g.initialized) return;
-        s = g.stream;
+        s = g.stream; si = g.stream_in; so = g.stream_out;
     }
-    cudaError_t e = cudaStreamSynchronize(s);
+    cudaError_t e = sync_all_streams(s, si, so);
+    {
+        std::lock_guard<std::mutex> lock(g.mu);
+        for (StageSlot& sl : g.slots) { sl.out_pending = false; sl.out_ptr = nullptr; sl.out_bytes = 0; }
+        g.main_d2h_pending = false;
+    }
     if (e != cudaSuccess) {
         std::lock_guard<std::mutex> lock(g.mu);
         set_error(std::string("stream error: ") + cudaGetErrorString(e));
@@ -255,7 +344,14 @@ bool m4_bridge_is_initialized(void) {
 void m4_bridge_shutdown(void) {
     std::lock_guard<std::mutex> lock(g.mu);
     if (!g.initialized) return;
-    cudaStreamSynchronize(g.stream);
+    sync_all_streams(g.stream, g.stream_in, g.stream_out);
+    for (StageSlot& sl : g.slots) {
+        sl.x.release(); sl.w0.release(); sl.w1.release(); sl.res.release(); sl.y.release();
+        cudaEventDestroy(sl.ev_in); cudaEventDestroy(sl.ev_kernel); cudaEventDestroy(sl.ev_out);
+        sl.ev_in = sl.ev_kernel = sl.ev_out = nullptr; sl.used = false; sl.out_pending = false;
+    }
+    cudaEventDestroy(g.ev_main_d2h); g.ev_main_d2h = nullptr;
+    cudaStreamDestroy(g.stream_in); cudaStreamDestroy(g.stream_out); g.stream_in = g.stream_out = nullptr;
     g.stage_x.release(); g.stage_w0.release(); g.stage_w1.release(); g.stage_y.release(); g.stage_res.release();
     g.stage_aux0.release(); g.stage_aux1.release(); g.stage_aux2.release();
     g.ws_partial.release();

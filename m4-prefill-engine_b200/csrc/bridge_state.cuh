@@ -18,11 +18,29 @@ struct DevBuf {                 // grow-only device block
 
 struct Registered { void* dev; size_t bytes; };
 
+// One of two staging sets of the projection entry points.  A call that is handed host buffers copies its
+// inputs on the copy-in stream, runs its kernel on the main stream and copies its result back on the copy-out
+// stream, so the upload of call i+1 and the download of call i overlap (they use different copy engines).
+struct StageSlot {
+    DevBuf x, w0, w1, res, y;
+    cudaEvent_t ev_in = nullptr, ev_kernel = nullptr, ev_out = nullptr;
+    bool used = false;               // ev_kernel has been recorded at least once
+    bool out_pending = false;        // a copy back from y has been enqueued since the last synchronize
+    const char* out_ptr = nullptr;   // host range that copy writes
+    size_t out_bytes = 0;
+};
+
 struct State {
     std::mutex mu;
     bool initialized = false;
     int device = 0;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;       // kernels (and the staging copies of everything but the projections)
+    cudaStream_t stream_in = nullptr;    // host -> device copies of the projection entry points
+    cudaStream_t stream_out = nullptr;   // device -> host copies of the projection entry points
+    StageSlot slots[2];
+    uint64_t slot_seq = 0;
+    cudaEvent_t ev_main_d2h = nullptr;   // last copy back issued on the main stream by another entry point
+    bool main_d2h_pending = false;
     DevBuf stage_x, stage_w0, stage_w1, stage_y, stage_res, stage_aux0, stage_aux1, stage_aux2;
     DevBuf ws_partial;          // split-K partial tiles
     uint32_t* counters = nullptr;  // 4096 tile counters (kept zero between launches) + error word
@@ -39,5 +57,7 @@ void set_error(const std::string& s);
 bool is_device_ptr(const void* ptr);
 const void* resolve_in(const void* ptr, size_t bytes, DevBuf& stage, bool weights, int* rc);
 void* resolve_out(void* ptr, size_t bytes, DevBuf& stage, void** host_dst, int* rc);
+// Device -> host copy of a staged result on the main stream (entry points other than the projections).
+int copy_back(void* host_dst, const void* dev_src, size_t bytes);
 
 }  // namespace bridge

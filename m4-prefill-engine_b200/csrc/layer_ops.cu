@@ -129,7 +129,7 @@ int b200_bridge_rmsnorm(void* X, void* weight, void* Y, uint32_t M, uint32_t K, 
     if (rc) return rc;
     if (lops::rmsnorm(x, w, y, M, K, eps, g.stream) != cudaSuccess) return -6;
     g.launches++;
-    if (host_dst) { cudaMemcpyAsync(host_dst, y, bytes, cudaMemcpyDeviceToHost, g.stream); g.d2h_bytes += bytes; }
+    if (host_dst && copy_back(host_dst, y, bytes) != 0) return -5;
     return 0;
 }
 
@@ -150,9 +150,7 @@ int b200_bridge_rope(void* X, uint32_t H, uint32_t M, uint32_t D, float theta, u
     if (rc) return rc;
     if (lops::rope(x, H, M, D, theta, pos0, g.stream) != cudaSuccess) return -6;
     g.launches++;
-    cudaMemcpyAsync(X, x, bytes, cudaMemcpyDeviceToHost, g.stream);
-    g.d2h_bytes += bytes;
-    return 0;
+    return copy_back(X, x, bytes);
 }
 
 }  // extern "C"

@@ -272,9 +272,10 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 if (lane == 0) QTR(2, mtr, 0);
                 // (no tcgen05 fence here: the stage was written by TMA and by generic stores that were
                 // followed by fence.proxy.async; the mbarrier acquire orders them before the MMA's reads)
-                ok = ptx::mbar_wait(&op_full[st], sph, abort_flag, p.err, 104);
+                // (the vote keeps the warp converged for elect.sync even if a wait gives up)
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait(&op_full[st], sph, abort_flag, p.err, 104));
                 if (!ok) break;
-                if (lane == 0) {
+                if (ptx::elect_one()) {
                     QTR(2, mtr, 2);
                     const uint64_t bdesc = desc_hi | (uint64_t)(b_lo0 + st * (p.b_stage_bytes >> 4));
                     const uint64_t adesc = desc_hi | (uint64_t)(a_lo0 + st * (A_TILE_BYTES >> 4));
@@ -288,7 +289,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 __syncwarp();
                 if (++st == STAGES) { st = 0; sph ^= 1u; }
             }
-            if (ok && lane == 0) { ptx::umma_commit(&tm_full[buf]); QTRC(2, 200u + it, 1); }
+            if (ok && ptx::elect_one()) { ptx::umma_commit(&tm_full[buf]); QTRC(2, 200u + it, 1); }   // same lane as the MMAs
             __syncwarp();
         }
     } else if (pre_epi && wq != 2u && uw < (uint32_t)C::DQ_WARPS) {

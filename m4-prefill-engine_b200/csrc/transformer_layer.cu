@@ -260,7 +260,7 @@ int b200_layer_forward(void* layer, const void* X_in, const void* W_q, const voi
     h->layer->forward(g.stream, x, w[0], w[1], w[2], w[3], w[4], w[5], w[6], y);
     if (h->layer->last_status()) return h->layer->last_status();
     g.launches += h->layer->kernels_per_forward();
-    if (host_dst) { cudaMemcpyAsync(host_dst, y, bytes, cudaMemcpyDeviceToHost, g.stream); g.d2h_bytes += bytes; }
+    if (host_dst && copy_back(host_dst, y, bytes) != 0) return -5;
     return 0;
 }
 

@@ -154,6 +154,41 @@ def test_host_pointers_and_gemv(bridge):
     assert np.abs(y.cpu().numpy().astype(np.float64) - o.gemm_f64(o.Q4_0, X[:1], W, N)[0]).max() <= TOL
 
 
+def test_host_buffers_pipeline_in_order(bridge):
+    """Host buffers are staged on separate copy streams (upload of call i+1 overlaps download of call i); calls
+    that hand results to each other through host memory without a synchronize must still see them in order."""
+    K = N = 512
+    M = 64
+    g = o.RefLcg(9)
+    W = g.weights(o.Q4_0, K, N)
+    Wd = dev(W)
+    Xs = [(g.activations(M, K).astype(np.float32) * 0.5).astype(np.float16) for _ in range(6)]
+    want = [run_gemm(bridge, o.Q4_0, x, W, N) for x in Xs]
+    # 1. a burst of independent calls on alternating pinned buffers, one synchronize at the end
+    Xp = [torch.from_numpy(x).pin_memory() for x in Xs]
+    Yp = [torch.zeros(M, N, dtype=torch.float16).pin_memory() for _ in Xs]
+    for x, y in zip(Xp, Yp):
+        bridge.dispatch_gemm(x, Wd, y, o.Q4_0, M, K, N)
+    bridge.synchronize()
+    for y, w in zip(Yp, want):
+        assert np.array_equal(y.numpy().view(np.uint16), w.view(np.uint16))
+    # 2. a chain through host memory: the second call reads the buffer the first one writes
+    h1 = torch.zeros(M, N, dtype=torch.float16).pin_memory()
+    h2 = torch.zeros(M, N, dtype=torch.float16).pin_memory()
+    for rep in range(3):
+        bridge.dispatch_gemm(Xp[rep], Wd, h1, o.Q4_0, M, K, N)
+        bridge.dispatch_gemm(h1, Wd, h2, o.Q4_0, M, K, N)
+        bridge.synchronize()
+        assert np.array_equal(h1.numpy().view(np.uint16), want[rep].view(np.uint16))
+        chained = run_gemm(bridge, o.Q4_0, want[rep], W, N)
+        assert np.array_equal(h2.numpy().view(np.uint16), chained.view(np.uint16))
+    # 3. the same buffer reused as output by back-to-back calls: the last writer wins
+    for x in Xp[:4]:
+        bridge.dispatch_gemm(x, Wd, h1, o.Q4_0, M, K, N)
+    bridge.synchronize()
+    assert np.array_equal(h1.numpy().view(np.uint16), want[3].view(np.uint16))
+
+
 def test_residual_epilogue(bridge):
     M, K, N = 130, 512, 256
     g = o.RefLcg(4)
