@@ -68,7 +68,8 @@ constexpr int KSTEP = 64;       // fp16 elements per 128-byte swizzled row
 constexpr int KCHUNK = 256;     // K elements per packed-weight stage
 constexpr int MAX_RAW_STAGES = 6;   // packed-weight ring depth is chosen per launch from the shared memory left over
 constexpr int SMEM_BYTES = 226 * 1024;  // dynamic shared memory of every launch
-constexpr int STAGES = 3;       // operand ring: one stage = unpacked weight tile(s) + activation tile
+constexpr int STAGES = 3;       // ring of unpacked weight tiles (one 64-element K step each)
+constexpr int MAX_B_STAGES = 4;  // ring of activation tiles: deeper, so a tile is requested three steps before its MMA
 constexpr int A_TILE_BYTES = W_TILE * 128;
 constexpr int TMEM_COLS = 512;
 constexpr int ACC_STRIDE = 256; // tensor-memory columns per accumulator buffer
@@ -102,7 +103,7 @@ struct Params {
     uint32_t M, N, K;
     uint32_t T;                  // tokens per tile (multiple of 16)
     uint32_t n_tok_tiles, n_w_tiles, k_splits, kchunks;   // kchunks: 256-element chunks per split
-    uint32_t raw_stages, b_stage_bytes;                   // ring depth of packed weights; bytes of one activation stage (T*128)
+    uint32_t raw_stages, b_stage_bytes, b_stages;         // ring depth of packed weights; bytes of one activation stage (T*128); activation ring depth
     __half* Y;
     const __half* residual;
     float* partial_out;
@@ -119,10 +120,17 @@ struct Params {
 };
 
 // Packed-weight stages that fit beside the operand ring for a given activation-tile height.
-template <int FMT> inline uint32_t raw_stages_for(uint32_t T, bool swiglu) {
+template <int FMT> inline long raw_stages_fit(uint32_t T, bool swiglu, uint32_t b_stages) {
     const long avail = (long)SMEM_BYTES - 1024 /*alignment slack*/ - 512 /*barriers*/ - (swiglu ? XCHG_BYTES : 0) -
-                       (long)STAGES * A_TILE_BYTES - (long)STAGES * T * 128;
-    long n = avail / ((long)cdc::Codec<FMT>::ROW_BYTES * W_TILE);
+                       (long)STAGES * A_TILE_BYTES - (long)b_stages * T * 128;
+    return avail / ((long)cdc::Codec<FMT>::ROW_BYTES * W_TILE);
+}
+// Activation ring depth: four stages when two packed-weight stages still fit beside them, else three.
+template <int FMT> inline uint32_t b_stages_for(uint32_t T, bool swiglu) {
+    return raw_stages_fit<FMT>(T, swiglu, MAX_B_STAGES) >= 2 ? MAX_B_STAGES : STAGES;
+}
+template <int FMT> inline uint32_t raw_stages_for(uint32_t T, bool swiglu) {
+    const long n = raw_stages_fit<FMT>(T, swiglu, b_stages_for<FMT>(T, swiglu));
     return (uint32_t)(n < 2 ? 2 : (n > MAX_RAW_STAGES ? MAX_RAW_STAGES : n));
 }
 
@@ -157,17 +165,20 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     QCTA(0);
     const uint32_t pad = (1024u - (ptx::smem_u32(smem_dyn) & 1023u)) & 1023u;
     uint8_t* sB = smem_dyn + pad;
-    uint8_t* sA = sB + STAGES * p.b_stage_bytes;
+    uint8_t* sA = sB + p.b_stages * p.b_stage_bytes;
     uint8_t* sRaw = sA + STAGES * A_TILE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + p.raw_stages * RAW_TILE_BYTES);
     uint64_t* raw_full = bars;
     uint64_t* raw_empty = raw_full + MAX_RAW_STAGES;
-    // One full/empty pair per operand stage: "full" collects the unpack threads' arrivals plus the
-    // activation TMA's byte count, "empty" is one tcgen05.commit -- so the MMA thread does one wait
-    // and one commit per 64-element step.
-    uint64_t* op_full = raw_empty + MAX_RAW_STAGES;
-    uint64_t* op_empty = op_full + STAGES;
-    uint64_t* tm_full = op_empty + STAGES;
+    // Two operand rings with their own full/empty pairs.  The activation ring is one stage deeper than the
+    // unpacked-weight ring: an activation tile comes from L2 / HBM and has to be requested about three steps
+    // before its MMA for the load latency to stay off the critical path when the inputs are not L2-resident
+    // (with a shared three-deep ring the request could only go out two steps ahead).
+    uint64_t* a_full = raw_empty + MAX_RAW_STAGES;      // unpacked weight tile published (one arrival per unpack warp)
+    uint64_t* a_empty = a_full + STAGES;                // ... consumed (one tcgen05.commit)
+    uint64_t* b_full = a_empty + STAGES;                // activation tile landed (producer's arrival + TMA byte count)
+    uint64_t* b_empty = b_full + MAX_B_STAGES;          // ... consumed (one tcgen05.commit)
+    uint64_t* tm_full = b_empty + MAX_B_STAGES;
     uint64_t* tm_empty = tm_full + 2;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tm_empty + 2);
     volatile uint32_t* abort_flag = tmem_holder + 1;
@@ -180,7 +191,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < MAX_RAW_STAGES; i++) { ptx::mbar_init(&raw_full[i], 1); ptx::mbar_init(&raw_empty[i], C::DQ_THREADS / 32); }
-        for (int i = 0; i < STAGES; i++) { ptx::mbar_init(&op_full[i], C::FILL_THREADS / 32 + 1); ptx::mbar_init(&op_empty[i], 1); }
+        for (int i = 0; i < STAGES; i++) { ptx::mbar_init(&a_full[i], C::FILL_THREADS / 32); ptx::mbar_init(&a_empty[i], 1); }
+        for (int i = 0; i < MAX_B_STAGES; i++) { ptx::mbar_init(&b_full[i], 1); ptx::mbar_init(&b_empty[i], 1); }
         for (int i = 0; i < 2; i++) { ptx::mbar_init(&tm_full[i], 1); ptx::mbar_init(&tm_empty[i], 4); }
         *abort_flag = 0u;
         *last_flag = 0u;
@@ -241,16 +253,16 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             const Tile t = decode_tile(idx, p);
             const uint32_t k0 = t.ks * p.kchunks * KCHUNK;
             for (uint32_t ks = 0; ks < ksteps; ks++) {
-                ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&op_empty[bs], bph ^ 1u, abort_flag, p.err, 102));
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&b_empty[bs], bph ^ 1u, abort_flag, p.err, 102));
                 if (!ok) break;
                 if (lane == 0) {
                     QTR(1, xtr, 0);
-                    ptx::mbar_arrive_expect_tx(&op_full[bs], p.T * 128u);
-                    ptx::tma_load_2d(sB + bs * p.b_stage_bytes, &tmX, &op_full[bs], (int)(k0 + ks * KSTEP), (int)(t.tt * p.T));
+                    ptx::mbar_arrive_expect_tx(&b_full[bs], p.T * 128u);
+                    ptx::tma_load_2d(sB + bs * p.b_stage_bytes, &tmX, &b_full[bs], (int)(k0 + ks * KSTEP), (int)(t.tt * p.T));
                     QTR(1, xtr, 1); xtr++;
                 }
                 __syncwarp();
-                if (++bs == STAGES) { bs = 0; bph ^= 1u; }
+                if (++bs == p.b_stages) { bs = 0; bph ^= 1u; }
             }
         }
     } else if (warp == 2) {
@@ -259,7 +271,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         // operand descriptors differ between stages only in the 14-bit start-address field
         const uint64_t desc_hi = ptx::umma_desc_k_sw128(0u);
         const uint32_t a_lo0 = (ptx::smem_u32(sA) & 0x3FFFFu) >> 4, b_lo0 = (ptx::smem_u32(sB) & 0x3FFFFu) >> 4;
-        uint32_t st = 0, sph = 0, it = 0, mtr = 0;
+        uint32_t st = 0, sph = 0, bst = 0, bsph = 0, it = 0, mtr = 0;
         (void)mtr;
         bool ok = true;
         for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x, it++) {
@@ -273,21 +285,24 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 // (no tcgen05 fence here: the stage was written by TMA and by generic stores that were
                 // followed by fence.proxy.async; the mbarrier acquire orders them before the MMA's reads)
                 // (the vote keeps the warp converged for elect.sync even if a wait gives up)
-                ok = __all_sync(0xffffffffu, ptx::mbar_wait(&op_full[st], sph, abort_flag, p.err, 104));
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait(&a_full[st], sph, abort_flag, p.err, 104) &&
+                                                 ptx::mbar_wait(&b_full[bst], bsph, abort_flag, p.err, 105));
                 if (!ok) break;
                 if (ptx::elect_one()) {
                     QTR(2, mtr, 2);
-                    const uint64_t bdesc = desc_hi | (uint64_t)(b_lo0 + st * (p.b_stage_bytes >> 4));
+                    const uint64_t bdesc = desc_hi | (uint64_t)(b_lo0 + bst * (p.b_stage_bytes >> 4));
                     const uint64_t adesc = desc_hi | (uint64_t)(a_lo0 + st * (A_TILE_BYTES >> 4));
                     const uint32_t dcol = tmem_base + buf * ACC_STRIDE;
 #pragma unroll
                     for (int kk = 0; kk < KSTEP / 16; kk++)
                         ptx::umma_f16_ss(dcol, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | (uint32_t)kk) != 0u);
-                    ptx::umma_commit(&op_empty[st]);
+                    ptx::umma_commit(&a_empty[st]);
+                    ptx::umma_commit(&b_empty[bst]);
                     QTR(2, mtr, 3); mtr++;
                 }
                 __syncwarp();
                 if (++st == STAGES) { st = 0; sph ^= 1u; }
+                if (++bst == p.b_stages) { bst = 0; bsph ^= 1u; }
             }
             if (ok && ptx::elect_one()) { ptx::umma_commit(&tm_full[buf]); QTRC(2, 200u + it, 1); }   // same lane as the MMAs
             __syncwarp();
@@ -347,7 +362,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                         Cd::dequant64(r, s, o, meta);
                         if (row == 0) QTR(4 + grp, kn + s, 0);
                         const uint32_t step = kn + s, as = step % STAGES, aph = (step / STAGES) & 1u;
-                        ok = __all_sync(0xffffffffu, ok && ptx::mbar_wait<32>(&op_empty[as], aph ^ 1u, abort_flag, p.err, 107));
+                        ok = __all_sync(0xffffffffu, ok && ptx::mbar_wait<32>(&a_empty[as], aph ^ 1u, abort_flag, p.err, 107));
                         if (row == 0) QTR(4 + grp, kn + s, 1);
                         if (ok) {
                             uint8_t* dst = sA + as * A_TILE_BYTES + row_off;
@@ -356,7 +371,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                                 *reinterpret_cast<uint4*>(dst + ((c ^ xr) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
                             ptx::fence_proxy_async_smem();
                             __syncwarp();                      // every lane's stores are fenced; one arrival per warp
-                            if (lane == 0) ptx::mbar_arrive(&op_full[as]);
+                            if (lane == 0) ptx::mbar_arrive(&a_full[as]);
                             if (row == 0) QTR(4 + grp, kn + s, 2);
                         }
                     }
@@ -782,6 +797,7 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     p.T = pl.T; p.n_tok_tiles = pl.n_tok_tiles; p.n_w_tiles = pl.n_w_tiles; p.k_splits = pl.k_splits; p.kchunks = pl.kchunks;
     p.swiglu = a.W1 ? 1u : 0u;
     p.raw_stages = raw_stages_for<FMT>(pl.T, a.W1 != nullptr); p.b_stage_bytes = pl.T * 128u;
+    p.b_stages = b_stages_for<FMT>(pl.T, a.W1 != nullptr);
     p.Y = (__half*)a.Y; p.residual = (const __half*)a.residual; p.partial_out = a.partial_out;
     p.layout = (uint32_t)a.layout; p.H = a.H; p.D = a.D ? a.D : 1;
     p.ws_partial = ws.partial; p.ws_counters = ws.counters; p.err = ws.err;
