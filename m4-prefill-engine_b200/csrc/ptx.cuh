@@ -163,6 +163,12 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// Programmatic dependent launch.  launch_dependents lets the next kernel in the stream (if it was launched with
+// the programmatic-serialization attribute) begin its prologue while this grid is still running; grid_dependency_wait
+// blocks until the preceding grid has completed and its memory is visible, and is a no-op without such a launch.
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // named barrier among a subset of warps
 __device__ __forceinline__ void bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

@@ -152,6 +152,63 @@ __device__ __forceinline__ size_t out_index(const Params& p, uint32_t tok, uint3
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
+// Adds the S partial tiles of output tile t (fp32 [S][tiles][T][128] scratch) and writes the result the way the
+// launch asked for: fp16 Y (either layout, optional residual) or fp32 partial_out.  Thread i of n handles float4
+// column groups i, i + n, ... of the tile's valid token rows, U of them per round.
+template <int S>
+__device__ __forceinline__ void splitk_fixup(const Params& p, const Tile& t, uint32_t tid, uint32_t nthreads) {
+    constexpr int U = 16 / S;
+    const uint32_t tok0 = t.tt * p.T;
+    const uint32_t valid = tok0 < p.M ? min(p.T, p.M - tok0) : 0u;
+    const uint32_t total4 = valid * (W_TILE / 4);
+    const size_t split_stride = (size_t)(p.n_w_tiles * p.n_tok_tiles) * p.T * W_TILE;
+    const float4* base = reinterpret_cast<const float4*>(p.ws_partial + (size_t)t.id * p.T * W_TILE);
+    const bool vec_ok = (p.layout == 1) ? (p.D % 4u == 0u) : (p.N % 4u == 0u);
+    for (uint32_t i0 = tid; i0 < total4; i0 += nthreads * U) {
+        float4 v[U][S];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const uint32_t i = i0 + u * nthreads;
+#pragma unroll
+            for (int sp = 0; sp < S; sp++)
+                v[u][sp] = i < total4 ? __ldcg(base + sp * (split_stride / 4) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const uint32_t i = i0 + u * nthreads;
+            if (i >= total4) continue;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int sp = 0; sp < S; sp++) { acc[0] += v[u][sp].x; acc[1] += v[u][sp].y; acc[2] += v[u][sp].z; acc[3] += v[u][sp].w; }
+            const uint32_t tok = tok0 + (i >> 5), n0 = t.wt * W_TILE + (i & 31u) * 4u;
+            if (n0 >= p.N) continue;
+            if (p.partial_out) {
+                float* dst = p.partial_out + (size_t)tok * p.N + n0;
+                if (vec_ok && n0 + 3u < p.N) *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                else
+                    for (uint32_t e = 0; e < 4u && n0 + e < p.N; e++) dst[e] = acc[e];
+            } else if (vec_ok && n0 + 3u < p.N) {
+                const size_t o = out_index(p, tok, n0);            // n0 % 4 == 0: the four outputs are contiguous
+                if (p.residual) {
+                    const uint2 r = *reinterpret_cast<const uint2*>(p.residual + o);
+                    const __half2 r01 = *reinterpret_cast<const __half2*>(&r.x), r23 = *reinterpret_cast<const __half2*>(&r.y);
+                    acc[0] += __low2float(r01); acc[1] += __high2float(r01); acc[2] += __low2float(r23); acc[3] += __high2float(r23);
+                }
+                const __half2 h01 = __halves2half2(__float2half_rn(acc[0]), __float2half_rn(acc[1]));
+                const __half2 h23 = __halves2half2(__float2half_rn(acc[2]), __float2half_rn(acc[3]));
+                uint2 w;
+                w.x = *reinterpret_cast<const uint32_t*>(&h01); w.y = *reinterpret_cast<const uint32_t*>(&h23);
+                *reinterpret_cast<uint2*>(p.Y + o) = w;
+            } else {
+                for (uint32_t e = 0; e < 4u && n0 + e < p.N; e++) {
+                    const size_t o = out_index(p, tok, n0 + e);
+                    p.Y[o] = __float2half_rn(p.residual ? acc[e] + __half2float(p.residual[o]) : acc[e]);
+                }
+            }
+        }
+    }
+}
+
 template <int FMT>
 __global__ void __launch_bounds__(Cfg<FMT>::THREADS, 1)
 qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW0,
@@ -162,6 +219,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     constexpr int RAW_TILE_BYTES = ROW_BYTES * W_TILE;
 
     extern __shared__ uint8_t smem_dyn[];
+    ptx::launch_dependents();     // the next projection in the stream may set itself up on SMs this grid leaves idle
     QCTA(0);
     const uint32_t pad = (1024u - (ptx::smem_u32(smem_dyn) & 1023u)) & 1023u;
     uint8_t* sB = smem_dyn + pad;
@@ -206,6 +264,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    // Everything above touched only this CTA's shared and tensor memory; global memory (inputs another kernel may
+    // still be writing, the split-K scratch the previous launch may still be using) is first touched below.
+    ptx::grid_dependency_wait();
     if (threadIdx.x == 0) QTRC(7, 0u, 0);
     QCTA(1);
 
@@ -499,57 +560,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             if (lane == 0) ptx::mbar_arrive(&tm_empty[buf]);
             if (et == 0) QTRC(6, it, 1);
             if (p.k_splits > 1) {
-                // the last CTA to finish a tile adds the partial tiles in split order
+                // count this partial tile in; the CTA that completes the count adds the partial tiles after the
+                // role loops have ended (every CTA of a split launch owns exactly one work item)
                 __threadfence();
                 ptx::bar_sync(1, 128);
                 if (et == 0) {
                     const uint32_t old = atomicAdd(&p.ws_counters[t.id], 1u);
                     *last_flag = (old == p.k_splits - 1u) ? 1u : 0u;
                 }
-                ptx::bar_sync(1, 128);
-                if (*last_flag) {
-                    __threadfence();
-                    const size_t split_stride = (size_t)(p.n_w_tiles * p.n_tok_tiles) * p.T * W_TILE;
-                    const float* base = p.ws_partial + (size_t)t.id * p.T * W_TILE + q * 32 + lane;
-                    // 16 tokens x k_splits loads in flight per thread (T is a multiple of 16); the sum runs in
-                    // split order, so the result does not depend on which CTA arrived last
-                    const int fmode = p.partial_out ? 1 : (p.residual ? 2 : 3);
-                    for (uint32_t j0 = 0; j0 < valid; j0 += 16) {
-                        float acc[16];
-#pragma unroll
-                        for (int j = 0; j < 16; j++) acc[j] = 0.0f;
-                        const float* b0 = base + (size_t)j0 * W_TILE;
-                        if (p.k_splits == 4) {
-#pragma unroll
-                            for (int s = 0; s < 4; s++)
-#pragma unroll
-                                for (int j = 0; j < 16; j++) acc[j] += __ldcg(b0 + s * split_stride + (size_t)j * W_TILE);
-                        } else {
-                            for (uint32_t s = 0; s < p.k_splits; s++)
-#pragma unroll
-                                for (int j = 0; j < 16; j++) acc[j] += __ldcg(b0 + s * split_stride + (size_t)j * W_TILE);
-                        }
-                        if (n_ok) {
-                            const uint32_t lim = valid - j0;
-                            if (fmode == 1) {
-                                float* dst = p.partial_out + (size_t)(tok0 + j0) * p.N + n;
-#pragma unroll
-                                for (int j = 0; j < 16; j++) if ((uint32_t)j < lim) dst[(size_t)j * p.N] = acc[j];
-                            } else if (fmode == 2) {
-                                const size_t o = out_base + (size_t)(tok0 + j0) * out_stride;
-#pragma unroll
-                                for (int j = 0; j < 16; j++)
-                                    if ((uint32_t)j < lim) p.Y[o + j * out_stride] = __float2half_rn(acc[j] + __half2float(p.residual[o + j * out_stride]));
-                            } else {
-                                __half* dst = p.Y + out_base + (size_t)(tok0 + j0) * out_stride;
-#pragma unroll
-                                for (int j = 0; j < 16; j++) if ((uint32_t)j < lim) dst[j * out_stride] = __float2half_rn(acc[j]);
-                            }
-                        }
-                    }
-                    if (et == 0) p.ws_counters[t.id] = 0u;
-                }
-                ptx::bar_sync(1, 128);
             }
         }
     }
@@ -568,6 +586,20 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     if (warp == 2) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    if (p.k_splits > 1 && *last_flag && !*abort_flag) {
+        // Split-K fix-up by the whole CTA: the partial tiles of this output tile are complete (this CTA's arrival
+        // completed the count), every warp is idle by now, and 16 float4 loads per thread keep enough bytes in
+        // flight to cover the L2 latency in one or two rounds.  The sum runs in split order, so the result does not
+        // depend on which CTA arrived last.
+        __threadfence();
+        const Tile t = decode_tile(blockIdx.x, p);
+        switch (p.k_splits) {
+            case 2: splitk_fixup<2>(p, t, threadIdx.x, C::THREADS); break;
+            case 4: splitk_fixup<4>(p, t, threadIdx.x, C::THREADS); break;
+            default: splitk_fixup<8>(p, t, threadIdx.x, C::THREADS); break;
+        }
+        if (threadIdx.x == 0) p.ws_counters[t.id] = 0u;
     }
     QCTA(3);
 }
@@ -823,8 +855,17 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     }
     const uint32_t total = pl.n_tok_tiles * pl.n_w_tiles * pl.k_splits;
     const uint32_t grid = total < (uint32_t)sm_count() ? total : (uint32_t)sm_count();
-    qgemm_kernel<FMT><<<grid, C::THREADS, smem, stream>>>(tmX, tmW0, tmW1, p);
-    return cudaGetLastError();
+    // Programmatic stream serialization: this grid's CTAs may be placed (and run their prologue up to
+    // griddepcontrol.wait) while the previous kernel in the stream drains, which hides the launch latency between
+    // back-to-back projections.  Stream order is unchanged: nothing is read or written before that wait.
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(C::THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, qgemm_kernel<FMT>, tmX, tmW0, tmW1, p);
 }
 
 cudaError_t dispatch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t s) {
