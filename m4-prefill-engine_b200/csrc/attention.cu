@@ -522,22 +522,56 @@ template <int D, int G> cudaError_t launch_gqa(const Params& p, cudaStream_t str
 // Q8_0 compression, one thread per 32-value block.  Bit-exact with the reference: the scale is
 // amax/127 in fp32, stored rounded to fp16, while the quantisation step uses the reciprocal of
 // the *unrounded* fp32 scale; rounding is half away from zero; codes are clamped to [-128, 127].
-__global__ void quantize_q8_0_kernel(const __half* __restrict__ src, uint8_t* __restrict__ dst, size_t nblocks) {
-    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= nblocks) return;
-    const __half* s = src + b * 32;
-    float v[32], amax = 0.0f;
+// A CTA's 128 blocks (4352 output bytes, a multiple of 16) are assembled in shared memory and written
+// back with 16-byte stores; inputs are read with 16-byte loads.
+constexpr int QZ_THREADS = 128;
+__global__ void __launch_bounds__(QZ_THREADS) quantize_q8_0_kernel(const __half* __restrict__ src, uint8_t* __restrict__ dst, size_t nblocks) {
+    __shared__ __align__(16) uint8_t stage[QZ_THREADS * 34];
+    const size_t b0 = (size_t)blockIdx.x * QZ_THREADS;
+    const size_t b = b0 + threadIdx.x;
+    const bool vec_in = (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
+    if (b < nblocks) {
+        const __half* s = src + b * 32;
+        float v[32], amax = 0.0f;
+        if (vec_in) {
 #pragma unroll
-    for (int i = 0; i < 32; i++) { v[i] = __half2float(s[i]); amax = fmaxf(amax, fabsf(v[i])); }
-    const float d = __fdiv_rn(amax, 127.0f);
-    const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-    uint8_t* o = dst + b * 34;
-    *reinterpret_cast<__half*>(o) = __float2half_rn(d);
+            for (int i = 0; i < 4; i++) {
+                const uint4 w = reinterpret_cast<const uint4*>(s)[i];
+                const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-    for (int i = 0; i < 32; i++) {
-        int q = (int)roundf(__fmul_rn(v[i], id));
-        q = max(-128, min(127, q));
-        o[2 + i] = (uint8_t)(int8_t)q;
+                for (int k = 0; k < 4; k++) {
+                    const __half2 h = *reinterpret_cast<const __half2*>(&ws[k]);
+                    v[8 * i + 2 * k] = __low2float(h); v[8 * i + 2 * k + 1] = __high2float(h);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] = __half2float(s[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(v[i]));
+        const float d = __fdiv_rn(amax, 127.0f);
+        const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+        uint16_t* o = reinterpret_cast<uint16_t*>(stage + threadIdx.x * 34);      // 34 is even: 2-byte aligned
+        o[0] = __half_as_ushort(__float2half_rn(d));
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            int q0 = (int)roundf(__fmul_rn(v[2 * i], id)), q1 = (int)roundf(__fmul_rn(v[2 * i + 1], id));
+            q0 = max(-128, min(127, q0)); q1 = max(-128, min(127, q1));
+            o[1 + i] = (uint16_t)((uint32_t)(uint8_t)(int8_t)q0 | ((uint32_t)(uint8_t)(int8_t)q1 << 8));
+        }
+    }
+    __syncthreads();
+    const size_t nb_here = nblocks - b0 < (size_t)QZ_THREADS ? nblocks - b0 : (size_t)QZ_THREADS;
+    const size_t bytes = nb_here * 34;
+    uint8_t* out = dst + b0 * 34;
+    if ((reinterpret_cast<uintptr_t>(out) & 15u) == 0) {
+        for (size_t i = threadIdx.x; i < bytes / 16; i += QZ_THREADS)
+            reinterpret_cast<uint4*>(out)[i] = reinterpret_cast<const uint4*>(stage)[i];
+        for (size_t i = (bytes / 16) * 16 + threadIdx.x; i < bytes; i += QZ_THREADS) out[i] = stage[i];
+    } else {
+        for (size_t i = threadIdx.x; i < bytes / 2; i += QZ_THREADS)
+            reinterpret_cast<uint16_t*>(out)[i] = reinterpret_cast<const uint16_t*>(stage)[i];
     }
 }
 
@@ -586,7 +620,7 @@ cudaError_t launch_attention(const Params& p, uint32_t D, cudaStream_t stream) {
 cudaError_t launch_quantize(const void* src, void* dst, size_t n_elements, cudaStream_t stream) {
     const size_t nb = n_elements / 32;
     if (nb == 0) return cudaSuccess;
-    quantize_q8_0_kernel<<<(unsigned)((nb + 127) / 128), 128, 0, stream>>>((const __half*)src, (uint8_t*)dst, nb);
+    quantize_q8_0_kernel<<<(unsigned)((nb + QZ_THREADS - 1) / QZ_THREADS), QZ_THREADS, 0, stream>>>((const __half*)src, (uint8_t*)dst, nb);
     return cudaGetLastError();
 }
 

@@ -124,7 +124,10 @@ CDC_HD uint32_t lut8_pair(const uint32_t* L, uint32_t q0, uint32_t q1) {
 // Traits every codec may override: META_WORDS 32-bit words of per-chunk metadata that live outside the packed
 // row (fetched from global memory by the unpack thread), ROW_SCALE when the weights are unpacked to exact small
 // integers and one fp16 scale per output row is applied to the fp32 accumulator instead.
+// HDR_WORDS / sub_lo / sub_hi describe which 32-bit words of the packed row dequant64(r, s, ...) reads: the
+// header words [0, HDR_WORDS) plus the words [sub_lo(s), sub_hi(s)).  The unpack thread loads only those.
 struct CodecDefaults {
+    static constexpr int HDR_WORDS = 0;
     static constexpr int META_WORDS = 0;
     static constexpr bool ROW_SCALE = false;
     static constexpr bool RAW_SWIZZLE_128 = false;   // packed tile staged with the 128-byte swizzle (ROW_BYTES == 128 only)
@@ -136,6 +139,8 @@ template <int FMT> struct Codec;
 template <> struct Codec<QUANT_Q4_0> : CodecDefaults {
     static constexpr int ROW_BYTES = 144;   // 8 blocks per 256 elements
     static constexpr int GROUPS = 3;      // unpack warp groups per matrix in the projection kernel
+    CDC_HD static constexpr int sub_lo(int s) { return 9 * s; }
+    CDC_HD static constexpr int sub_hi(int s) { return 9 * s + 9; }
     CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
 #pragma unroll
         for (int bi = 0; bi < 2; bi++) {
@@ -156,6 +161,8 @@ template <> struct Codec<QUANT_Q4_0> : CodecDefaults {
 template <> struct Codec<QUANT_MLX_4BIT> : CodecDefaults {
     static constexpr int ROW_BYTES = 160;
     static constexpr int GROUPS = 3;      // unpack warp groups per matrix in the projection kernel
+    CDC_HD static constexpr int sub_lo(int s) { return 10 * s; }
+    CDC_HD static constexpr int sub_hi(int s) { return 10 * s + 10; }
     CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
 #pragma unroll
         for (int bi = 0; bi < 2; bi++) {
@@ -176,6 +183,9 @@ template <> struct Codec<QUANT_MLX_4BIT> : CodecDefaults {
 template <> struct Codec<QUANT_Q4_K> : CodecDefaults {
     static constexpr int ROW_BYTES = 144;
     static constexpr int GROUPS = 3;      // unpack warp groups per matrix in the projection kernel
+    static constexpr int HDR_WORDS = 4;   // d, dmin, 12 bytes of 6-bit scales / minimums
+    CDC_HD static constexpr int sub_lo(int s) { return 4 + 8 * s; }
+    CDC_HD static constexpr int sub_hi(int s) { return 12 + 8 * s; }
     CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
         const uint32_t d_dmin = r[0];   // (d, dmin) as an fp16 pair
 #pragma unroll
@@ -207,6 +217,8 @@ template <> struct Codec<QUANT_Q4_K> : CodecDefaults {
 template <> struct Codec<QUANT_TERNARY_1_58> : CodecDefaults {
     static constexpr int ROW_BYTES = 96;
     static constexpr int GROUPS = 3;      // unpack warp groups per matrix in the projection kernel
+    CDC_HD static constexpr int sub_lo(int s) { return 6 * s; }
+    CDC_HD static constexpr int sub_hi(int s) { return 6 * s + 6; }
     CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
 #pragma unroll
         for (int bi = 0; bi < 2; bi++) {
@@ -230,6 +242,9 @@ template <> struct Codec<QUANT_TERNARY_1_58> : CodecDefaults {
 template <> struct Codec<QUANT_EXL3> : CodecDefaults {
     static constexpr int ROW_BYTES = 144;
     static constexpr int GROUPS = 2;      // unpack warp groups per matrix in the projection kernel
+    static constexpr int HDR_WORDS = 9;   // d, bias, sub-scales, residual scales, two 8-entry codebooks
+    CDC_HD static constexpr int sub_lo(int s) { return 12 + 6 * s; }
+    CDC_HD static constexpr int sub_hi(int s) { return 18 + 6 * s; }
     CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
         const float d = h_lo_to_float(r[0]), bias = h_hi_to_float(r[0]);
 #pragma unroll
@@ -264,6 +279,10 @@ template <> struct Codec<QUANT_EXL3> : CodecDefaults {
 template <> struct Codec<QUANT_VAR_RATE_AFFINE> : CodecDefaults {
     static constexpr int ROW_BYTES = 160;
     static constexpr int GROUPS = 2;      // unpack warp groups per matrix in the projection kernel
+    static constexpr int HDR_WORDS = 7;   // d, bias, sub-scales, sub-biases, mode bytes
+    // payload runs start at bytes 32 + {0,12,24,40,56,72,88,108}; any run may be read as five words
+    CDC_HD static constexpr int sub_lo(int s) { return s == 0 ? 8 : (s == 1 ? 14 : (s == 2 ? 22 : 30)); }
+    CDC_HD static constexpr int sub_hi(int s) { return s == 0 ? 16 : (s == 1 ? 23 : (s == 2 ? 31 : 40)); }
     CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
         const float d = h_lo_to_float(r[0]), bias = h_hi_to_float(r[0]);
 #pragma unroll
@@ -331,6 +350,8 @@ template <> struct Codec<QUANT_VAR_RATE_AFFINE> : CodecDefaults {
 template <> struct Codec<QUANT_MLX_4BIT_G64> : CodecDefaults {
     static constexpr int ROW_BYTES = 128;
     static constexpr int GROUPS = 3;
+    CDC_HD static constexpr int sub_lo(int s) { return 8 * s; }
+    CDC_HD static constexpr int sub_hi(int s) { return 8 * s + 8; }
     static constexpr int META_WORDS = 4;
     static constexpr bool RAW_SWIZZLE_128 = true;
     CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* meta) {
@@ -358,6 +379,8 @@ template <> struct Codec<QUANT_MLX_4BIT_G64> : CodecDefaults {
 template <> struct Codec<QUANT_TERNARY_ROW> : CodecDefaults {
     static constexpr int ROW_BYTES = 64;
     static constexpr int GROUPS = 3;
+    CDC_HD static constexpr int sub_lo(int s) { return 4 * s; }
+    CDC_HD static constexpr int sub_hi(int s) { return 4 * s + 4; }
     static constexpr bool ROW_SCALE = true;
     CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
 #pragma unroll

@@ -80,6 +80,28 @@ __global__ void rope_kernel(__half* __restrict__ X, uint32_t M, uint32_t D, floa
     x[j + half] = __float2half_rn(b * c + a * s);
 }
 
+// Rotate-half RoPE for D % 4 == 0: one thread owns two adjacent frequencies of one token and walks all heads, so
+// the sine and cosine (the expensive part) are computed once per token and frequency instead of once per head, and
+// every access is a 4-byte pair.  Element arithmetic is that of rope_kernel.
+__global__ void rope_heads_kernel(__half* __restrict__ X, uint32_t H, uint32_t M, uint32_t D, float log2_theta, uint32_t pos0) {
+    const uint32_t half = D / 2, per_tok = half / 2;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)M * per_tok) return;
+    const uint32_t m = (uint32_t)(i / per_tok), j = 2u * (uint32_t)(i % per_tok);
+    float s0, c0, s1, c1;
+    sincosf((float)(pos0 + m) * exp2f(-2.0f * (float)j / (float)D * log2_theta), &s0, &c0);
+    sincosf((float)(pos0 + m) * exp2f(-2.0f * (float)(j + 1) / (float)D * log2_theta), &s1, &c1);
+    __half* x = X + (size_t)m * D + j;
+    const size_t head_stride = (size_t)M * D;
+#pragma unroll 4
+    for (uint32_t h = 0; h < H; h++, x += head_stride) {
+        const __half2 lo = *reinterpret_cast<const __half2*>(x), hi = *reinterpret_cast<const __half2*>(x + half);
+        const float a0 = __low2float(lo), a1 = __high2float(lo), b0 = __low2float(hi), b1 = __high2float(hi);
+        *reinterpret_cast<__half2*>(x) = __halves2half2(__float2half_rn(a0 * c0 - b0 * s0), __float2half_rn(a1 * c1 - b1 * s1));
+        *reinterpret_cast<__half2*>(x + half) = __halves2half2(__float2half_rn(b0 * c0 + a0 * s0), __float2half_rn(b1 * c1 + a1 * s1));
+    }
+}
+
 __global__ void add_residual_f32_kernel(const __half* __restrict__ A, const float* __restrict__ B, __half* __restrict__ Y, size_t n) {
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i + 3 < n) {
@@ -97,6 +119,11 @@ cudaError_t rmsnorm(const void* X, const void* weight, void* Y, uint32_t M, uint
     return cudaGetLastError();
 }
 cudaError_t rope(void* X, uint32_t H, uint32_t M, uint32_t D, float theta, uint32_t pos0, cudaStream_t s) {
+    if (D % 4 == 0 && (reinterpret_cast<uintptr_t>(X) & 3u) == 0) {
+        const size_t threads = (size_t)M * (D / 4);
+        rope_heads_kernel<<<(unsigned)((threads + 127) / 128), 128, 0, s>>>((__half*)X, H, M, D, log2f(theta), pos0);
+        return cudaGetLastError();
+    }
     const size_t pairs = (size_t)H * M * (D / 2);
     rope_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>((__half*)X, M, D, log2f(theta), pos0, pairs);
     return cudaGetLastError();

@@ -84,6 +84,7 @@ template <int FMT> struct Cfg {
     // two phases ahead, which holds when its own previous wait already implied the phase before.
     static constexpr int DQ_GROUPS = cdc::Codec<FMT>::GROUPS;
     static_assert(DQ_GROUPS >= 1 && DQ_GROUPS <= STAGES, "unpack groups are bounded by the operand ring depth");
+    static_assert(STAGES == 3 && KCHUNK / KSTEP == 4, "the unpack loop's ownership counter relies on 4 = 1 (mod STAGES)");
     static constexpr int DQ_THREADS = 128 * DQ_GROUPS;   // arrivals that release a packed stage
     static constexpr int FILL_THREADS = 128;             // arrivals that publish an unpacked stage
     // Warp placement.  A warp's scheduler is warp % 4.  The MMA-issuing thread is back-pressured by the tensor
@@ -133,6 +134,29 @@ template <int FMT> inline uint32_t raw_stages_for(uint32_t T, bool swiglu) {
     const long n = raw_stages_fit<FMT>(T, swiglu, b_stages_for<FMT>(T, swiglu));
     return (uint32_t)(n < 2 ? 2 : (n > MAX_RAW_STAGES ? MAX_RAW_STAGES : n));
 }
+
+// Loads the words [W, HI) of a packed row from shared memory into r[] with the widest aligned loads.  SW: the row
+// was staged with the 128-byte TMA swizzle (16-byte chunk index ^ row % 8); such rows are read in whole chunks.
+template <int W, int HI, bool SW>
+__device__ __forceinline__ void ld_words(const uint8_t* rowp, uint32_t xr, uint32_t* r) {
+    if constexpr (W < HI) {
+        if constexpr (W % 4 == 0 && W + 4 <= HI) {
+            const uint4 v = *reinterpret_cast<const uint4*>(rowp + (SW ? ((uint32_t)(W / 4) ^ xr) << 4 : (uint32_t)W * 4u));
+            r[W] = v.x; r[W + 1] = v.y; r[W + 2] = v.z; r[W + 3] = v.w;
+            ld_words<W + 4, HI, SW>(rowp, xr, r);
+        } else if constexpr (W % 2 == 0 && W + 2 <= HI) {
+            static_assert(!SW, "swizzled rows are read in 16-byte chunks");
+            const uint2 v = *reinterpret_cast<const uint2*>(rowp + W * 4);
+            r[W] = v.x; r[W + 1] = v.y;
+            ld_words<W + 2, HI, SW>(rowp, xr, r);
+        } else {
+            static_assert(!SW, "swizzled rows are read in 16-byte chunks");
+            r[W] = *reinterpret_cast<const uint32_t*>(rowp + W * 4);
+            ld_words<W + 1, HI, SW>(rowp, xr, r);
+        }
+    }
+}
+template <int S> struct IntC { static constexpr int value = S; };
 
 struct Tile { uint32_t wt, tt, ks, id; };
 __device__ __forceinline__ Tile decode_tile(uint32_t idx, const Params& p) {
@@ -379,6 +403,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         const uint32_t mrow_in_tile = p.swiglu ? (row & 63u) : row;
         const uint32_t row_off = (row >> 3) * 1024 + (row & 7) * 128, xr = row & 7;
         uint32_t rs = 0, rph = 0, kn = 0;                     // kn: running 64-element step of this CTA
+        uint32_t km = 0, own_ph = 0;                          // (kn / 4) % STAGES; phase of the group's own operand stage
         bool ok = true;
         for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
             const Tile t = decode_tile(idx, p);
@@ -407,22 +432,26 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&raw_full[rs], rph, abort_flag, p.err, 106));
                 if (!ok) break;
                 if (row == 0) QTR(3, (kn >> 2) * 2 + grp, 0);
+                // Only the words a sub-tile needs are loaded, right before it is unpacked: a group handles one or
+                // two of a chunk's four sub-tiles, and short-lived inputs leave the registers to the 32 outputs.
                 uint32_t r[ROW_BYTES / 4];
-                const uint4* src = reinterpret_cast<const uint4*>(sRaw + rs * RAW_TILE_BYTES + row * ROW_BYTES);
-#pragma unroll
-                for (int i = 0; i < ROW_BYTES / 16; i++) {
-                    // rows of exactly 128 bytes would put every lane on the same banks: those tiles are loaded
-                    // with the 128-byte TMA swizzle (16-byte chunk index ^ row % 8) and read back through it
-                    uint4 v = src[Cd::RAW_SWIZZLE_128 ? (i ^ (int)(row & 7u)) : i];
-                    r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
-                }
-#pragma unroll
-                for (int s = 0; s < KCHUNK / KSTEP; s++) {
-                    if ((G == STAGES ? (kn + s) % STAGES : (uint32_t)(s % G)) == grp) {
+                const uint8_t* rowp = sRaw + rs * RAW_TILE_BYTES + row * ROW_BYTES;
+                constexpr bool SW = Cd::RAW_SWIZZLE_128;
+                ld_words<0, Cd::HDR_WORDS, SW>(rowp, xr, r);
+                auto sub_tile = [&](auto S) {
+                    constexpr int s = decltype(S)::value;
+                    // owner of this 64-element step: with G == STAGES the group that owns operand stage
+                    // (step % STAGES); the chunk counter km = (kn / 4) % 3 stands in for kn % 3 (4 = 1 mod 3)
+                    uint32_t own = (G == STAGES) ? km + (uint32_t)(s % STAGES) : (uint32_t)(s % G);
+                    if (G == STAGES && own >= (uint32_t)STAGES) own -= (uint32_t)STAGES;
+                    if (own == grp) {
                         uint32_t o[32];
+                        ld_words<Cd::sub_lo(s), Cd::sub_hi(s), SW>(rowp, xr, r);
                         Cd::dequant64(r, s, o, meta);
                         if (row == 0) QTR(4 + grp, kn + s, 0);
-                        const uint32_t step = kn + s, as = step % STAGES, aph = (step / STAGES) & 1u;
+                        uint32_t as, aph;
+                        if (G == STAGES) { as = grp; aph = own_ph; own_ph ^= 1u; }     // the group's own stage, phase toggles per use
+                        else { const uint32_t step = kn + s; as = step % STAGES; aph = (step / STAGES) & 1u; }
                         ok = __all_sync(0xffffffffu, ok && ptx::mbar_wait<32>(&a_empty[as], aph ^ 1u, abort_flag, p.err, 107));
                         if (row == 0) QTR(4 + grp, kn + s, 1);
                         if (ok) {
@@ -436,7 +465,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                             if (row == 0) QTR(4 + grp, kn + s, 2);
                         }
                     }
-                }
+                };
+                sub_tile(IntC<0>{}); sub_tile(IntC<1>{}); sub_tile(IntC<2>{}); sub_tile(IntC<3>{});
+                km = (km == (uint32_t)STAGES - 1u) ? 0u : km + 1u;
                 kn += KCHUNK / KSTEP;
                 // Release the packed stage only now: the stores above consumed every register loaded
                 // from it, so the loads have certainly returned.  (An arrive issued right after the
@@ -515,9 +546,28 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                         }
                     }
                 }
-            } else
+            } else {
+            // Residual epilogue: the 16 residual values of a batch are requested one batch ahead, all at once and
+            // with no store in between (Y may alias the residual, so the compiler would otherwise order every load
+            // behind the previous store and pay one memory latency per element).
+            __half res_next[16];
+            auto load_residual = [&](uint32_t c0, __half (&dst)[16]) {
+                if (mode == 2 && n_ok && c0 < valid) {
+                    const uint32_t lim = valid - c0;
+                    const __half* src = p.residual + out_base + (size_t)(tok0 + c0) * out_stride;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) dst[j] = (uint32_t)j < lim ? __ldg(src + j * out_stride) : __half(0.0f);
+                }
+            };
+            load_residual(0u, res_next);
             for (uint32_t c0 = 0; c0 < p.T; c0 += 16) {
                 uint32_t v[16];
+                __half res[16];
+                if (mode == 2) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) res[j] = res_next[j];
+                    if (c0 + 16 < p.T) load_residual(c0 + 16, res_next);
+                }
                 if (et == 0 && it == 0) QTR(7, 1 + c0 / 16, 0);
                 ptx::tmem_ld_x16(taddr + c0, v);
                 ptx::tmem_ld_wait();
@@ -542,7 +592,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                         const size_t o = out_base + (size_t)(tok0 + c0) * out_stride;
 #pragma unroll
                         for (int j = 0; j < 16; j++)
-                            if ((uint32_t)j < lim) p.Y[o + j * out_stride] = __float2half_rn(f[j] + __half2float(p.residual[o + j * out_stride]));
+                            if ((uint32_t)j < lim) p.Y[o + j * out_stride] = __float2half_rn(f[j] + __half2float(res[j]));
                     } else {
                         __half* dst = p.Y + out_base + (size_t)(tok0 + c0) * out_stride;
                         if (lim >= 16u) {                                       // whole batch exists: no per-store predicate
@@ -554,6 +604,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                         }
                     }
                 }
+            }
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
