@@ -136,6 +136,9 @@ void* b200_bridge_stream(void);
 
 /* Testing hook: non-zero routes every GEMM through the CUDA-core fallback kernel. */
 void b200_bridge_force_generic(int on);
+/* Testing hook: != 0 routes head-dim-128 Q8_0 attention to the warp-level MMA kernels instead of the
+ * tensor-memory kernel, so the two can be compared on the same inputs. */
+void b200_bridge_force_legacy_attention(int on);
 
 #ifdef __cplusplus
 }

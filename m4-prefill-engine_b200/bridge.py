@@ -87,6 +87,8 @@ def bind(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.b200_bridge_stream.restype = _vp
     lib.b200_bridge_force_generic.argtypes = [_i]
     lib.b200_bridge_force_generic.restype = None
+    lib.b200_bridge_force_legacy_attention.argtypes = [_i]
+    lib.b200_bridge_force_legacy_attention.restype = None
     for name, args in _OPTIONAL.items():
         if hasattr(lib, name):
             fn = getattr(lib, name)

@@ -25,8 +25,11 @@
 #include "../../include/quant_router.h"
 #include "bridge_state.cuh"
 #include "layer_ops.cuh"
+#include "ptx.cuh"
 
 namespace attn {
+
+int g_force_legacy = 0;      // testing hook: route head-dim-128 Q8_0 attention to the warp-level MMA kernels
 
 constexpr int BQ = 64, BK = 64, THREADS = 128;
 
@@ -584,6 +587,427 @@ __global__ void dequantize_q8_0_kernel(const uint8_t* __restrict__ src, __half* 
     for (int i = 0; i < 32; i++) dst[b * 32 + i] = __float2half_rn((float)(int8_t)blk[2 + i] * d);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-memory variant (head dim 128, Q8_0 cache): the two contractions of a 128-key step run as
+// tcgen05.mma with their accumulators in tensor memory.
+//
+//   CTA = one kv head x 128/G query positions x the G query heads sharing it (128 rows = UMMA M).
+//   Shared memory holds four fp16 operand tiles in the 128-byte-swizzled K-major layout of the
+//   projection kernel (two 64-column atoms each): Q [row][d], K [key][d], V^T [d][key], P [row][key],
+//   plus two stages of packed K/V bytes fetched with cp.async.  Per key tile:
+//     all threads     unpack K (16-byte stores) and V (transposed: 2-byte stores, a warp writes 32
+//                     consecutive keys of one d, i.e. 64 contiguous bytes)
+//     one thread      S = Q.K^T        : 8 MMAs 128x128x16 -> tensor-memory columns 0..127
+//     warps 0-3       thread = query row = tensor-memory lane: scale, causal mask, running max and
+//                     sum in registers (no shuffles: a thread owns its whole row), P = exp2(s - m) to
+//                     shared memory as fp16, O *= exp2(m_old - m_new) in tensor memory, skipped while
+//                     no row of the warp raised its maximum
+//     one thread      O += P.V         : 8 MMAs 128x128x16 -> tensor-memory columns 128..255
+//   The phases of one tile are separated by CTA barriers and two mbarriers the MMAs commit to.
+//   Every mbarrier wait is bounded; on expiry the CTA stops issuing work and leaves.
+// ---------------------------------------------------------------------------------------------
+constexpr int TC_ROWS = 128, TC_BK = 128, TC_WORKERS = 256, TC_THREADS = TC_WORKERS + 32, TC_D = 128;   // 8 worker warps + the MMA issuer
+
+// Development aid: with -DATTN_TRACE thread 0 of CTA (0,0) accumulates clock64() deltas per phase of the key-tile loop.
+#ifdef ATTN_TRACE
+__device__ unsigned long long g_attn_trace[8];
+#define ATR_DECL unsigned long long atr_t = clock64(), atr_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define ATR(i) do { const unsigned long long n_ = clock64(); atr_acc[i] += n_ - atr_t; atr_t = n_; } while (0)
+#define ATR_FLUSH() do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) for (int i_ = 0; i_ < 8; i_++) g_attn_trace[i_] = atr_acc[i_]; } while (0)
+#else
+#define ATR_DECL do { } while (0)
+#define ATR(i) do { } while (0)
+#define ATR_FLUSH() do { } while (0)
+#endif
+constexpr int TC_ATOM = 128 * 128;                       // bytes of one [128 rows][64 fp16] atom
+constexpr int TC_TILE = 2 * TC_ATOM;                     // one operand tile
+constexpr int TC_ROW_RAW = (TC_D / 32) * 34;             // packed bytes of one key
+constexpr int TC_RAW_TILE = TC_BK * TC_ROW_RAW;
+constexpr int TC_RAW_PAD = ((TC_RAW_TILE + 15) & ~15) + 16;
+constexpr size_t TC_SMEM = 1024 + 4 * (size_t)TC_TILE + 4 * (size_t)TC_RAW_PAD + 64 + 2 * 2 * 128 * 4;
+
+__device__ __forceinline__ float ex2(float x) {        // 2^x, one MUFU instruction; ex2(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// byte offset of fp16 element (row, col) inside a K-major swizzled tile of two 64-column atoms
+__device__ __forceinline__ uint32_t tc_off(uint32_t row, uint32_t col) {
+    return (col >> 6) * TC_ATOM + (row >> 3) * 1024u + (row & 7u) * 128u + ((((col & 63u) >> 3) ^ (row & 7u)) << 4) + (col & 7u) * 2u;
+}
+
+template <int G>
+__global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const Params p, int* err) {
+    constexpr int BP = TC_ROWS / G;                      // query positions per CTA
+    extern __shared__ uint8_t smem_raw_[];
+    uint8_t* base = smem_raw_ + ((1024u - (ptx::smem_u32(smem_raw_) & 1023u)) & 1023u);
+    uint8_t* sQ = base;
+    uint8_t* sK = sQ + TC_TILE;
+    uint8_t* sVt = sK + TC_TILE;
+    uint8_t* sP = sVt + TC_TILE;
+    uint8_t* sRaw = sP + TC_TILE;                        // [2 stages][K, V][TC_RAW_PAD]
+    uint64_t* bar_s = reinterpret_cast<uint64_t*>(sRaw + 4 * TC_RAW_PAD);
+    uint64_t* bar_o = bar_s + 1;
+    uint64_t* bar_raw = bar_o + 1;                       // [2] packed K/V bytes of a stage landed (bulk copies)
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_raw + 2);
+    volatile uint32_t* abort_flag = tmem_holder + 1;
+    float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bar_s) + 64);   // [2 parities][2 halves][128 rows]
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t pb = gridDim.x - 1 - blockIdx.x;      // latest position blocks (longest) first
+    const uint32_t hk = blockIdx.y;
+    const uint32_t p0 = pb * BP;
+    const uint32_t last_pos = min(p.pos0 + min(p0 + BP, p.M) - 1, p.Mkv - 1);
+    const uint32_t n_ktiles = last_pos / TC_BK + 1;
+
+    if (tid == 0) {
+        ptx::mbar_init(bar_s, 1); ptx::mbar_init(bar_o, 1); ptx::mbar_init(&bar_raw[0], 1); ptx::mbar_init(&bar_raw[1], 1);
+        *abort_flag = 0u;
+        ptx::fence_barrier_init();
+    }
+    __syncwarp();
+    // Warp 8 issues every MMA and every bulk copy and does nothing else: the issuing thread is held while the
+    // tensor pipe works through its MMAs, which would otherwise delay a worker warp's share of the unpacking.
+    const bool worker = warp < 8u;
+    if (warp == 8) { ptx::tmem_alloc(tmem_holder, 256); ptx::tmem_relinquish(); }
+
+    // ---- stage Q: row r = head (r / BP), position p0 + r % BP ----
+    for (uint32_t i = tid; i < TC_ROWS * (TC_D / 8); i += TC_THREADS) {
+        const uint32_t r = i / (TC_D / 8), c = i % (TC_D / 8);
+        const uint32_t h = hk * G + r / BP, pos = p0 + r % BP;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (pos < p.M) v = *reinterpret_cast<const uint4*>(p.Q + ((size_t)h * p.M + pos) * TC_D + c * 8);
+        *reinterpret_cast<uint4*>(sQ + tc_off(r, c * 8)) = v;
+    }
+    const uint8_t* Kh = p.K + (size_t)hk * p.Mkv * TC_ROW_RAW;
+    const uint8_t* Vh = p.V + (size_t)hk * p.Mkv * TC_ROW_RAW;
+
+    // async copy of the packed bytes of key tile kt into raw stage kt & 1.  Global addresses are only 2-byte
+    // aligned in general: the 16-byte phase of the source (the same for every tile of a head, a tile being 17408
+    // bytes) is kept in shared memory, the ragged ends (< 16 bytes each) go through registers.
+    const uint32_t phK = (uint32_t)((uintptr_t)Kh & 15u), phV = (uint32_t)((uintptr_t)Vh & 15u);
+    const uint8_t* const k_end = p.K + (size_t)p.Hkv * p.Mkv * TC_ROW_RAW;
+    const uint8_t* const v_end = p.V + (size_t)p.Hkv * p.Mkv * TC_ROW_RAW;
+    // A tile goes as two bulk copies issued by one thread when the 16-byte-aligned span around it stays inside
+    // the K and V buffers (always, except possibly at the very first and very last bytes of a buffer); otherwise
+    // every thread copies 16-byte pieces with cp.async and the ragged ends through registers.
+    auto bulk_ok = [&](uint32_t kt) {
+        const uint32_t k0 = kt * TC_BK, bytes = min((uint32_t)TC_BK, p.Mkv - k0) * TC_ROW_RAW;
+        const uint8_t* ks = Kh + (size_t)k0 * TC_ROW_RAW - phK;
+        const uint8_t* vs = Vh + (size_t)k0 * TC_ROW_RAW - phV;
+        return ks >= p.K && vs >= p.V && ks + ((phK + bytes + 15u) & ~15u) <= k_end && vs + ((phV + bytes + 15u) & ~15u) <= v_end;
+    };
+    auto issue = [&](uint32_t kt) {
+        const uint32_t k0 = kt * TC_BK, rows = min((uint32_t)TC_BK, p.Mkv - k0);
+        const uint32_t bytes = rows * TC_ROW_RAW;
+        if (bulk_ok(kt)) {
+            if (tid == TC_WORKERS) {
+                const uint32_t nk = (phK + bytes + 15u) & ~15u, nv = (phV + bytes + 15u) & ~15u;
+                ptx::mbar_arrive_expect_tx(&bar_raw[kt & 1u], nk + nv);
+                ptx::bulk_load_1d(sRaw + ((kt & 1u) * 2 + 0) * TC_RAW_PAD, Kh + (size_t)k0 * TC_ROW_RAW - phK, nk, &bar_raw[kt & 1u]);
+                ptx::bulk_load_1d(sRaw + ((kt & 1u) * 2 + 1) * TC_RAW_PAD, Vh + (size_t)k0 * TC_ROW_RAW - phV, nv, &bar_raw[kt & 1u]);
+            }
+            return;
+        }
+#pragma unroll
+        for (int which = 0; which < 2; which++) {
+            const uint32_t ph = which ? phV : phK;
+            const uint8_t* src = (which ? Vh : Kh) + (size_t)k0 * TC_ROW_RAW;
+            uint8_t* dst = sRaw + ((kt & 1u) * 2 + which) * TC_RAW_PAD + ph;
+            const uint32_t head = min(bytes, (16u - ph) & 15u);
+            const uint32_t chunks = (bytes - head) >> 4, tail0 = head + (chunks << 4);
+            if (tid * 2u < head) *reinterpret_cast<uint16_t*>(dst + tid * 2u) = *reinterpret_cast<const uint16_t*>(src + tid * 2u);
+            for (uint32_t i = tid; i < chunks; i += TC_THREADS) cp_async16(dst + head + (i << 4), src + head + (i << 4));
+            if (tail0 + tid * 2u < bytes)
+                *reinterpret_cast<uint16_t*>(dst + tail0 + tid * 2u) = *reinterpret_cast<const uint16_t*>(src + tail0 + tid * 2u);
+        }
+        cp_async_commit();
+    };
+    // packed bytes of tile kt have landed (a CTA barrier must follow before other threads' copies are read)
+    uint32_t raw_phase = 0;                               // bit s: parity of the next bulk completion of stage s
+    auto wait_raw = [&](uint32_t kt) {
+        if (bulk_ok(kt)) {
+            const uint32_t st = kt & 1u;
+            ptx::mbar_wait<32>(&bar_raw[st], (raw_phase >> st) & 1u, abort_flag, err, 204);
+            raw_phase ^= 1u << st;
+        } else {
+            cp_async_wait<0>();
+        }
+    };
+
+    // raw stage kt & 1 -> sK (row-major keys) or sVt (transposed), one matrix per call, by all 256 threads: thread
+    // t takes dims [64 h, 64 h + 64) of key r (r = t % 128, h = t / 128), 68 packed bytes read as 17 words when the
+    // row is 4-byte aligned (it is whenever the cache base is), values = fp16(q * d) rounded once as the reference's
+    // dequantize_q8_0.  K goes out as 16-byte stores, V^T as 2-byte stores (a warp writes 32 consecutive keys of
+    // one d: 64 contiguous bytes, no bank conflict).
+    auto unpack = [&](uint32_t kt, const uint32_t which) {
+        const uint32_t k0 = kt * TC_BK, rows = min((uint32_t)TC_BK, p.Mkv - k0);
+        const uint32_t r = tid & 127u, h = tid >> 7;
+        const uint8_t* rawp = sRaw + (size_t)((kt & 1u) * 2 + which) * TC_RAW_PAD +
+                              (which ? phV : phK) + r * TC_ROW_RAW + h * 68u;
+        const __half2 off = __half2half2(__float2half(1152.0f));
+        uint8_t* vt[8];
+        if (which) {
+            const uint32_t cr = (r & 63u) >> 3;
+            uint8_t* vb = sVt + (r >> 6) * TC_ATOM + h * 8u * 1024u + (r & 7u) * 2u;     // dims 64 h ..: 8 row groups further
+#pragma unroll
+            for (int x = 0; x < 8; x++) vt[x] = vb + x * 128 + ((cr ^ (uint32_t)x) << 4);
+        }
+        uint32_t q[17];                                    // two blocks: 68 bytes
+        if (r < rows) {
+            if ((ptx::smem_u32(rawp) & 3u) == 0u) {
+#pragma unroll
+                for (int i = 0; i < 17; i++) q[i] = reinterpret_cast<const uint32_t*>(rawp)[i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < 17; i++) {
+                    const uint16_t* hp = reinterpret_cast<const uint16_t*>(rawp) + 2 * i;
+                    q[i] = (uint32_t)hp[0] | ((uint32_t)hp[1] << 16);
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < 2; b++) {                      // block b of this half: bytes [34 b, 34 b + 34)
+            uint32_t w[16];
+            if (r < rows) {
+                // 16-bit field f of the block sits at byte 34 b + 2 f: half (17 b + f) & 1 of word (17 b + f) / 2
+                const uint32_t dw = q[(17 * b) >> 1];
+                const uint32_t dd = ((17 * b) & 1) ? (dw >> 16) : (dw & 0xFFFFu);
+                const uint32_t d2 = dd | (dd << 16);
+#pragma unroll
+                for (int f = 0; f < 16; f++) {
+                    const int hidx = 17 * b + 1 + f;       // index of the 16-bit field holding codes 2f, 2f+1
+                    const uint32_t word = q[hidx >> 1];
+                    // bytes (b0, b1) -> (bits 0-7, bits 16-23); flip the sign bit: unsigned q + 128; 0x6400 | x = 1024 + x
+                    const uint32_t sp = (hidx & 1) ? __byte_perm(word, 0u, 0x4342u) : __byte_perm(word, 0u, 0x4140u);
+                    const uint32_t x = (sp ^ 0x00800080u) | 0x64006400u;
+                    const __half2 qh = __hsub2(*reinterpret_cast<const __half2*>(&x), off);
+                    const __half2 v = __hmul2(qh, *reinterpret_cast<const __half2*>(&d2));
+                    w[f] = *reinterpret_cast<const uint32_t*>(&v);
+                }
+            } else {
+#pragma unroll
+                for (int f = 0; f < 16; f++) w[f] = 0u;    // absent keys: zero (P is zero there, 0 * garbage is not)
+            }
+            if (which == 0) {
+                // row r, 16-byte chunks 4 b .. 4 b + 3 of atom h: (rowbase | xr << 4) ^ (c << 4) = rowbase + ((c ^ xr) << 4)
+                uint8_t* rowb = sK + h * TC_ATOM + (r >> 3) * 1024u + (r & 7u) * 128u + ((r & 7u) << 4);
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    *reinterpret_cast<uint4*>(rowb + (((b * 4 + e) << 4) ^ ((r & 7u) << 4)) - ((r & 7u) << 4)) =
+                        make_uint4(w[4 * e], w[4 * e + 1], w[4 * e + 2], w[4 * e + 3]);
+            } else {
+                // element (d, key r) of V^T: vt[d & 7] + (d >> 3) * 1024 with the eight swizzled row starts vt[]
+                // computed once per call, so every store is base register + immediate
+#pragma unroll
+                for (int f = 0; f < 16; f++) {
+                    const int d = b * 32 + 2 * f;          // within this thread's 64 dims
+                    *reinterpret_cast<uint16_t*>(vt[d & 7] + (d >> 3) * 1024) = (uint16_t)(w[f] & 0xFFFFu);
+                    *reinterpret_cast<uint16_t*>(vt[(d + 1) & 7] + ((d + 1) >> 3) * 1024) = (uint16_t)(w[f] >> 16);
+                }
+            }
+        }
+    };
+
+    issue(0);
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_holder;
+    const uint32_t tS = tmem, tO = tmem + 128u;
+    const uint32_t idesc = ptx::umma_idesc_f16(128, 128);
+    const uint64_t desc_hi = ptx::umma_desc_k_sw128(0u);
+    auto desc = [&](const uint8_t* tile, int atom, int kk) {
+        return desc_hi | (uint64_t)((((ptx::smem_u32(tile) + atom * TC_ATOM) & 0x3FFFFu) >> 4) + 2 * kk);
+    };
+
+    // Two threads per query row: thread t and t + 128 (warps w and w + 4 address the same tensor-memory lanes)
+    // own columns [0, 64) and [64, 128) of the row's scores and outputs.  They share the running maximum (one
+    // float exchanged through shared memory per tile) and keep partial sums that meet only in the epilogue.
+    const uint32_t row = tid & 127u, half_id = tid >> 7, c_base = half_id * 64u;
+    const uint32_t head = hk * G + row / BP, pos = p0 + row % BP;
+    const uint32_t row_pos = p.pos0 + pos;
+    float m_run = -1e30f, l_run = 0.0f;
+    const uint32_t lane_addr = ((warp & 3u) * 32u) << 16;
+    bool ok = true;
+
+    // Schedule of one key tile: the S MMAs run while V is unpacked, the PV MMAs while the next tile's K is unpacked.
+    //   sK  : written by unpack K(kt) during PV(kt-1), read by S(kt)
+    //   sVt : written by unpack V(kt) during S(kt) (after PV(kt-1) has completed), read by PV(kt)
+    //   sP / O in tensor memory : written by the softmax of tile kt after PV(kt-1) has completed
+    wait_raw(0);
+    __syncthreads();                                       // packed bytes of tile 0 visible to every thread
+    if (worker) unpack(0, 0);
+    if (n_ktiles > 1) issue(1);
+    ATR_DECL;
+    for (uint32_t kt = 0; kt < n_ktiles; kt++) {
+        const uint32_t ph = kt & 1u;
+        ptx::fence_proxy_async_smem();                     // this thread's part of sK(kt)
+        __syncthreads();
+        ATR(0);
+        if (*abort_flag) break;
+        if (warp == 8) {
+            ptx::tc_fence_after_sync();
+            if (ptx::elect_one()) {
+#pragma unroll
+                for (int a = 0; a < 2; a++)
+#pragma unroll
+                    for (int kk = 0; kk < 4; kk++)
+                        ptx::umma_f16_ss(tS, desc(sQ, a, kk), desc(sK, a, kk), idesc, (uint32_t)(a | kk) != 0u);
+                ptx::umma_commit(bar_s);
+            }
+            __syncwarp();
+        }
+        // PV(kt-1) must be done before sVt, sP and O are touched again (a failed wait sets the abort flag, which
+        // is tested after the next CTA barrier)
+        if (kt > 0) ptx::mbar_wait<32>(bar_o, ph ^ 1u, abort_flag, err, 202);
+        if (worker) unpack(kt, 1);
+        ATR(1);
+        if (worker) {
+            ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(bar_s, ph, abort_flag, err, 201));
+            ATR(2);
+            // (a failed wait has set the abort flag; the code below still runs so that the pair barrier and the
+            // warp-collective tensor-memory accesses stay matched, its results are discarded after the CTA barrier)
+            ptx::tc_fence_after_sync();
+            const uint32_t k0 = kt * TC_BK;
+            // tiles entirely at or below every row's position (and inside the cache) need no mask
+            const bool full = (k0 + TC_BK - 1 <= p.pos0 + p0) && (k0 + TC_BK <= p.Mkv);
+            float sc[64];
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+                uint32_t v[16];
+                ptx::tmem_ld_x16(tS + lane_addr + c_base + c0, v);
+#pragma unroll
+                for (int j = 0; j < 16; j++) sc[c0 + j] = __uint_as_float(v[j]);
+            }
+            ptx::tmem_ld_wait();
+            float mx = -1e30f;
+            if (full) {
+#pragma unroll
+                for (int j = 0; j < 64; j++) mx = fmaxf(mx, sc[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 64; j++) {
+                    const uint32_t key = k0 + c_base + j;
+                    if (key > row_pos || key >= p.Mkv) sc[j] = -INFINITY;
+                    mx = fmaxf(mx, sc[j]);
+                }
+            }
+            mx = mx * p.scale_log2e;                        // the scale is positive: max and scaling commute
+            float* xm = xch + ph * 256u;
+            xm[half_id * 128u + row] = mx;
+            ptx::bar_sync(1 + (int)(warp & 3u), 64);        // this warp and its partner
+            mx = fmaxf(fmaxf(mx, xm[(half_id ^ 1u) * 128u + row]), m_run);
+            const float corr = ex2(m_run - mx);
+            m_run = mx;
+            ATR(3);
+            float rs = 0.0f;
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+                uint32_t pk[8];
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                    // masked scores are -inf: fma gives -inf, ex2 gives 0
+                    const float e0 = ex2(fmaf(sc[c0 + j], p.scale_log2e, -mx));
+                    const float e1 = ex2(fmaf(sc[c0 + j + 1], p.scale_log2e, -mx));
+                    rs += e0 + e1;
+                    pk[j >> 1] = pack_h2(e0, e1);
+                }
+                *reinterpret_cast<uint4*>(sP + tc_off(row, c_base + c0)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4*>(sP + tc_off(row, c_base + c0 + 8)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            }
+            l_run = l_run * corr + rs;
+            ATR(4);
+            // O *= corr on this thread's 64 columns, skipped while no row of this warp raised its maximum
+            if (kt > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll
+                for (int c0 = 0; c0 < 64; c0 += 16) {
+                    uint32_t v[16];
+                    ptx::tmem_ld_x16(tO + lane_addr + c_base + c0, v);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
+                    ptx::tmem_st_x16(tO + lane_addr + c_base + c0, v);
+                }
+                ptx::tmem_st_wait();
+            }
+            ptx::fence_proxy_async_smem();
+            ATR(5);
+            ptx::tc_fence_before_sync();
+        }
+        __syncthreads();
+        ATR(6);
+        if (*abort_flag) break;
+        if (warp == 8) {
+            ptx::tc_fence_after_sync();
+            if (ptx::elect_one()) {
+#pragma unroll
+                for (int a = 0; a < 2; a++)
+#pragma unroll
+                    for (int kk = 0; kk < 4; kk++)
+                        ptx::umma_f16_ss(tO, desc(sP, a, kk), desc(sVt, a, kk), idesc, (kt | (uint32_t)(a | kk)) != 0u);
+                ptx::umma_commit(bar_o);
+            }
+            __syncwarp();
+        }
+        if (kt + 1 < n_ktiles) {
+            wait_raw(kt + 1);
+            __syncthreads();                               // ... visible to every thread; raw stage kt & 1 is free
+            ATR(0);
+            if (kt + 2 < n_ktiles) issue(kt + 2);
+            ATR(6);
+            if (worker) unpack(kt + 1, 0);                 // sK is free: S(kt) completed before this tile's softmax
+        }
+        ATR(7);
+    }
+    // the last PV
+    ptx::mbar_wait<32>(bar_o, (n_ktiles - 1u) & 1u, abort_flag, err, 203);
+    __syncthreads();
+    ATR_FLUSH();
+    cp_async_wait<0>();
+
+    if (worker) xch[half_id * 128u + row] = l_run;         // (the loop's last use of this buffer is behind a CTA barrier)
+    __syncthreads();
+    if (worker && !*abort_flag) {
+        // (the tensor-memory loads are warp-collective: every lane takes part, only the stores depend on the row)
+        ptx::tc_fence_after_sync();
+        const bool row_ok = pos < p.M;
+        const float l_tot = l_run + xch[(half_id ^ 1u) * 128u + row];
+        const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
+        __half* dst = (p.out_tokens_major ? p.O + ((size_t)pos * p.Hq + head) * TC_D : p.O + ((size_t)head * p.M + pos) * TC_D) + c_base;
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 16) {
+            uint32_t v[16];
+            ptx::tmem_ld_x16(tO + lane_addr + c_base + c0, v);
+            ptx::tmem_ld_wait();
+            uint32_t pk[8];
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) pk[j >> 1] = pack_h2(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv);
+            if (row_ok) {
+                *reinterpret_cast<uint4*>(dst + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4*>(dst + c0 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            }
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 8) { ptx::tc_fence_after_sync(); ptx::tmem_dealloc(tmem, 256); }
+}
+
+template <int G> cudaError_t launch_tc(const Params& p, cudaStream_t stream) {
+    constexpr int BP = TC_ROWS / G;
+    dim3 grid((p.M + BP - 1) / BP, p.Hkv);
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    attn_tc_kernel<G><<<grid, TC_THREADS, TC_SMEM, stream>>>(p, bridge::g.err_word);
+    return cudaGetLastError();
+}
+
 template <int D> size_t smem_bytes() {
     constexpr int LD = D + 8;
     constexpr int RAW_TILE_PAD = (((BK * (D / 32) * 34) + 15) & ~15) + 16;
@@ -593,6 +1017,13 @@ template <int D> size_t smem_bytes() {
 cudaError_t launch_attention(const Params& p, uint32_t D, cudaStream_t stream) {
     // grouped-head kernel when the group size divides its 128-row tile into whole warps
     const uint32_t G = p.Hq / p.Hkv;
+    // tensor-memory kernel: head dim 128, Q8_0 cache, every row of a lone pointer 16-byte aligned for the Q loads
+    if (D == 128 && !p.kv_fp16 && !g_force_legacy && ((uintptr_t)p.Q & 15u) == 0 && ((uintptr_t)p.O & 15u) == 0) {
+        if (G == 1) return launch_tc<1>(p, stream);
+        if (G == 2) return launch_tc<2>(p, stream);
+        if (G == 4) return launch_tc<4>(p, stream);
+        if (G == 8) return launch_tc<8>(p, stream);
+    }
     if (D == 128) {
         if (G == 1) return launch_gqa<128, 1>(p, stream);
         if (G == 2) return launch_gqa<128, 2>(p, stream);
@@ -686,6 +1117,11 @@ int b200_bridge_dequantize_q8_0(void* src, size_t src_bytes, void* dst, size_t d
     if (host_dst && copy_back(host_dst, d, n_elements * 2) != 0) return -5;
     return 0;
 }
+
+void b200_bridge_force_legacy_attention(int on) { attn::g_force_legacy = on; }
+#ifdef ATTN_TRACE
+void b200_bridge_debug_attn_trace(unsigned long long* out) { cudaMemcpyFromSymbol(out, attn::g_attn_trace, 64); }
+#endif
 
 /* Causal attention.  Q [Hq][M][D] fp16; K, V [Hkv][Mkv][D/32] Q8_0 blocks (or fp16 [Hkv][Mkv][D] when
  * kv_fp16 != 0); O [Hq][M][D], or [M][Hq*D] when out_tokens_major != 0.  D is 64 or 128; Hq % Hkv == 0. */

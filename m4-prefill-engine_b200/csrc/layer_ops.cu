@@ -93,12 +93,25 @@ __global__ void rope_heads_kernel(__half* __restrict__ X, uint32_t H, uint32_t M
     sincosf((float)(pos0 + m) * exp2f(-2.0f * (float)(j + 1) / (float)D * log2_theta), &s1, &c1);
     __half* x = X + (size_t)m * D + j;
     const size_t head_stride = (size_t)M * D;
-#pragma unroll 4
-    for (uint32_t h = 0; h < H; h++, x += head_stride) {
-        const __half2 lo = *reinterpret_cast<const __half2*>(x), hi = *reinterpret_cast<const __half2*>(x + half);
-        const float a0 = __low2float(lo), a1 = __high2float(lo), b0 = __low2float(hi), b1 = __high2float(hi);
-        *reinterpret_cast<__half2*>(x) = __halves2half2(__float2half_rn(a0 * c0 - b0 * s0), __float2half_rn(a1 * c1 - b1 * s1));
-        *reinterpret_cast<__half2*>(x + half) = __halves2half2(__float2half_rn(b0 * c0 + a0 * s0), __float2half_rn(b1 * c1 + a1 * s1));
+    // heads in batches of four: all loads of a batch are issued before its first store (the stores would
+    // otherwise order every later load behind them, one memory round trip per head)
+    for (uint32_t h0 = 0; h0 < H; h0 += 4, x += 4 * head_stride) {
+        __half2 lo[4], hi[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+            if (h0 + u < H) {
+                lo[u] = *reinterpret_cast<const __half2*>(x + u * head_stride);
+                hi[u] = *reinterpret_cast<const __half2*>(x + u * head_stride + half);
+            }
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+            if (h0 + u < H) {
+                const float a0 = __low2float(lo[u]), a1 = __high2float(lo[u]), b0 = __low2float(hi[u]), b1 = __high2float(hi[u]);
+                *reinterpret_cast<__half2*>(x + u * head_stride) =
+                    __halves2half2(__float2half_rn(a0 * c0 - b0 * s0), __float2half_rn(a1 * c1 - b1 * s1));
+                *reinterpret_cast<__half2*>(x + u * head_stride + half) =
+                    __halves2half2(__float2half_rn(b0 * c0 + a0 * s0), __float2half_rn(b1 * c1 + a1 * s1));
+            }
     }
 }
 

@@ -486,6 +486,17 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         for (uint32_t idx = blockIdx.x; idx < total_tiles; idx += gridDim.x, it++) {
             const Tile t = decode_tile(idx, p);
             const uint32_t buf = it & 1u;
+            if (p.residual && p.k_splits == 1u) {
+                // The epilogue warps idle through the tile's main loop: use that time to pull the residual tile
+                // (T rows of 256 bytes) into L2, so the loads below wait for an L2 hit rather than for HBM.
+                const uint32_t rows = t.tt * p.T < p.M ? min(p.T, p.M - t.tt * p.T) : 0u;
+                const uint32_t n0 = t.wt * W_TILE;
+                for (uint32_t r = et; r < rows; r += 128u) {
+                    const char* line = reinterpret_cast<const char*>(p.residual + (size_t)(t.tt * p.T + r) * p.N + n0);
+                    if (n0 < p.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
+                    if (n0 + 64u < p.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(line + 128));
+                }
+            }
             if (!ptx::mbar_wait<256>(&tm_full[buf], (it >> 1) & 1u, abort_flag, p.err, 108)) break;
             if (et == 0) QTRC(6, it, 0);
             ptx::tc_fence_after_sync();

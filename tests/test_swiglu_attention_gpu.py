@@ -144,6 +144,46 @@ def test_attention_cases(bridge, case):
     assert np.abs(O.astype(np.float64) - gold.astype(np.float64)).max() <= TOL
 
 
+def test_attention_tensor_memory_kernel_long(bridge):
+    """Head dim 128 over a Q8_0 cache runs on the tcgen05 / tensor-memory kernel: several 128-key tiles, ragged last
+    tile, a position offset, grouped heads; against the oracle and against the warp-level MMA kernel."""
+    Hq, Hkv, M, Mkv, D, pos0 = 8, 2, 700, 1000, 128, 300
+    g = o.RefLcg(77)
+    Q = g.activations(Hq, M, D); K = g.activations(Hkv, Mkv, D); V = g.activations(Hkv, Mkv, D)
+    Kq, Vq = o.quantize_q8_0(K), o.quantize_q8_0(V)
+    gold = o.attention(Q, o.dequantize_q8_0(Kq, K.shape), o.dequantize_q8_0(Vq, V.shape), D ** -0.5, pos0, True)
+    a = run_attn(bridge, Q, Kq, Vq, D ** -0.5, Hkv, Mkv, pos0, True)
+    assert np.abs(a.astype(np.float64) - gold.astype(np.float64)).max() <= TOL
+    bridge.lib.b200_bridge_force_legacy_attention(1)
+    try:
+        b = run_attn(bridge, Q, Kq, Vq, D ** -0.5, Hkv, Mkv, pos0, True)
+    finally:
+        bridge.lib.b200_bridge_force_legacy_attention(0)
+    assert np.abs(b.astype(np.float64) - gold.astype(np.float64)).max() <= TOL
+    assert np.abs(a.astype(np.float32) - b.astype(np.float32)).max() <= 2e-3
+    assert bridge.device_error() == 0
+
+
+def test_attention_unaligned_cache(bridge):
+    """K and V caches that start on an odd 2-byte boundary (a view into a larger buffer) take the piecewise copy path."""
+    Hq, Hkv, M, D = 4, 2, 260, 128
+    g = o.RefLcg(78)
+    Q = g.activations(Hq, M, D); K = g.activations(Hkv, M, D); V = g.activations(Hkv, M, D)
+    Kq, Vq = o.quantize_q8_0(K), o.quantize_q8_0(V)
+    gold = o.attention(Q, o.dequantize_q8_0(Kq, K.shape), o.dequantize_q8_0(Vq, V.shape), D ** -0.5, 0, False)
+    for shift in (2, 6, 10):
+        Kb = torch.zeros(Kq.size + 32, dtype=torch.uint8, device="cuda"); Vb = torch.zeros(Vq.size + 32, dtype=torch.uint8, device="cuda")
+        Kb[shift:shift + Kq.size] = dev(Kq); Vb[shift:shift + Vq.size] = dev(Vq)
+        Qd = dev(Q)
+        O = torch.full((Hq, M, D), float("nan"), dtype=torch.float16, device="cuda")
+        rc = bridge.lib.b200_bridge_dispatch_attention_q8kv(Qd.data_ptr(), Kb.data_ptr() + shift, Vb.data_ptr() + shift, O.data_ptr(),
+                                                            Hq, Hkv, M, M, D, cfloat(D ** -0.5), 0, 0, 0)
+        assert rc == 0
+        bridge.synchronize()
+        assert np.abs(O.cpu().numpy().astype(np.float64) - gold.astype(np.float64)).max() <= TOL, f"shift {shift}"
+    assert bridge.device_error() == 0
+
+
 def test_attention_causal_isolation(bridge):
     # changing token t leaves every output before t unchanged (tests/redteam_engine.py:303-352)
     H, M, D, t = 4, 150, 128, 97
