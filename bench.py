@@ -234,11 +234,11 @@ def roll_rows(Wh: np.ndarray, i: int, cuts: list) -> np.ndarray:
     return np.concatenate([np.roll(pl.reshape(N, -1), i, axis=0).reshape(-1) for pl in np.split(Wh, cuts)])
 
 
-def time_layer(br, pkg, world: int, rank: int, steps: int, warmup: int):
+def time_layer(br, pkg, world: int, rank: int, steps: int, warmup: int, collective: str = "peer"):
     """Tensor-parallel decoder layer (Q4_0, RMSNorm, GQA 32/8, RoPE, Q8_0 KV, SwiGLU 14336), M=2048."""
     import torch
     import torch.distributed as dist
-    from m4_prefill_engine_b200.layer import TransformerLayerConfig, TransformerLayerCoordinator, torch_allreduce_hook
+    from m4_prefill_engine_b200.layer import PeerExchange, TransformerLayerConfig, TransformerLayerCoordinator, torch_allreduce_hook
     c = LAYER
     if c["Hkv"] % world or c["F"] % world:
         return None
@@ -257,7 +257,11 @@ def time_layer(br, pkg, world: int, rank: int, steps: int, warmup: int):
     n1 = torch.ones(c["K"], dtype=torch.float16, device=dev); n2 = torch.ones_like(n1)
     layer = TransformerLayerCoordinator(cfg, br)
     layer.set_norm_weights(n1, n2)
-    if world > 1:
+    px = None
+    if world > 1 and collective == "peer" and (c["M"] // world) % 256 == 0:
+        px = PeerExchange.setup(layer)           # reduce-scatter fused into the projection epilogue, over peer memory
+    elif world > 1:
+        collective = "nccl"
         layer.set_allreduce(torch_allreduce_hook(br))
     stream = torch.cuda.ExternalStream(br.lib.b200_bridge_stream())
     args = (X, w["q"], w["k"], w["v"], w["o"], w["gate"], w["up"], w["down"], Y)
@@ -280,13 +284,20 @@ def time_layer(br, pkg, world: int, rank: int, steps: int, warmup: int):
     ms = float(t.item())
     finite = bool(torch.isfinite(Y.float()).all().item())
     kernels = layer.kernels_per_forward()
+    if world > 1:
+        dist.barrier()
     layer.close()
+    if px is not None:
+        px.close()
     qd, kd = c["H"] * c["D"], c["Hkv"] * c["D"]
     flops = 2.0 * c["M"] * c["K"] * (qd + 2 * kd) + 2.0 * c["H"] * c["M"] * (c["M"] + 1) * c["D"] + 2.0 * c["M"] * qd * c["K"] + \
         4.0 * c["M"] * c["K"] * c["F"] + 2.0 * c["M"] * c["F"] * c["K"]
     return {"workload": "Llama-style 8B decoder layer prefill, M=2048, Q4_0, GQA 32/8, D=128, RoPE, Q8_0 KV, SwiGLU 14336",
             "parallelism": f"tp{world}", "scaling": "strong", "ms": ms, "tflops": flops / ms / 1e9, "gflop_per_layer": flops / 1e9,
-            "kernels_per_layer": kernels, "allreduce": "nccl fp32 [M,K] x2" if world > 1 else None, "finite": finite}
+            "kernels_per_layer": kernels, "finite": finite,
+            "allreduce": None if world == 1 else ("nccl fp32 [M,K] x2" if collective == "nccl" else
+                                                  "fp32 partial rows scattered to their owner from the projection epilogue over peer memory, "
+                                                  "owner adds + residual, fp16 rows written to every rank, x2")}
 
 
 def roofline(achieved_tflops, algo_bytes, ms_step, burst, sustained, hbm, src) -> dict:
@@ -424,6 +435,10 @@ def run_ours(args) -> None:
         e2e_ok = all(bool(torch.isfinite(y.float()).all().item()) and float(y.float().abs().max()) > 0 for y in Yp)
 
     layer = time_layer(br, pkg, world, rank, max(3, min(args.steps, 20)), 3) if not args.no_layer else None
+    if layer is not None and world > 1:          # the same layer with NCCL all-reduces, for comparison
+        nccl = time_layer(br, pkg, world, rank, max(3, min(args.steps, 20)), 3, collective="nccl")
+        if nccl is not None:
+            layer["nccl_allreduce_ms"] = nccl["ms"]
 
     if rank == 0:
         burst, sustained, hbm, src = peaks()

@@ -55,8 +55,15 @@ public:
 
     // fp16 [K] RMSNorm weights (device pointers); required when rms_eps > 0.
     void set_norm_weights(const void* attn_norm, const void* mlp_norm);
-    // required when tp_size > 1
+    // required when tp_size > 1 (unless the peer exchange below is set)
     void set_allreduce(AllReduceFn fn, void* ctx);
+    // Tensor-parallel reduction fused into the row-split projections: their epilogue scatters fp32 partial rows
+    // straight into the owning rank's receive buffer over NVLink, the owner adds them and the residual and writes
+    // the fp16 rows into every rank's result buffer.  All pointers are mapped into this process (peer / IPC
+    // mappings for the other ranks): recv[o] fp32 [world][M/world][K], out0[o] / out1[o] fp16 [M][K] (result of the
+    // O and down projections), flags[o] 16 zero-initialised words.  Needs M / world to be a multiple of 256.
+    bool set_peer_exchange(uint32_t rank, uint32_t world, void* const* recv, void* const* out0, void* const* out1,
+                           void* const* flags);
 
     // Enqueue one layer on `stream`.  All pointers are device pointers.  Weight shapes for rank r of
     // tp_size: W_q [H/tp*D][K], W_k/W_v [Hkv/tp*D][K], W_o [K][H/tp*D], W_gate/W_up [N_mlp/tp][K],
@@ -103,4 +110,22 @@ int b200_layer_set_allreduce(void* layer, void (*fn)(void* ctx, void* buf, size_
 int b200_layer_forward(void* layer, const void* X_in, const void* W_q, const void* W_k, const void* W_v,
                        const void* W_o, const void* W_gate, const void* W_up, const void* W_down, void* X_out);
 uint32_t b200_layer_kernels_per_forward(void* layer);
+
+/* ---- tensor-parallel exchange over peer memory (no counterpart in the reference, which is single-device) ---- */
+/* Device memory that other processes of the node can map: allocates `bytes` (zero-filled) and writes a 64-byte
+ * handle to pass to the peers; the peers map it with b200_peer_open.  Return 0 or -5. */
+int b200_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
+int b200_peer_open(const unsigned char* handle64, void** ptr);
+int b200_peer_close(void* ptr);
+int b200_peer_free(void* ptr);
+/* See TransformerLayerCoordinator::set_peer_exchange; arrays of `world` pointers indexed by rank. */
+int b200_layer_set_peer_exchange(void* layer, uint32_t rank, uint32_t world, void* const* recv, void* const* out0,
+                                 void* const* out1, void* const* flags);
+/* The three steps on their own (device pointers): partial sums of Y = X.W^T scattered to the owners' receive
+ * buffers; the owner's reduction + residual + broadcast into out[]; the wait for every rank's rows. */
+int b200_peer_gemm_scatter(const void* X, const void* W, int format, uint32_t M, uint32_t K, uint32_t N, uint32_t rank,
+                           uint32_t world, void* const* recv, void* const* flags, uint32_t epoch);
+int b200_peer_reduce_broadcast(uint32_t rank, uint32_t world, void* const* recv, void* const* out, void* const* flags,
+                               uint32_t epoch, const void* residual, uint32_t M, uint32_t K);
+int b200_peer_wait_rows(uint32_t rank, uint32_t world, void* const* flags, uint32_t epoch);
 }

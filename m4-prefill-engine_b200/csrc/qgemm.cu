@@ -113,6 +113,7 @@ struct Params {
     uint32_t* ws_counters;
     int* err;
     // planar layouts: per-64 scale plane followed by the bias plane (meta), or one fp16 scale per row
+    GemmArgs::Scatter scatter;   // fused reduce-scatter of fp32 partial sums to peer ranks (world == 0: off)
     uint32_t swiglu;             // 1: tiles are 64 gate rows (matrix 0) + their 64 up rows (matrix 1); output = silu(g) * u
     const uint8_t* meta0;
     const uint8_t* meta1;
@@ -512,7 +513,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             // The destination kind is fixed per launch; branching on it once per tile (not per element) keeps
             // the inner loops to a convert, an address add and a store.
             const uint32_t valid = tok0 < p.M ? min(p.T, p.M - tok0) : 0u;     // token columns of this tile that exist
-            const int mode = p.k_splits > 1 ? 0 : (p.partial_out ? 1 : (p.residual ? 2 : 3));
+            // fused reduce-scatter: this tile's token rows belong to one rank; its fp32 sums go to that rank's
+            // receive buffer (slot = this rank) over NVLink, tile by tile, while other tiles are still being computed
+            float* partial_dst = p.partial_out;
+            if (p.scatter.world) {
+                const uint32_t owner = tok0 / p.scatter.rows;
+                partial_dst = p.scatter.recv[owner] + ((ptrdiff_t)p.scatter.rank - (ptrdiff_t)owner) * (ptrdiff_t)p.scatter.rows * (ptrdiff_t)p.N;
+            }
+            const int mode = p.k_splits > 1 ? 0 : (partial_dst ? 1 : (p.residual ? 2 : 3));
             // integer-valued codecs: the row's scale multiplies the fp32 accumulator (before SiLU, before split-K sums)
             float rsc0 = 1.0f;
             if (Cd::ROW_SCALE && !p.swiglu) rsc0 = n_ok ? __half2float(p.row_scale0[n]) : 0.0f;
@@ -596,7 +604,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 } else if (n_ok && c0 < valid) {
                     const uint32_t lim = valid - c0;                            // >= 1 columns of this batch exist
                     if (mode == 1) {
-                        float* dst = p.partial_out + (size_t)(tok0 + c0) * p.N + n;
+                        float* dst = partial_dst + (size_t)(tok0 + c0) * p.N + n;
 #pragma unroll
                         for (int j = 0; j < 16; j++) if ((uint32_t)j < lim) dst[(size_t)j * p.N] = f[j];
                     } else if (mode == 2) {
@@ -648,6 +656,21 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     if (warp == 2) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    if (p.scatter.world) {
+        // every thread's peer stores are fenced at system scope before this CTA is counted; the CTA that completes
+        // the count tells every rank that this rank's partial sums have arrived
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const uint32_t old = atomicAdd(p.scatter.done_counter, 1u);
+            if (old == gridDim.x - 1u) {
+                *p.scatter.done_counter = 0u;
+                __threadfence_system();
+                for (uint32_t o = 0; o < p.scatter.world; o++)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.scatter.flags[o] + p.scatter.rank), "r"(p.scatter.epoch) : "memory");
+            }
+        }
     }
     if (p.k_splits > 1 && *last_flag && !*abort_flag) {
         // Split-K fix-up by the whole CTA: the partial tiles of this output tile are complete (this CTA's arrival
@@ -855,7 +878,7 @@ Plan make_plan(const GemmArgs& a) {
     pl.n_w_tiles = (a.N + rows_per_tile - 1) / rows_per_tile;
     const uint32_t chunks = a.K / KCHUNK;
     pl.k_splits = 1;
-    if (!a.W1) {
+    if (!a.W1 && !a.scatter.world) {       // (the fused reduce-scatter epilogue writes whole tiles: no K split)
         // split K while the grid would leave most SMs idle and every split keeps >= 2 chunks
         const uint32_t tiles = pl.n_tok_tiles * pl.n_w_tiles;
         const uint32_t sms = (uint32_t)sm_count();
@@ -893,6 +916,8 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     p.raw_stages = raw_stages_for<FMT>(pl.T, a.W1 != nullptr); p.b_stage_bytes = pl.T * 128u;
     p.b_stages = b_stages_for<FMT>(pl.T, a.W1 != nullptr);
     p.Y = (__half*)a.Y; p.residual = (const __half*)a.residual; p.partial_out = a.partial_out;
+    p.scatter = a.scatter;
+    if (a.scatter.world && (pl.k_splits != 1 || a.W1 || a.scatter.rows % pl.T != 0 || a.scatter.rows * a.scatter.world != a.M)) return cudaErrorInvalidValue;
     p.layout = (uint32_t)a.layout; p.H = a.H; p.D = a.D ? a.D : 1;
     p.ws_partial = ws.partial; p.ws_counters = ws.counters; p.err = ws.err;
     // planar layouts: everything behind the N x (K/256 * ROW_BYTES) plane of packed values
@@ -967,6 +992,7 @@ size_t workspace_floats(const GemmArgs& a) {
 cudaError_t launch(const GemmArgs& a, const Workspace& ws, cudaStream_t stream) {
     g_last_launches = 1;
     if (fast_path_ok(a)) return dispatch_fast(a, ws, stream);
+    if (a.scatter.world) return cudaErrorInvalidValue;      // the fused reduce-scatter exists on the tensor-core path only
     Params p;
     memset(&p, 0, sizeof(p));
     p.M = a.M; p.N = a.N; p.K = a.K;

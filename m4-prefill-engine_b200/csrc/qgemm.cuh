@@ -19,6 +19,17 @@ struct GemmArgs {
     const void* residual;     // optional fp16 [M][N] added in the epilogue (standard layout only)
     float* partial_out;       // optional fp32 [M][N]: write raw accumulators instead of fp16 Y
     int force_generic;        // testing hook: use the CUDA-core fallback kernel
+    // Tensor-parallel reduce-scatter fused into the epilogue (row-split projections): instead of one local fp32
+    // [M][N] buffer, token rows [o * rows, (o + 1) * rows) go to rank o's receive buffer, slot `rank`, through
+    // peer-mapped pointers.  When the grid's last CTA is done it raises flag `rank` in every rank's flag array to
+    // `epoch` (stores fenced at system scope).  world == 0: off.
+    struct Scatter {
+        uint32_t world, rank, rows;      // rows = M / world token rows owned by each rank (a multiple of the token tile)
+        float* recv[8];                  // recv[o]: rank o's buffer, fp32 [world][rows][N]
+        uint32_t* flags[8];              // flags[o]: rank o's arrival flags, one word per source rank
+        uint32_t epoch;
+        uint32_t* done_counter;          // device-local word, zero between launches
+    } scatter;
 };
 
 struct Workspace {            // split-K scratch, owned by the caller

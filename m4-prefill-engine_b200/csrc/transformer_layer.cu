@@ -6,11 +6,13 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <string>
 
 #include "../../include/b200_bridge.h"
 #include "../../include/transformer_layer.h"
 #include "bridge_state.cuh"
 #include "layer_ops.cuh"
+#include "peer_reduce.cuh"
 #include "qgemm.cuh"
 
 namespace b200_llm {
@@ -28,6 +30,7 @@ struct TransformerLayerCoordinator::Impl {
     AllReduceFn allreduce = nullptr;
     void* allreduce_ctx = nullptr;
     KernelBinding gemm_binding, head_binding;
+    peer::Exchange px;               // fused tensor-parallel reduction over peer memory (world == 0: not set)
     bool bound = false;
     cudaStream_t stream = nullptr;
 };
@@ -46,7 +49,7 @@ TransformerLayerCoordinator::TransformerLayerCoordinator(int device, cudaStream_
 
 TransformerLayerCoordinator::~TransformerLayerCoordinator() {
     void* bufs[] = {impl_->xn, impl_->q, impl_->k, impl_->v, impl_->kq, impl_->vq, impl_->attn, impl_->x_mid, impl_->act,
-                    impl_->partial, impl_->ws, impl_->counters};
+                    impl_->partial, impl_->ws, impl_->counters, impl_->px.done_counter};
     for (void* b : bufs) if (b) cudaFree(b);
     delete impl_;
 }
@@ -106,6 +109,23 @@ bool TransformerLayerCoordinator::initialize_pipelines(const void*) {
 void TransformerLayerCoordinator::set_norm_weights(const void* a, const void* m) { impl_->norm1 = a; impl_->norm2 = m; }
 void TransformerLayerCoordinator::set_allreduce(AllReduceFn fn, void* ctx) { impl_->allreduce = fn; impl_->allreduce_ctx = ctx; }
 
+bool TransformerLayerCoordinator::set_peer_exchange(uint32_t rank, uint32_t world, void* const* recv, void* const* out0,
+                                                    void* const* out1, void* const* flags) {
+    const TransformerLayerConfig& c = config_;
+    if (world != c.tp_size || world < 2 || world > 8 || rank >= world || c.M % world != 0 || (c.M / world) % 256 != 0) return false;
+    peer::Exchange& x = impl_->px;
+    if (!x.done_counter) {
+        if (!dev_alloc((void**)&x.done_counter, 16)) return false;
+        cudaMemset(x.done_counter, 0, 16);
+    }
+    for (uint32_t o = 0; o < world; o++) {
+        if (!recv[o] || !out0[o] || !out1[o] || !flags[o]) return false;
+        x.recv[o] = (float*)recv[o]; x.out[0][o] = out0[o]; x.out[1][o] = out1[o]; x.flags[o] = (uint32_t*)flags[o];
+    }
+    x.rank = rank; x.world = world; x.epoch = 0;
+    return true;
+}
+
 void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in, const void* W_q, const void* W_k,
                                           const void* W_v, const void* W_o, const void* W_gate, const void* W_up,
                                           const void* W_down, void* X_out) {
@@ -115,7 +135,7 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
     if (!im.bound) { status_ = -1; return; }
     if (!X_in || !W_q || !W_k || !W_v || !W_o || !W_gate || !W_up || !W_down || !X_out) { status_ = -2; return; }
     if (c.rms_eps > 0.0f && (!im.norm1 || !im.norm2)) { status_ = -2; return; }
-    if (c.tp_size > 1 && !im.allreduce) { status_ = -2; return; }
+    if (c.tp_size > 1 && !im.allreduce && !im.px.world) { status_ = -2; return; }
     status_ = 0;
     const uint32_t hq = c.H / c.tp_size, hkv = c.num_kv_heads / c.tp_size, f = c.N_mlp / c.tp_size;
     qg::Workspace ws;
@@ -150,19 +170,41 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
     }
     check(attn::launch_attention_simple(im.q, kk, vv, im.attn, hq, hkv, c.M, c.M, c.D, c.attn_scale, 0, 1, c.kv_q8_0 ? 0 : 1, stream));
     // 2. O projection + first residual
+    const void* x_mid = im.x_mid;
+    // row-split projection with the reduction fused in: scatter in the epilogue, owner reduces and broadcasts
+    auto reduced_gemm = [&](const void* X, const void* W, uint32_t Kin, const void* residual, int which_out) {
+        if (status_) return;
+        peer::Exchange& x = im.px;
+        x.epoch++;
+        qg::GemmArgs a; memset(&a, 0, sizeof(a));
+        a.format = im.gemm_binding.format; a.X = X; a.W0 = W; a.M = c.M; a.N = c.K; a.K = Kin; a.layout = im.gemm_binding.layout;
+        a.scatter.world = x.world; a.scatter.rank = x.rank; a.scatter.rows = c.M / x.world; a.scatter.epoch = x.epoch;
+        a.scatter.done_counter = x.done_counter;
+        for (uint32_t o = 0; o < x.world; o++) { a.scatter.recv[o] = x.recv[o]; a.scatter.flags[o] = x.flags[o]; }
+        if (qg::launch(a, ws, stream) != cudaSuccess) { status_ = -6; return; }
+        launches_ += (uint32_t)qg::last_launch_count();
+        check(peer::reduce_broadcast(x, which_out, residual, c.M, c.K, im.err, stream));
+        check(peer::wait_rows(x, im.err, stream));
+    };
     if (c.tp_size == 1) {
         gemm(im.gemm_binding, im.attn, W_o, nullptr, im.x_mid, c.K, hq * c.D, 0, X_in, nullptr);
+    } else if (im.px.world) {
+        reduced_gemm(im.attn, W_o, hq * c.D, X_in, 0);
+        x_mid = im.px.out[0][im.px.rank];
     } else {
         gemm(im.gemm_binding, im.attn, W_o, nullptr, nullptr, c.K, hq * c.D, 0, nullptr, im.partial);
         if (!status_) im.allreduce(im.allreduce_ctx, im.partial, (size_t)c.M * c.K, stream);
         check(lops::add_residual_f32(X_in, im.partial, im.x_mid, (size_t)c.M * c.K, stream));
     }
     // 3. MLP
-    const void* x_mlp = im.x_mid;
-    if (c.rms_eps > 0.0f) { check(lops::rmsnorm(im.x_mid, im.norm2, im.xn, c.M, c.K, c.rms_eps, stream)); x_mlp = im.xn; }
+    const void* x_mlp = x_mid;
+    if (c.rms_eps > 0.0f) { check(lops::rmsnorm(x_mid, im.norm2, im.xn, c.M, c.K, c.rms_eps, stream)); x_mlp = im.xn; }
     gemm(im.gemm_binding, x_mlp, W_gate, W_up, im.act, f, c.K, 0, nullptr, nullptr);
     if (c.tp_size == 1) {
         gemm(im.gemm_binding, im.act, W_down, nullptr, X_out, c.K, f, 0, im.x_mid, nullptr);
+    } else if (im.px.world) {
+        reduced_gemm(im.act, W_down, f, x_mid, 1);
+        if (!status_) check(cudaMemcpyAsync(X_out, im.px.out[1][im.px.rank], (size_t)c.M * c.K * 2, cudaMemcpyDeviceToDevice, stream));
     } else {
         gemm(im.gemm_binding, im.act, W_down, nullptr, nullptr, c.K, f, 0, nullptr, im.partial);
         if (!status_) im.allreduce(im.allreduce_ctx, im.partial, (size_t)c.M * c.K, stream);
@@ -265,5 +307,101 @@ int b200_layer_forward(void* layer, const void* X_in, const void* W_q, const voi
 }
 
 uint32_t b200_layer_kernels_per_forward(void* layer) { return layer ? ((LayerHandle*)layer)->layer->kernels_per_forward() : 0; }
+
+int b200_layer_set_peer_exchange(void* layer, uint32_t rank, uint32_t world, void* const* recv, void* const* out0,
+                                 void* const* out1, void* const* flags) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!layer || !recv || !out0 || !out1 || !flags) return -2;
+    return ((LayerHandle*)layer)->layer->set_peer_exchange(rank, world, recv, out0, out1, flags) ? 0 : -4;
+}
+
+int b200_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!ptr || !handle64 || bytes == 0) return -2;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); return -5; }
+    cudaIpcMemHandle_t h;
+    if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
+        set_error(std::string("b200_peer_alloc: ") + cudaGetErrorString(cudaGetLastError()));
+        cudaFree(p);
+        return -5;
+    }
+    memcpy(handle64, &h, 64);
+    *ptr = p;
+    return 0;
+}
+
+int b200_peer_open(const unsigned char* handle64, void** ptr) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!handle64 || !ptr) return -2;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) { set_error(std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e)); cudaGetLastError(); return -5; }
+    return 0;
+}
+
+int b200_peer_close(void* ptr) { return ptr && cudaIpcCloseMemHandle(ptr) == cudaSuccess ? 0 : -2; }
+int b200_peer_free(void* ptr) { return ptr && cudaFree(ptr) == cudaSuccess ? 0 : -2; }
+
+namespace {
+uint32_t* g_peer_counter = nullptr;      // two words for the primitive entry points below
+bool peer_counter_ready() {
+    if (g_peer_counter) return true;
+    if (cudaMalloc((void**)&g_peer_counter, 16) != cudaSuccess) { cudaGetLastError(); g_peer_counter = nullptr; return false; }
+    cudaMemsetAsync(g_peer_counter, 0, 16, g.stream);
+    return true;
+}
+}  // namespace
+
+int b200_peer_gemm_scatter(const void* X, const void* W, int format, uint32_t M, uint32_t K, uint32_t N, uint32_t rank,
+                           uint32_t world, void* const* recv, void* const* flags, uint32_t epoch) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!X || !W || !recv || !flags || world < 1 || world > 8 || rank >= world) return -2;
+    if (M == 0 || K == 0 || N == 0 || M % world != 0) return -4;
+    if (!peer_counter_ready()) return -5;
+    qg::GemmArgs a; memset(&a, 0, sizeof(a));
+    a.format = format; a.X = X; a.W0 = W; a.M = M; a.N = N; a.K = K; a.layout = LAYOUT_STANDARD;
+    a.scatter.world = world; a.scatter.rank = rank; a.scatter.rows = M / world; a.scatter.epoch = epoch;
+    a.scatter.done_counter = g_peer_counter;
+    for (uint32_t o = 0; o < world; o++) { a.scatter.recv[o] = (float*)recv[o]; a.scatter.flags[o] = (uint32_t*)flags[o]; }
+    qg::Workspace ws;
+    ws.partial = (float*)g.ws_partial.p; ws.partial_floats = g.ws_partial.cap / sizeof(float); ws.counters = g.counters; ws.err = g.err_word;
+    cudaError_t e = qg::launch(a, ws, g.stream);
+    if (e != cudaSuccess) { set_error(std::string("gemm_scatter launch failed: ") + cudaGetErrorString(e)); return e == cudaErrorInvalidValue ? -4 : -6; }
+    g.launches += (uint64_t)qg::last_launch_count();
+    return 0;
+}
+
+int b200_peer_reduce_broadcast(uint32_t rank, uint32_t world, void* const* recv, void* const* out, void* const* flags,
+                               uint32_t epoch, const void* residual, uint32_t M, uint32_t K) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!recv || !out || !flags || !residual || world < 1 || world > 8 || rank >= world) return -2;
+    if (!peer_counter_ready()) return -5;
+    peer::Exchange x;
+    x.world = world; x.rank = rank; x.epoch = epoch; x.done_counter = g_peer_counter;
+    for (uint32_t o = 0; o < world; o++) { x.recv[o] = (float*)recv[o]; x.out[0][o] = out[o]; x.flags[o] = (uint32_t*)flags[o]; }
+    if (peer::reduce_broadcast(x, 0, residual, M, K, g.err_word, g.stream) != cudaSuccess) { cudaGetLastError(); return -4; }
+    g.launches++;
+    return 0;
+}
+
+int b200_peer_wait_rows(uint32_t rank, uint32_t world, void* const* flags, uint32_t epoch) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!flags || world < 1 || world > 8 || rank >= world) return -2;
+    peer::Exchange x;
+    x.world = world; x.rank = rank; x.epoch = epoch;
+    for (uint32_t o = 0; o < world; o++) x.flags[o] = (uint32_t*)flags[o];
+    if (peer::wait_rows(x, g.err_word, g.stream) != cudaSuccess) { cudaGetLastError(); return -6; }
+    g.launches++;
+    return 0;
+}
 
 }  // extern "C"

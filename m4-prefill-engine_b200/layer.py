@@ -61,6 +61,18 @@ def _bind_layer(lib) -> None:
     lib.b200_layer_forward.restype = ctypes.c_int
     lib.b200_layer_kernels_per_forward.argtypes = [vp]
     lib.b200_layer_kernels_per_forward.restype = ctypes.c_uint32
+    u32, pp = ctypes.c_uint32, ctypes.POINTER(ctypes.c_void_p)
+    lib.b200_peer_alloc.argtypes = [ctypes.c_size_t, pp, ctypes.c_char_p]
+    lib.b200_peer_open.argtypes = [ctypes.c_char_p, pp]
+    lib.b200_peer_close.argtypes = [vp]
+    lib.b200_peer_free.argtypes = [vp]
+    lib.b200_layer_set_peer_exchange.argtypes = [vp, u32, u32, pp, pp, pp, pp]
+    lib.b200_peer_gemm_scatter.argtypes = [vp, vp, ctypes.c_int, u32, u32, u32, u32, u32, pp, pp, u32]
+    lib.b200_peer_reduce_broadcast.argtypes = [u32, u32, pp, pp, pp, u32, vp, u32, u32]
+    lib.b200_peer_wait_rows.argtypes = [u32, u32, pp, u32]
+    for f in ("b200_peer_alloc", "b200_peer_open", "b200_peer_close", "b200_peer_free", "b200_layer_set_peer_exchange",
+              "b200_peer_gemm_scatter", "b200_peer_reduce_broadcast", "b200_peer_wait_rows"):
+        getattr(lib, f).restype = ctypes.c_int
     lib._layer_bound = True
 
 
@@ -102,6 +114,15 @@ class TransformerLayerCoordinator:
         if rc:
             raise RuntimeError(f"b200_layer_set_allreduce failed with status code {rc}")
 
+    def set_peer_exchange(self, rank: int, world: int, recv: list, out0: list, out1: list, flags: list) -> None:
+        """Lists of `world` device addresses indexed by rank (this rank's own buffers and the mapped buffers of the
+        others); see ``PeerExchange.setup`` for the usual way to get them."""
+        arr = lambda xs: (ctypes.c_void_p * world)(*xs)
+        rc = self.lib.b200_layer_set_peer_exchange(self._h, rank, world, arr(recv), arr(out0), arr(out1), arr(flags))
+        if rc:
+            raise RuntimeError(f"b200_layer_set_peer_exchange failed with status code {rc} "
+                               "(needs tp_size == world and M / world a multiple of 256)")
+
     def forward(self, X_in, W_q, W_k, W_v, W_o, W_gate, W_up, W_down, X_out) -> None:
         ts = (X_in, W_q, W_k, W_v, W_o, W_gate, W_up, W_down, X_out)
         if any(t.is_cuda for t in ts):
@@ -123,6 +144,67 @@ class TransformerLayerCoordinator:
             self.close()
         except Exception:
             pass
+
+
+class PeerExchange:
+    """Buffers of the tensor-parallel reduction over peer memory (one instance per rank and layer shape): this rank's
+    receive buffer, two result buffers and flag words, allocated so that the other processes of the node can map them,
+    plus the mappings of every other rank's buffers.  Handles travel through torch.distributed (any backend)."""
+
+    KINDS = ("recv", "out0", "out1", "flags")
+
+    def __init__(self, bridge: B200Bridge, M: int, K: int, rank: int, world: int) -> None:
+        self.bridge, self.rank, self.world = bridge, rank, world
+        _bind_layer(bridge.lib)
+        self.sizes = {"recv": M * K * 4, "out0": M * K * 2, "out1": M * K * 2, "flags": 64}
+        self.own: dict = {}
+        self.handles: dict = {}
+        self.ptrs: dict = {k: [0] * world for k in self.KINDS}
+        self._opened: list = []
+        for kind in self.KINDS:
+            p = ctypes.c_void_p()
+            h = ctypes.create_string_buffer(64)
+            rc = bridge.lib.b200_peer_alloc(self.sizes[kind], ctypes.byref(p), h)
+            if rc:
+                raise RuntimeError(f"b200_peer_alloc failed with status code {rc}")
+            self.own[kind] = p.value
+            self.handles[kind] = h.raw
+            self.ptrs[kind][rank] = p.value
+
+    def connect(self, all_handles: list) -> None:
+        """all_handles[r] = the ``handles`` dict of rank r (e.g. from dist.all_gather_object)."""
+        for r, hs in enumerate(all_handles):
+            if r == self.rank:
+                continue
+            for kind in self.KINDS:
+                p = ctypes.c_void_p()
+                rc = self.bridge.lib.b200_peer_open(hs[kind], ctypes.byref(p))
+                if rc:
+                    raise RuntimeError(f"b200_peer_open failed with status code {rc}: " +
+                                       (self.bridge.lib.b200_bridge_last_error_string() or b"").decode())
+                self.ptrs[kind][r] = p.value
+                self._opened.append(p.value)
+
+    @classmethod
+    def setup(cls, layer: "TransformerLayerCoordinator", group=None) -> "PeerExchange":
+        """Allocate, exchange handles over `group` and attach to `layer` (collective: every rank calls it)."""
+        import torch.distributed as dist
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        px = cls(layer.bridge, layer.config.M, layer.config.K, rank, world)
+        gathered: list = [None] * world
+        dist.all_gather_object(gathered, px.handles, group=group)
+        px.connect(gathered)
+        layer.set_peer_exchange(rank, world, px.ptrs["recv"], px.ptrs["out0"], px.ptrs["out1"], px.ptrs["flags"])
+        dist.barrier(group)
+        return px
+
+    def close(self) -> None:
+        for p in self._opened:
+            self.bridge.lib.b200_peer_close(p)
+        self._opened = []
+        for p in self.own.values():
+            self.bridge.lib.b200_peer_free(p)
+        self.own = {}
 
 
 def torch_allreduce_hook(bridge: B200Bridge, group=None) -> Callable[[int, int], None]:

@@ -1,0 +1,76 @@
+"""Tensor-parallel reduction over peer memory: the fused reduce-scatter epilogue of the row-split projection, the
+owner's reduce + residual + broadcast, and the wait for every rank's rows.
+
+On one GPU the ranks of a group are emulated phase by phase on the bridge's single stream (all scatters, then all
+reductions, then all waits), the "peer" buffers being ordinary local allocations: every flag a kernel waits for has
+been raised by a kernel that ran before it, so nothing waits on a later launch.  The two-process run over real IPC
+mappings is in test_tp_nccl_gpu.py."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import oracle as o
+from gpu_util import check, dev
+
+pytestmark = pytest.mark.gpu
+
+
+def _arr(xs):
+    return (ctypes.c_void_p * len(xs))(*[int(x) for x in xs])
+
+
+@pytest.mark.parametrize("world,fmt", [(2, o.Q4_0), (4, o.Q4_0), (2, o.Q4_K), (2, o.TERNARY_1_58)])
+def test_scatter_reduce_broadcast_emulated_ranks(bridge, pkg, world, fmt):
+    from m4_prefill_engine_b200.layer import _bind_layer, shard_cols
+    L = bridge.lib
+    _bind_layer(L)
+    M, K_total, N = 256 * world, 1024 * world, 384           # rows per rank = 256 (one token tile)
+    g = o.RefLcg(5 + world)
+    W = g.weights(fmt, K_total, N)
+    X = (g.activations(M, K_total).astype(np.float32) * 0.5).astype(np.float16)
+    R = g.activations(M, N)
+    gold = o.gemm_f64(fmt, X, W, N) + R.astype(np.float64)
+    k_loc = K_total // world
+    Xs = [dev(np.ascontiguousarray(X[:, r * k_loc:(r + 1) * k_loc])) for r in range(world)]
+    Ws = [dev(shard_cols(W, fmt, K_total, N, r, world)) for r in range(world)]
+    Rd = dev(R)
+    rows = M // world
+    recv = [torch.full((world, rows, N), float("nan"), dtype=torch.float32, device="cuda") for _ in range(world)]
+    out = [torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(world)]
+    torch.cuda.synchronize()
+    recv_p, out_p, flag_p = _arr([t.data_ptr() for t in recv]), _arr([t.data_ptr() for t in out]), _arr([t.data_ptr() for t in flags])
+    for epoch in (1, 2):                                       # twice: the flags only grow, buffers are reused
+        for r in range(world):
+            assert L.b200_peer_gemm_scatter(Xs[r].data_ptr(), Ws[r].data_ptr(), fmt, M, k_loc, N, r, world, recv_p, flag_p, epoch) == 0
+        for r in range(world):
+            assert L.b200_peer_reduce_broadcast(r, world, recv_p, out_p, flag_p, epoch, Rd.data_ptr(), M, N) == 0
+        for r in range(world):
+            assert L.b200_peer_wait_rows(r, world, flag_p, epoch) == 0
+        bridge.synchronize()
+        assert bridge.device_error() == 0
+        for r in range(world):
+            assert flags[r].cpu().tolist() == [epoch] * world + [0] * (8 - world) + [epoch] * world + [0] * (8 - world)
+            check(out[r].cpu().numpy(), gold, f"rank {r} world {world} fmt {fmt}")
+        assert all(torch.equal(out[0], out[r]) for r in range(1, world))     # every rank holds the same bits
+
+
+def test_scatter_rejects_unsupported_shapes(bridge, pkg):
+    from m4_prefill_engine_b200.layer import _bind_layer
+    L = bridge.lib
+    _bind_layer(L)
+    K, N = 512, 256
+    W = dev(o.RefLcg(1).weights(o.Q4_0, K, N))
+    buf = torch.zeros(1 << 20, dtype=torch.float32, device="cuda")
+    fl = torch.zeros(16, dtype=torch.int32, device="cuda")
+    p2 = _arr([buf.data_ptr()] * 2)
+    f2 = _arr([fl.data_ptr()] * 2)
+    X = torch.zeros(200, K, dtype=torch.float16, device="cuda")
+    # 100 rows per rank is not a whole number of token tiles; K = 96 has no tensor-core path: both refused, nothing runs
+    assert L.b200_peer_gemm_scatter(X.data_ptr(), W.data_ptr(), o.Q4_0, 200, K, N, 0, 2, p2, f2, 1) == -4
+    X2 = torch.zeros(512, 96, dtype=torch.float16, device="cuda")
+    assert L.b200_peer_gemm_scatter(X2.data_ptr(), W.data_ptr(), o.Q4_0, 512, 96, N, 0, 2, p2, f2, 1) == -4
+    bridge.synchronize()
+    assert int(fl.sum().item()) == 0

@@ -1,5 +1,6 @@
-"""Tensor-parallel decoder layer over NCCL on two GPUs (skipped where fewer are visible): both ranks must
-hold the same output, and it must match the CPU oracle's layer.  One process per GPU, 127.0.0.1 rendezvous."""
+"""Tensor-parallel decoder layer on two GPUs (skipped where fewer are visible), with the row-split projections
+reduced either by NCCL or by the fused exchange over peer memory: both ranks must hold the same output, and it must
+match the CPU oracle's layer.  One process per GPU, 127.0.0.1 rendezvous."""
 import os
 import subprocess
 import sys
@@ -18,14 +19,15 @@ import oracle as o
 from __graft_entry__ import load_package
 load_package()
 from m4_prefill_engine_b200.bridge import B200Bridge
-from m4_prefill_engine_b200.layer import TransformerLayerConfig, TransformerLayerCoordinator, shard_layer_weights, torch_allreduce_hook
-rank, world = int(sys.argv[3]), int(sys.argv[4])
+from m4_prefill_engine_b200.layer import (PeerExchange, TransformerLayerConfig, TransformerLayerCoordinator, shard_layer_weights,
+                                           torch_allreduce_hook)
+rank, world, mode = int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
 torch.cuda.set_device(rank)
 os.environ["NCCL_NVLS_ENABLE"] = "0"
 dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{sys.argv[2]}", rank=rank, world_size=world,
                         device_id=torch.device("cuda", rank))
 br = B200Bridge.get_instance(); assert br.init()
-M, K, H, Hkv, D, F = 70, 512, 4, 2, 128, 1024
+M, K, H, Hkv, D, F = (70 if mode == "nccl" else 512), 512, 4, 2, 128, 1024
 g = o.RefLcg(1337)
 shapes = {"q": (H * D, K), "k": (Hkv * D, K), "v": (Hkv * D, K), "o": (K, H * D), "gate": (F, K), "up": (F, K), "down": (K, F)}
 w = {n: g.q4_0_bench(k, r, 0.003, 0.0003) for n, (r, k) in shapes.items()}
@@ -34,9 +36,13 @@ cfg = TransformerLayerConfig(M=M, K=K, H=H, D=D, N_mlp=F, attn_scale=D ** -0.5, 
                              rope_theta=10000.0, tp_size=world)
 sw = {k: torch.from_numpy(v).cuda() for k, v in shard_layer_weights(o.Q4_0, w, cfg, rank, world).items()}
 layer = TransformerLayerCoordinator(cfg, br)
-layer.set_allreduce(torch_allreduce_hook(br))
+px = None
+if mode == "nccl":
+    layer.set_allreduce(torch_allreduce_hook(br))
+else:
+    px = PeerExchange.setup(layer)          # IPC mappings of the other rank's buffers
 Xd = torch.from_numpy(X).cuda(); Yd = torch.zeros_like(Xd)
-for _ in range(2):
+for _ in range(3):
     layer.forward(Xd, sw["q"], sw["k"], sw["v"], sw["o"], sw["gate"], sw["up"], sw["down"], Yd)
 br.synchronize(); torch.cuda.synchronize()
 assert br.device_error() == 0
@@ -48,17 +54,22 @@ assert diff <= 2 * 0.0078125, diff
 other = [torch.zeros_like(Yd) for _ in range(world)]
 dist.all_gather(other, Yd)
 assert all(torch.equal(other[0], t) for t in other), "ranks disagree"
-layer.close(); dist.barrier(); dist.destroy_process_group()
+dist.barrier()
+layer.close()
+if px is not None:
+    px.close()
+dist.barrier(); dist.destroy_process_group()
 print("rank", rank, "ok maxdiff", diff)
 '''
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_layer_tp2_nccl(tmp_path):
+@pytest.mark.parametrize("mode", ["nccl", "peer"])
+def test_layer_tp2(tmp_path, mode):
     script = tmp_path / "tp_worker.py"
     script.write_text(WORKER)
-    port = 29600 + (os.getpid() % 300)
-    procs = [subprocess.Popen([sys.executable, str(script), str(ROOT), str(port), str(r), "2"], stdout=subprocess.PIPE,
+    port = 29600 + (os.getpid() % 300) + (0 if mode == "nccl" else 301)
+    procs = [subprocess.Popen([sys.executable, str(script), str(ROOT), str(port), str(r), "2", mode], stdout=subprocess.PIPE,
                               stderr=subprocess.STDOUT, text=True) for r in range(2)]
     outs = []
     for p in procs:
