@@ -265,7 +265,17 @@ def time_layer(br, pkg, world: int, rank: int, steps: int, warmup: int, collecti
         layer.set_allreduce(torch_allreduce_hook(br))
     stream = torch.cuda.ExternalStream(br.lib.b200_bridge_stream())
     args = (X, w["q"], w["k"], w["v"], w["o"], w["gate"], w["up"], w["down"], Y)
-    for _ in range(max(3, warmup)):
+    layer.forward(*args)
+    br.synchronize()
+    if px is not None:
+        # a rank that did not hear from its peers within the wait limit has set the error word: every rank then
+        # drops the fused exchange together and the caller measures the NCCL path instead
+        bad = torch.tensor([1 if br.device_error() != 0 else 0], device=dev)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()):
+            layer.close(); px.close()
+            return {"error": "peer exchange timed out on the first layer", "device_error": br.device_error()}
+    for _ in range(max(3, warmup) - 1):
         layer.forward(*args)
     br.synchronize()
     if world > 1:
@@ -435,9 +445,12 @@ def run_ours(args) -> None:
         e2e_ok = all(bool(torch.isfinite(y.float()).all().item()) and float(y.float().abs().max()) > 0 for y in Yp)
 
     layer = time_layer(br, pkg, world, rank, max(3, min(args.steps, 20)), 3) if not args.no_layer else None
-    if layer is not None and world > 1:          # the same layer with NCCL all-reduces, for comparison
+    if layer is not None and world > 1:          # the same layer with NCCL all-reduces, for comparison (or as the fallback)
         nccl = time_layer(br, pkg, world, rank, max(3, min(args.steps, 20)), 3, collective="nccl")
-        if nccl is not None:
+        if "error" in layer:
+            nccl["peer_exchange_error"] = layer["error"]
+            layer = nccl
+        elif nccl is not None:
             layer["nccl_allreduce_ms"] = nccl["ms"]
 
     if rank == 0:

@@ -1,6 +1,6 @@
 // Reduce + residual + broadcast over peer memory (NVLink), the consumer side of the fused reduce-scatter in the
 // projection epilogue.  Data moves with plain peer stores; ranks signal each other with release stores to flag
-// words and wait with acquire loads, every wait bounded (about one second) and reported through the error word.
+// words and wait with acquire loads, every wait bounded (about ten seconds) and reported through the error word.
 #include "peer_reduce.cuh"
 
 #include <cuda_fp16.h>
@@ -9,7 +9,9 @@ namespace peer {
 
 namespace {
 
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
+// About ten seconds: ranks reach their first exchange with the skew of their first kernel loads, which can be a
+// large fraction of a second; a rank that never arrives still ends the wait.
+constexpr long long WAIT_LIMIT_CYCLES = 20000000000LL;
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
@@ -22,6 +24,9 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
 
 // true when flags[0 .. world) have all reached epoch; gives up after WAIT_LIMIT_CYCLES
 __device__ bool wait_flags(const uint32_t* flags, uint32_t world, uint32_t epoch, int* err, int code) {
+    // once any wait of this process has given up, later ones do not wait again (the host reads the error word and
+    // stops using the exchange; without this a broken group would cost ten seconds per kernel)
+    if (err && *reinterpret_cast<volatile int*>(err) != 0) return false;
     const long long t0 = clock64();
     for (uint32_t s = 0; s < world; s++) {
         while ((int32_t)(ld_acquire_sys(flags + s) - epoch) < 0) {
