@@ -88,6 +88,9 @@ def bind(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.b200_bridge_force_generic.argtypes = [_i]
     lib.b200_bridge_force_generic.restype = None
     lib.b200_bridge_force_legacy_attention.argtypes = [_i]
+    lib.b200_bridge_dispatch_gemm_grouped.argtypes = [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(ctypes.c_uint32),
+                                                      ctypes.c_uint32, _i, ctypes.c_uint32, ctypes.c_uint32, _i, ctypes.c_uint32]
+    lib.b200_bridge_dispatch_gemm_grouped.restype = _i
     lib.b200_bridge_force_legacy_attention.restype = None
     for name, args in _OPTIONAL.items():
         if hasattr(lib, name):

@@ -285,6 +285,36 @@ int b200_bridge_dispatch_swiglu(void* X, size_t Xb, void* Wg, void* Wu, size_t W
     return run_gemm(X, Xb, Wg, Wu, Wb, Out, Ob, format, M, K, F, LAYOUT_STANDARD, 0, 0, nullptr);
 }
 
+int b200_bridge_dispatch_gemm_grouped(const void* X, const void* const* W, void* const* Y, const uint32_t* N, uint32_t count,
+                                      int format, uint32_t M, uint32_t K, int layout, uint32_t D) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!X || !W || !Y || !N || count < 1 || count > 3) return -2;
+    if (format < 0 || format >= 6) return -3;
+    if (M == 0 || K == 0 || (K % 256) != 0) return -4;
+    if (layout != LAYOUT_STANDARD && layout != LAYOUT_DIRECT_HEAD) return -4;
+    for (uint32_t i = 0; i < count; i++) {
+        if (!W[i] || !Y[i] || !is_device_ptr(W[i]) || !is_device_ptr(Y[i])) return -2;
+        if (N[i] == 0 || (layout == LAYOUT_DIRECT_HEAD && (D == 0 || N[i] % D != 0))) return -4;
+    }
+    if (!is_device_ptr(X)) return -2;
+    qg::GemmArgs a;
+    memset(&a, 0, sizeof(a));
+    a.format = format; a.X = X; a.W0 = W[0]; a.Y = Y[0]; a.M = M; a.N = N[0]; a.K = K; a.layout = layout; a.D = D;
+    a.H = layout == LAYOUT_DIRECT_HEAD ? N[0] / D : 0;
+    a.n_extra = count - 1;
+    for (uint32_t i = 1; i < count; i++) { a.W_extra[i - 1] = W[i]; a.Y_extra[i - 1] = Y[i]; a.N_extra[i - 1] = N[i]; }
+    a.force_generic = g.force_generic;
+    qg::Workspace ws;
+    ws.partial = (float*)g.ws_partial.p; ws.partial_floats = g.ws_partial.cap / sizeof(float);
+    ws.counters = g.counters; ws.err = g.err_word;
+    cudaError_t e = qg::launch(a, ws, g.stream);
+    if (e == cudaErrorInvalidValue) { cudaGetLastError(); return -4; }
+    if (e != cudaSuccess) { set_error(std::string("kernel launch failed: ") + cudaGetErrorString(e)); return -6; }
+    g.launches += (uint64_t)qg::last_launch_count();
+    return 0;
+}
+
 int b200_bridge_register_weights(const void* host_ptr, size_t bytes) {
     std::lock_guard<std::mutex> lock(g.mu);
     if (!g.initialized) return -1;

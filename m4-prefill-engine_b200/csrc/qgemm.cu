@@ -113,6 +113,9 @@ struct Params {
     uint32_t* ws_counters;
     int* err;
     // planar layouts: per-64 scale plane followed by the bias plane (meta), or one fp16 scale per row
+    // grouped launch: weight tiles [0, grp_tiles[0]) belong to matrix 0 (W0 -> Y), the next grp_tiles[1] to matrix 1, ...
+    uint32_t groups, grp_tiles[3], grp_N[3];
+    __half* grp_Y[3];
     GemmArgs::Scatter scatter;   // fused reduce-scatter of fp32 partial sums to peer ranks (world == 0: off)
     uint32_t swiglu;             // 1: tiles are 64 gate rows (matrix 0) + their 64 up rows (matrix 1); output = silu(g) * u
     const uint8_t* meta0;
@@ -237,7 +240,7 @@ __device__ __forceinline__ void splitk_fixup(const Params& p, const Tile& t, uin
 template <int FMT>
 __global__ void __launch_bounds__(Cfg<FMT>::THREADS, 1)
 qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW0,
-             const __grid_constant__ CUtensorMap tmW1, const Params p) {
+             const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmW2, const Params p) {
     using C = Cfg<FMT>;
     using Cd = cdc::Codec<FMT>;
     constexpr int ROW_BYTES = Cd::ROW_BYTES;
@@ -303,7 +306,11 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         // ---------------- packed-weight producer ----------------
         // The whole warp walks the loop (only lane 0 issues): a lone lane looping while its 31 siblings
         // already sit at the final barrier gets scheduled far less often than a converged warp.
-        if (lane == 0) { ptx::prefetch_tensormap(&tmW0); if (p.swiglu) ptx::prefetch_tensormap(&tmW1); }
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&tmW0);
+            if (p.swiglu || p.groups > 1u) ptx::prefetch_tensormap(&tmW1);
+            if (p.groups > 2u) ptx::prefetch_tensormap(&tmW2);
+        }
         uint32_t rs = 0, rph = 0, wtr = 0;
         (void)wtr;
         bool ok = true;
@@ -320,6 +327,12 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                         const int y = (int)(t.wt * GATE_ROWS);
                         ptx::tma_load_2d(sRaw + rs * RAW_TILE_BYTES, &tmW0, &raw_full[rs], x, y);
                         ptx::tma_load_2d(sRaw + rs * RAW_TILE_BYTES + GATE_ROWS * ROW_BYTES, &tmW1, &raw_full[rs], x, y);
+                    } else if (p.groups > 1u) {
+                        // grouped launch: this weight tile belongs to one of up to three matrices
+                        uint32_t wl = t.wt;
+                        const CUtensorMap* tm = &tmW0;
+                        if (wl >= p.grp_tiles[0]) { wl -= p.grp_tiles[0]; tm = &tmW1; if (wl >= p.grp_tiles[1]) { wl -= p.grp_tiles[1]; tm = &tmW2; } }
+                        ptx::tma_load_2d(sRaw + rs * RAW_TILE_BYTES, tm, &raw_full[rs], x, (int)(wl * W_TILE));
                     } else {
                         ptx::tma_load_2d(sRaw + rs * RAW_TILE_BYTES, &tmW0, &raw_full[rs], x, (int)(t.wt * W_TILE));
                     }
@@ -501,11 +514,19 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             if (!ptx::mbar_wait<256>(&tm_full[buf], (it >> 1) & 1u, abort_flag, p.err, 108)) break;
             if (et == 0) QTRC(6, it, 0);
             ptx::tc_fence_after_sync();
-            const uint32_t n = t.wt * W_TILE + q * 32 + lane;
-            const bool n_ok = n < p.N;
+            // grouped launch: the matrix this tile belongs to decides the output buffer and its width
+            uint32_t wt_l = t.wt, Ng = p.N;
+            __half* Yg = p.Y;
+            if (p.groups > 1u) {
+                uint32_t gi = 0;
+                if (wt_l >= p.grp_tiles[0]) { wt_l -= p.grp_tiles[0]; gi = 1; if (wt_l >= p.grp_tiles[1]) { wt_l -= p.grp_tiles[1]; gi = 2; } }
+                Ng = p.grp_N[gi]; Yg = p.grp_Y[gi];
+            }
+            const uint32_t n = wt_l * W_TILE + q * 32 + lane;
+            const bool n_ok = n < Ng;
             // output element (tok, n) lives at out_base + tok * out_stride in either layout; the head split
             // (a division by a run-time D) is done once per tile here, never per element
-            const size_t out_stride = (p.layout == 1) ? (size_t)p.D : (size_t)p.N;
+            const size_t out_stride = (p.layout == 1) ? (size_t)p.D : (size_t)Ng;
             const size_t out_base = (p.layout == 1) ? ((size_t)(n / p.D) * p.M * p.D + (n % p.D)) : (size_t)n;
             const uint32_t taddr = tmem_base + ((q * 32u) << 16) + buf * ACC_STRIDE;
             const uint32_t tok0 = t.tt * p.T;
@@ -613,7 +634,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                         for (int j = 0; j < 16; j++)
                             if ((uint32_t)j < lim) p.Y[o + j * out_stride] = __float2half_rn(f[j] + __half2float(res[j]));
                     } else {
-                        __half* dst = p.Y + out_base + (size_t)(tok0 + c0) * out_stride;
+                        __half* dst = Yg + out_base + (size_t)(tok0 + c0) * out_stride;
                         if (lim >= 16u) {                                       // whole batch exists: no per-store predicate
 #pragma unroll
                             for (int j = 0; j < 16; j++) dst[j * out_stride] = __float2half_rn(f[j]);
@@ -876,6 +897,7 @@ Plan make_plan(const GemmArgs& a) {
     pl.T = (per + 15u) & ~15u;
     const uint32_t rows_per_tile = a.W1 ? GATE_ROWS : W_TILE;    // output features per tile
     pl.n_w_tiles = (a.N + rows_per_tile - 1) / rows_per_tile;
+    for (uint32_t e = 0; e < a.n_extra && e < 2u; e++) pl.n_w_tiles += (a.N_extra[e] + W_TILE - 1) / W_TILE;   // grouped launch
     const uint32_t chunks = a.K / KCHUNK;
     pl.k_splits = 1;
     if (!a.W1 && !a.scatter.world) {       // (the fused reduce-scatter epilogue writes whole tiles: no K split)
@@ -898,7 +920,7 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     const Plan pl = make_plan(a);
     const int rb = cdc::Codec<FMT>::ROW_BYTES;
     const uint64_t w_row_bytes = (uint64_t)(a.K / KCHUNK) * rb;
-    CUtensorMap tmX, tmW0, tmW1;
+    CUtensorMap tmX, tmW0, tmW1, tmW2;
     if (!make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.X, a.K, a.M, (uint64_t)a.K * 2, KSTEP, pl.T,
                      CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
@@ -906,7 +928,18 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     const uint32_t box_rows = a.W1 ? GATE_ROWS : W_TILE;
     if (!make_map_2d(&tmW0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.W0, w_row_bytes, a.N, w_row_bytes, rb, box_rows, wsw))
         return cudaErrorInvalidValue;
-    if (!make_map_2d(&tmW1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.W1 ? a.W1 : a.W0, w_row_bytes, a.N, w_row_bytes, rb, box_rows, wsw))
+    // second / third map: the up matrix of a SwiGLU launch, or the extra matrices of a grouped launch
+    const bool grouped = a.n_extra > 0;
+    if (grouped && (a.n_extra > 2 || a.W1 || a.residual || a.partial_out || a.scatter.world || pl.k_splits != 1 ||
+                    cdc::Codec<FMT>::META_WORDS != 0 || cdc::Codec<FMT>::ROW_SCALE))
+        return cudaErrorInvalidValue;
+    const void* w1 = a.W1 ? a.W1 : (grouped ? a.W_extra[0] : a.W0);
+    const uint32_t n1 = grouped ? a.N_extra[0] : a.N;
+    const void* w2 = a.n_extra > 1 ? a.W_extra[1] : a.W0;
+    const uint32_t n2 = a.n_extra > 1 ? a.N_extra[1] : a.N;
+    if (!make_map_2d(&tmW1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w1, w_row_bytes, n1, w_row_bytes, rb, box_rows, wsw))
+        return cudaErrorInvalidValue;
+    if (!make_map_2d(&tmW2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2, w_row_bytes, n2, w_row_bytes, rb, box_rows, wsw))
         return cudaErrorInvalidValue;
 
     Params p;
@@ -917,6 +950,13 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     p.b_stages = b_stages_for<FMT>(pl.T, a.W1 != nullptr);
     p.Y = (__half*)a.Y; p.residual = (const __half*)a.residual; p.partial_out = a.partial_out;
     p.scatter = a.scatter;
+    p.groups = 1u + a.n_extra;
+    p.grp_tiles[0] = (a.N + W_TILE - 1) / W_TILE; p.grp_N[0] = a.N; p.grp_Y[0] = (__half*)a.Y;
+    for (uint32_t e = 0; e < 2u; e++) {
+        const bool on = e < a.n_extra;
+        p.grp_tiles[1 + e] = on ? (a.N_extra[e] + W_TILE - 1) / W_TILE : 0u;
+        p.grp_N[1 + e] = on ? a.N_extra[e] : 0u; p.grp_Y[1 + e] = on ? (__half*)a.Y_extra[e] : nullptr;
+    }
     if (a.scatter.world && (pl.k_splits != 1 || a.W1 || a.scatter.rows % pl.T != 0 || a.scatter.rows * a.scatter.world != a.M)) return cudaErrorInvalidValue;
     p.layout = (uint32_t)a.layout; p.H = a.H; p.D = a.D ? a.D : 1;
     p.ws_partial = ws.partial; p.ws_counters = ws.counters; p.err = ws.err;
@@ -952,7 +992,7 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, qgemm_kernel<FMT>, tmX, tmW0, tmW1, p);
+    return cudaLaunchKernelEx(&cfg, qgemm_kernel<FMT>, tmX, tmW0, tmW1, tmW2, p);
 }
 
 cudaError_t dispatch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t s) {
@@ -978,6 +1018,8 @@ bool fast_path_ok(const GemmArgs& a) {
     if (row_bytes_256(a.format) == 0) return false;
     if (a.K == 0 || a.K % KCHUNK != 0) return false;
     if (((uintptr_t)a.X & 15u) || ((uintptr_t)a.W0 & 15u) || (a.W1 && ((uintptr_t)a.W1 & 15u))) return false;
+    for (uint32_t e = 0; e < a.n_extra && e < 2u; e++)
+        if (!a.W_extra[e] || ((uintptr_t)a.W_extra[e] & 15u) || !a.Y_extra[e] || a.N_extra[e] == 0) return false;
     if (a.M == 0 || a.N == 0) return false;
     return encode_fn() != nullptr;
 }
@@ -992,7 +1034,7 @@ size_t workspace_floats(const GemmArgs& a) {
 cudaError_t launch(const GemmArgs& a, const Workspace& ws, cudaStream_t stream) {
     g_last_launches = 1;
     if (fast_path_ok(a)) return dispatch_fast(a, ws, stream);
-    if (a.scatter.world) return cudaErrorInvalidValue;      // the fused reduce-scatter exists on the tensor-core path only
+    if (a.scatter.world || a.n_extra) return cudaErrorInvalidValue;   // fused reduce-scatter and grouped launches exist on the tensor-core path only
     Params p;
     memset(&p, 0, sizeof(p));
     p.M = a.M; p.N = a.N; p.K = a.K;

@@ -19,6 +19,12 @@ struct GemmArgs {
     const void* residual;     // optional fp16 [M][N] added in the epilogue (standard layout only)
     float* partial_out;       // optional fp32 [M][N]: write raw accumulators instead of fp16 Y
     int force_generic;        // testing hook: use the CUDA-core fallback kernel
+    // Grouped launch: up to two more projections of the same X (same K, format, layout and D) run in the same
+    // grid, their weight tiles queued behind those of W0.  n_extra == 0: off.  Plain fp16 outputs only.
+    uint32_t n_extra;
+    const void* W_extra[2];
+    void* Y_extra[2];
+    uint32_t N_extra[2];
     // Tensor-parallel reduce-scatter fused into the epilogue (row-split projections): instead of one local fp32
     // [M][N] buffer, token rows [o * rows, (o + 1) * rows) go to rank o's receive buffer, slot `rank`, through
     // peer-mapped pointers.  When the grid's last CTA is done it raises flag `rank` in every rank's flag array to

@@ -155,9 +155,23 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
     // 1. attention block
     const void* x_attn = X_in;
     if (c.rms_eps > 0.0f) { check(lops::rmsnorm(X_in, im.norm1, im.xn, c.M, c.K, c.rms_eps, stream)); x_attn = im.xn; }
-    gemm(im.head_binding, x_attn, W_q, nullptr, im.q, hq * c.D, c.K, hq, nullptr, nullptr);
-    gemm(im.head_binding, x_attn, W_k, nullptr, im.k, hkv * c.D, c.K, hkv, nullptr, nullptr);
-    gemm(im.head_binding, x_attn, W_v, nullptr, im.v, hkv * c.D, c.K, hkv, nullptr, nullptr);
+    // Q, K and V read the same activations: one grouped launch (their weight tiles share the persistent grid, so
+    // the two narrow projections do not each leave most SMs idle); separate launches where that is not available
+    bool qkv_done = false;
+    if (!status_) {
+        qg::GemmArgs a; memset(&a, 0, sizeof(a));
+        a.format = im.head_binding.format; a.X = x_attn; a.W0 = W_q; a.Y = im.q; a.M = c.M; a.N = hq * c.D; a.K = c.K;
+        a.layout = im.head_binding.layout; a.H = hq; a.D = c.D;
+        a.n_extra = 2; a.W_extra[0] = W_k; a.W_extra[1] = W_v; a.Y_extra[0] = im.k; a.Y_extra[1] = im.v;
+        a.N_extra[0] = a.N_extra[1] = hkv * c.D;
+        if (qg::launch(a, ws, stream) == cudaSuccess) { qkv_done = true; launches_ += (uint32_t)qg::last_launch_count(); }
+        else cudaGetLastError();
+    }
+    if (!qkv_done) {
+        gemm(im.head_binding, x_attn, W_q, nullptr, im.q, hq * c.D, c.K, hq, nullptr, nullptr);
+        gemm(im.head_binding, x_attn, W_k, nullptr, im.k, hkv * c.D, c.K, hkv, nullptr, nullptr);
+        gemm(im.head_binding, x_attn, W_v, nullptr, im.v, hkv * c.D, c.K, hkv, nullptr, nullptr);
+    }
     if (c.rope_theta > 0.0f) {
         check(lops::rope(im.q, hq, c.M, c.D, c.rope_theta, 0, stream));
         check(lops::rope(im.k, hkv, c.M, c.D, c.rope_theta, 0, stream));

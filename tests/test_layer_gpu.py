@@ -61,7 +61,7 @@ def test_layer_reference_fixture(bridge, pkg):
     Y, n = run_layer(pkg, dict(M=24, K=256, H=4, D=64, N_mlp=512, attn_scale=0.125), X, w)
     # the reference's pipeline bench passes at 0.05 against this gold (bench_8b_engine.mm:694)
     assert np.abs(Y.astype(np.float32) - z["Y"].view(np.float16).astype(np.float32)).max() <= TOL
-    assert n == 7      # q, k, v, attention, o(+residual), swiglu, down(+residual): residual adds and transposes are fused away
+    assert n in (5, 7)   # q+k+v (one grouped launch where the shape fills the GPU, else three), attention, o(+residual), swiglu, down(+residual): residual adds and transposes are fused away
 
 
 @pytest.mark.parametrize("fmt", [o.Q4_0, o.MLX_4BIT, o.Q4_K, o.TERNARY_1_58])
