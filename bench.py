@@ -260,7 +260,7 @@ def time_layer(br, pkg, world: int, rank: int, steps: int, warmup: int, collecti
     px = None
     if world > 1 and collective == "peer" and (c["M"] // world) % 256 == 0:
         px = PeerExchange.setup(layer)           # reduce-scatter fused into the projection epilogue, over peer memory
-    elif world > 1:
+    if world > 1 and px is None:                 # shape not supported, or peer mappings not available on this node
         collective = "nccl"
         layer.set_allreduce(torch_allreduce_hook(br))
     stream = torch.cuda.ExternalStream(br.lib.b200_bridge_stream())

@@ -186,16 +186,33 @@ class PeerExchange:
                 self._opened.append(p.value)
 
     @classmethod
-    def setup(cls, layer: "TransformerLayerCoordinator", group=None) -> "PeerExchange":
-        """Allocate, exchange handles over `group` and attach to `layer` (collective: every rank calls it)."""
+    def setup(cls, layer: "TransformerLayerCoordinator", group=None) -> Optional["PeerExchange"]:
+        """Allocate, exchange handles over `group` and attach to `layer` (collective: every rank calls it).  Returns
+        None on every rank when any rank could not allocate, map a peer's buffers or attach them (the ranks agree
+        through one all-gather), so that the group can fall back to ``set_allreduce`` together."""
         import torch.distributed as dist
         rank, world = dist.get_rank(group), dist.get_world_size(group)
-        px = cls(layer.bridge, layer.config.M, layer.config.K, rank, world)
+        px, err = None, None
+        try:
+            px = cls(layer.bridge, layer.config.M, layer.config.K, rank, world)
+        except Exception as e:                      # noqa: BLE001 - reported to the group below
+            err = repr(e)
         gathered: list = [None] * world
-        dist.all_gather_object(gathered, px.handles, group=group)
-        px.connect(gathered)
-        layer.set_peer_exchange(rank, world, px.ptrs["recv"], px.ptrs["out0"], px.ptrs["out1"], px.ptrs["flags"])
-        dist.barrier(group)
+        dist.all_gather_object(gathered, None if err else px.handles, group=group)
+        if err is None and all(h is not None for h in gathered):
+            try:
+                px.connect(gathered)
+                layer.set_peer_exchange(rank, world, px.ptrs["recv"], px.ptrs["out0"], px.ptrs["out1"], px.ptrs["flags"])
+            except Exception as e:                  # noqa: BLE001
+                err = repr(e)
+        else:
+            err = err or "another rank failed to allocate"
+        status: list = [None] * world
+        dist.all_gather_object(status, err, group=group)
+        if any(s is not None for s in status):
+            if px is not None:
+                px.close()
+            return None
         return px
 
     def close(self) -> None:

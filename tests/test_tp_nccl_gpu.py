@@ -41,6 +41,7 @@ if mode == "nccl":
     layer.set_allreduce(torch_allreduce_hook(br))
 else:
     px = PeerExchange.setup(layer)          # IPC mappings of the other rank's buffers
+    assert px is not None, "peer mappings not available"
 Xd = torch.from_numpy(X).cuda(); Yd = torch.zeros_like(Xd)
 for _ in range(3):
     layer.forward(Xd, sw["q"], sw["k"], sw["v"], sw["o"], sw["gate"], sw["up"], sw["down"], Yd)
