@@ -135,6 +135,8 @@ uint64_t b200_bridge_kernel_launches(void);
 void* b200_bridge_stream(void);
 
 /* Testing hook: non-zero routes every GEMM through the CUDA-core fallback kernel. */
+/* Clears the device error word after the caller has read it with b200_bridge_device_error (waits for the streams). */
+int b200_bridge_clear_device_error(void);
 void b200_bridge_force_generic(int on);
 /* Up to three projections of the same activations in one launch (the Q, K and V projections of a layer): Y[i] =
  * X . W[i]^T with W[i] packed [N[i]][K/blk] in `format`, outputs in `layout` (LAYOUT_DIRECT_HEAD: [N[i]/D][M][D]).

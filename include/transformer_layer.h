@@ -128,4 +128,8 @@ int b200_peer_gemm_scatter(const void* X, const void* W, int format, uint32_t M,
 int b200_peer_reduce_broadcast(uint32_t rank, uint32_t world, void* const* recv, void* const* out, void* const* flags,
                                uint32_t epoch, const void* residual, uint32_t M, uint32_t K);
 int b200_peer_wait_rows(uint32_t rank, uint32_t world, void* const* flags, uint32_t epoch);
+/* Bound of the exchange's flag waits in milliseconds (0 restores the default of about ten seconds).  A wait that runs
+ * out sets device error 301 (arrival flags) or 302 (result rows) and the kernel returns; later waits return at once
+ * until the error word is cleared. */
+void b200_peer_set_wait_limit_ms(unsigned ms);
 }

@@ -401,6 +401,13 @@ int b200_bridge_device_error(void) {
     return v;
 }
 
+int b200_bridge_clear_device_error(void) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    sync_all_streams(g.stream, g.stream_in, g.stream_out);
+    return cudaMemset(g.err_word, 0, sizeof(int)) == cudaSuccess ? 0 : -6;
+}
+
 const char* b200_bridge_last_error_string(void) { return g.last_error.c_str(); }
 uint64_t b200_bridge_kernel_launches(void) { return g.launches; }
 void* b200_bridge_stream(void) { return (void*)g.stream; }

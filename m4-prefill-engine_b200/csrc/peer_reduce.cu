@@ -11,7 +11,8 @@ namespace {
 
 // About ten seconds: ranks reach their first exchange with the skew of their first kernel loads, which can be a
 // large fraction of a second; a rank that never arrives still ends the wait.
-constexpr long long WAIT_LIMIT_CYCLES = 20000000000LL;
+constexpr long long DEFAULT_WAIT_LIMIT_CYCLES = 20000000000LL;
+long long g_wait_limit_cycles = DEFAULT_WAIT_LIMIT_CYCLES;      // host copy, passed to every launch
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
@@ -23,14 +24,14 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
 }
 
 // true when flags[0 .. world) have all reached epoch; gives up after WAIT_LIMIT_CYCLES
-__device__ bool wait_flags(const uint32_t* flags, uint32_t world, uint32_t epoch, int* err, int code) {
+__device__ bool wait_flags(const uint32_t* flags, uint32_t world, uint32_t epoch, int* err, int code, long long limit) {
     // once any wait of this process has given up, later ones do not wait again (the host reads the error word and
     // stops using the exchange; without this a broken group would cost ten seconds per kernel)
     if (err && *reinterpret_cast<volatile int*>(err) != 0) return false;
     const long long t0 = clock64();
     for (uint32_t s = 0; s < world; s++) {
         while ((int32_t)(ld_acquire_sys(flags + s) - epoch) < 0) {
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            if (clock64() - t0 > limit) {
                 if (err) atomicCAS(err, 0, code);
                 return false;
             }
@@ -49,11 +50,12 @@ struct ReduceParams {
     const uint32_t* my_flags;
     uint32_t* done_counter;
     int* err;
+    long long wait_limit;
 };
 
 __global__ void __launch_bounds__(256) reduce_broadcast_kernel(const ReduceParams p) {
     __shared__ uint32_t ok_s;
-    if (threadIdx.x == 0) ok_s = wait_flags(p.my_flags, p.world, p.epoch, p.err, 301) ? 1u : 0u;
+    if (threadIdx.x == 0) ok_s = wait_flags(p.my_flags, p.world, p.epoch, p.err, 301, p.wait_limit) ? 1u : 0u;
     __syncthreads();
     if (ok_s) {
         const size_t n4 = (size_t)p.rows * p.K / 4;               // K % 4 == 0 (K is a multiple of 32)
@@ -88,8 +90,8 @@ __global__ void __launch_bounds__(256) reduce_broadcast_kernel(const ReduceParam
     }
 }
 
-__global__ void wait_rows_kernel(const uint32_t* my_flags, uint32_t world, uint32_t epoch, int* err) {
-    if (threadIdx.x == 0) wait_flags(my_flags + 8, world, epoch, err, 302);
+__global__ void wait_rows_kernel(const uint32_t* my_flags, uint32_t world, uint32_t epoch, int* err, long long limit) {
+    if (threadIdx.x == 0) wait_flags(my_flags + 8, world, epoch, err, 302, limit);
 }
 
 }  // namespace
@@ -105,6 +107,7 @@ cudaError_t reduce_broadcast(const Exchange& x, int which_out, const void* resid
     p.my_flags = x.flags[x.rank];
     p.done_counter = x.done_counter + 1;
     p.err = err;
+    p.wait_limit = g_wait_limit_cycles;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -113,8 +116,10 @@ cudaError_t reduce_broadcast(const Exchange& x, int which_out, const void* resid
 }
 
 cudaError_t wait_rows(const Exchange& x, int* err, cudaStream_t stream) {
-    wait_rows_kernel<<<1, 32, 0, stream>>>(x.flags[x.rank], x.world, x.epoch, err);
+    wait_rows_kernel<<<1, 32, 0, stream>>>(x.flags[x.rank], x.world, x.epoch, err, g_wait_limit_cycles);
     return cudaGetLastError();
 }
+
+void set_wait_limit_ms(unsigned ms) { g_wait_limit_cycles = ms ? (long long)ms * 2000000LL : DEFAULT_WAIT_LIMIT_CYCLES; }
 
 }  // namespace peer

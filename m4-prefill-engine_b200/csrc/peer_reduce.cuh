@@ -23,4 +23,7 @@ cudaError_t reduce_broadcast(const Exchange& x, int which_out, const void* resid
 // Returns once every rank's rows of the current epoch are in this rank's out buffer (bounded wait).
 cudaError_t wait_rows(const Exchange& x, int* err, cudaStream_t stream);
 
+// Bound of the flag waits in milliseconds at about 2 GHz (0 = the default of ten seconds).
+void set_wait_limit_ms(unsigned ms);
+
 }  // namespace peer

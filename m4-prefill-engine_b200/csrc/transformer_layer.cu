@@ -406,6 +406,8 @@ int b200_peer_reduce_broadcast(uint32_t rank, uint32_t world, void* const* recv,
     return 0;
 }
 
+void b200_peer_set_wait_limit_ms(unsigned ms) { peer::set_wait_limit_ms(ms); }
+
 int b200_peer_wait_rows(uint32_t rank, uint32_t world, void* const* flags, uint32_t epoch) {
     std::lock_guard<std::mutex> lock(g.mu);
     if (!g.initialized) return -1;

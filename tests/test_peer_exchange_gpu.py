@@ -74,3 +74,51 @@ def test_scatter_rejects_unsupported_shapes(bridge, pkg):
     assert L.b200_peer_gemm_scatter(X2.data_ptr(), W.data_ptr(), o.Q4_0, 512, 96, N, 0, 2, p2, f2, 1) == -4
     bridge.synchronize()
     assert int(fl.sum().item()) == 0
+
+
+def test_wait_runs_out_and_reports(bridge, pkg):
+    """Failure detection without a fault: a rank waits for rows that no peer will ever write (a flag nothing sets),
+    with the wait limit lowered to 50 ms.  The kernel gives up, the host reads error 302, the waits that follow return
+    at once, and after clearing the error word the same context runs a projection correctly."""
+    import time
+    from m4_prefill_engine_b200.layer import _bind_layer
+    L = bridge.lib
+    _bind_layer(L)
+    L.b200_peer_set_wait_limit_ms.argtypes = [ctypes.c_uint]
+    L.b200_peer_set_wait_limit_ms.restype = None
+    flags = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(2)]
+    fp = _arr([f.data_ptr() for f in flags])
+    assert bridge.device_error() == 0
+    L.b200_peer_set_wait_limit_ms(50)
+    try:
+        t0 = time.perf_counter()
+        assert L.b200_peer_wait_rows(0, 2, fp, 7) == 0          # enqueues; nobody ever raises epoch 7
+        bridge.synchronize()
+        dt = time.perf_counter() - t0
+        assert bridge.device_error() == 302
+        assert 0.02 < dt < 5.0
+        t0 = time.perf_counter()
+        for _ in range(5):                                       # a wait that already failed is not repeated
+            assert L.b200_peer_wait_rows(0, 2, fp, 7) == 0
+        bridge.synchronize()
+        assert time.perf_counter() - t0 < 0.05 * 5
+        # the arrival side: a reduction whose sources never arrive reports 301 and writes nothing
+        assert L.b200_bridge_clear_device_error() == 0
+        assert bridge.device_error() == 0
+        M, K = 512, 256
+        recv = [torch.zeros(2, M // 2, K, dtype=torch.float32, device="cuda") for _ in range(2)]
+        out = [torch.full((M, K), 3.0, dtype=torch.float16, device="cuda") for _ in range(2)]
+        res = torch.zeros(M, K, dtype=torch.float16, device="cuda")
+        assert L.b200_peer_reduce_broadcast(0, 2, _arr([t.data_ptr() for t in recv]), _arr([t.data_ptr() for t in out]), fp, 9,
+                                            res.data_ptr(), M, K) == 0
+        bridge.synchronize()
+        assert bridge.device_error() == 301
+        assert float(out[0].min().item()) == 3.0 and float(out[1].min().item()) == 3.0
+    finally:
+        L.b200_peer_set_wait_limit_ms(0)
+        assert L.b200_bridge_clear_device_error() == 0
+    # the context is intact: an ordinary projection still matches the oracle
+    from gpu_util import run_gemm
+    X, W = o.baseline_inputs(o.Q4_0, 33, 512, 128, 3)
+    check(run_gemm(bridge, o.Q4_0, X, W, 128), o.gemm_f64(o.Q4_0, X, W, 128), "after a timed-out wait")
+    assert bridge.device_error() == 0
