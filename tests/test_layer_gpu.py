@@ -94,6 +94,39 @@ def test_layer_llama_style(bridge, pkg, host_io):
     assert diff.max() <= 2 * TOL, f"max-abs {diff.max()}"
 
 
+def test_layer_8b_full_size(bridge, pkg):
+    """The benchmark's layer at its full size (M=2048, K=4096, 32/8 heads, D=128, F=14336, Q4_0): grouped Q/K/V launch,
+    tensor-memory attention over 16 key tiles, residual epilogues.  Checked through two size-independent properties:
+    a causal layer's first rows depend on the first tokens only, so rows [0, 48) must match the oracle's layer run on
+    48 tokens; and changing the tokens from 1500 on must leave every earlier output row bit-identical."""
+    M, K, H, Hkv, D, F = 2048, 4096, 32, 8, 128, 14336
+    rng = np.random.default_rng(7)
+
+    def q4_0(rows, cols):                     # the reference layer's scale range (bench_8b_engine.mm:44-53)
+        nb = rows * cols // 32
+        W = rng.integers(0, 256, (nb, 18), dtype=np.uint8)
+        W[:, 0:2] = rng.uniform(0.0003, 0.0033, nb).astype(np.float16).view(np.uint8).reshape(-1, 2)
+        return W.reshape(-1)
+    w = {"q": q4_0(H * D, K), "k": q4_0(Hkv * D, K), "v": q4_0(Hkv * D, K), "o": q4_0(K, H * D), "gate": q4_0(F, K), "up": q4_0(F, K),
+         "down": q4_0(K, F)}
+    X = (rng.standard_normal((M, K), dtype=np.float32) * 0.35).astype(np.float16)
+    n1 = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    n2 = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    kw = dict(M=M, K=K, H=H, D=D, N_mlp=F, attn_scale=D ** -0.5, num_kv_heads=Hkv, rms_eps=1e-5, rope_theta=500000.0, kv_q8_0=True)
+    Y, n = run_layer(pkg, kw, X, w, (n1, n2))
+    assert n == 11 and np.all(np.isfinite(Y.astype(np.float32)))
+    R = 48
+    gold = o.layer(o.Q4_0, X[:R], w["q"], w["k"], w["v"], w["o"], w["gate"], w["up"], w["down"], H, Hkv, D, F, D ** -0.5,
+                   rms_eps=1e-5, norm1=n1, norm2=n2, rope_theta=500000.0, kv_q8=True)
+    diff = np.abs(Y[:R].astype(np.float64) - gold.astype(np.float64))
+    assert diff.max() <= 2 * TOL, f"max-abs {diff.max()}"
+    X2 = X.copy()
+    X2[1500:] = (rng.standard_normal((M - 1500, K), dtype=np.float32) * 0.35).astype(np.float16)
+    Y2, _ = run_layer(pkg, kw, X2, w, (n1, n2))
+    assert np.array_equal(Y[:1500].view(np.uint16), Y2[:1500].view(np.uint16))
+    assert not np.array_equal(Y[1500:].view(np.uint16), Y2[1500:].view(np.uint16))
+
+
 def test_rmsnorm_and_rope_ops(bridge):
     L = bridge.lib
     import ctypes
