@@ -237,7 +237,8 @@ __device__ __forceinline__ void splitk_fixup(const Params& p, const Tile& t, uin
     }
 }
 
-template <int FMT>
+// RESID: the launch adds a residual in the epilogue (its prefetch ring costs registers the plain launch should not pay for)
+template <int FMT, bool RESID>
 __global__ void __launch_bounds__(Cfg<FMT>::THREADS, 1)
 qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW0,
              const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmW2, const Params p) {
@@ -541,7 +542,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 const uint32_t owner = tok0 / p.scatter.rows;
                 partial_dst = p.scatter.recv[owner] + ((ptrdiff_t)p.scatter.rank - (ptrdiff_t)owner) * (ptrdiff_t)p.scatter.rows * (ptrdiff_t)p.N;
             }
-            const int mode = p.k_splits > 1 ? 0 : (partial_dst ? 1 : (p.residual ? 2 : 3));
+            const int mode = p.k_splits > 1 ? 0 : (partial_dst ? 1 : ((RESID && p.residual) ? 2 : 3));
             // integer-valued codecs: the row's scale multiplies the fp32 accumulator (before SiLU, before split-K sums)
             float rsc0 = 1.0f;
             if (Cd::ROW_SCALE && !p.swiglu) rsc0 = n_ok ? __half2float(p.row_scale0[n]) : 0.0f;
@@ -587,27 +588,23 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                     }
                 }
             } else {
-            // Residual epilogue: the 16 residual values of a batch are requested one batch ahead, all at once and
-            // with no store in between (Y may alias the residual, so the compiler would otherwise order every load
-            // behind the previous store and pay one memory latency per element).
-            __half res_next[16];
+            // Residual epilogue: the residual values of a batch (16 strided 2-byte loads per thread) are requested
+            // two batches ahead, all 16 at once and with no store in between (Y may alias the residual, so the
+            // compiler would otherwise order every load behind the previous store and pay one memory latency per
+            // element); 32 loads in flight per thread, on top of the L2 prefetch issued while the tile was computed.
+            __half ring[RESID ? 2 : 1][16];
             auto load_residual = [&](uint32_t c0, __half (&dst)[16]) {
-                if (mode == 2 && n_ok && c0 < valid) {
+                if (RESID && mode == 2 && n_ok && c0 < valid) {
                     const uint32_t lim = valid - c0;
                     const __half* src = p.residual + out_base + (size_t)(tok0 + c0) * out_stride;
 #pragma unroll
                     for (int j = 0; j < 16; j++) dst[j] = (uint32_t)j < lim ? __ldg(src + j * out_stride) : __half(0.0f);
                 }
             };
-            load_residual(0u, res_next);
-            for (uint32_t c0 = 0; c0 < p.T; c0 += 16) {
-                uint32_t v[16];
-                __half res[16];
-                if (mode == 2) {
 #pragma unroll
-                    for (int j = 0; j < 16; j++) res[j] = res_next[j];
-                    if (c0 + 16 < p.T) load_residual(c0 + 16, res_next);
-                }
+            for (int u = 0; u < (RESID ? 2 : 0); u++) load_residual(16u * u, ring[u]);
+            auto process_batch = [&](const uint32_t c0, const __half (&res)[16]) {
+                uint32_t v[16];
                 if (et == 0 && it == 0) QTR(7, 1 + c0 / 16, 0);
                 ptx::tmem_ld_x16(taddr + c0, v);
                 ptx::tmem_ld_wait();
@@ -628,7 +625,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                         float* dst = partial_dst + (size_t)(tok0 + c0) * p.N + n;
 #pragma unroll
                         for (int j = 0; j < 16; j++) if ((uint32_t)j < lim) dst[(size_t)j * p.N] = f[j];
-                    } else if (mode == 2) {
+                    } else if (RESID && mode == 2) {
                         const size_t o = out_base + (size_t)(tok0 + c0) * out_stride;
 #pragma unroll
                         for (int j = 0; j < 16; j++)
@@ -642,6 +639,21 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
 #pragma unroll
                             for (int j = 0; j < 16; j++) if ((uint32_t)j < lim) dst[j * out_stride] = __float2half_rn(f[j]);
                         }
+                    }
+                }
+            };
+            for (uint32_t c00 = 0; c00 < p.T; c00 += 32) {
+#pragma unroll
+                for (int u = 0; u < 2; u++) {
+                    const uint32_t c0 = c00 + 16u * u;
+                    if (c0 < p.T) {
+                        __half res[16];
+                        if (RESID) {
+#pragma unroll
+                            for (int j = 0; j < 16; j++) res[j] = ring[u][j];
+                            load_residual(c0 + 32u, ring[u]);
+                        }
+                        process_batch(c0, res);
                     }
                 }
             }
@@ -976,7 +988,8 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     int dev = 0;
     cudaGetDevice(&dev);
     if (attr_device != dev) {
-        cudaError_t e = cudaFuncSetAttribute(qgemm_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(qgemm_kernel<FMT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(qgemm_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         attr_device = dev;
     }
@@ -992,7 +1005,9 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, qgemm_kernel<FMT>, tmX, tmW0, tmW1, tmW2, p);
+    // (the split-K fix-up adds the residual outside the epilogue loop: only unsplit residual launches need the RESID build)
+    if (a.residual && pl.k_splits == 1) return cudaLaunchKernelEx(&cfg, qgemm_kernel<FMT, true>, tmX, tmW0, tmW1, tmW2, p);
+    return cudaLaunchKernelEx(&cfg, qgemm_kernel<FMT, false>, tmX, tmW0, tmW1, tmW2, p);
 }
 
 cudaError_t dispatch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t s) {

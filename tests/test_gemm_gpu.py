@@ -227,6 +227,23 @@ def test_host_buffers_pipeline_in_order(bridge):
     assert np.array_equal(h1.numpy().view(np.uint16), want[3].view(np.uint16))
 
 
+@pytest.mark.parametrize("fmt", [o.Q4_0, o.TERNARY_1_58])
+def test_residual_accumulator_preload(bridge, fmt):
+    """Residual projections that do not split K start their tensor-memory accumulators at the residual (loaded by
+    the epilogue warps two tiles ahead): ragged token and row tiles, several tiles per CTA."""
+    M, K, N = 1000, 512, 9000            # 4 token tiles x 71 row tiles = 284 work items on 148 CTAs
+    g = o.RefLcg(12)
+    W = g.weights(fmt, K, N)
+    X = (g.activations(M, K).astype(np.float32) * 0.5).astype(np.float16)
+    R = g.activations(M, N)
+    Y = run_gemm(bridge, fmt, X, W, N, residual=R)
+    rows = np.r_[0:40, 250:262, 990:1000]
+    check(Y[rows], o.gemm_f64(fmt, X[rows], W, N) + R[rows].astype(np.float64), f"residual preload fmt {fmt}")
+    plain = run_gemm(bridge, fmt, X, W, N)
+    want = (plain.astype(np.float32) + R.astype(np.float32))
+    assert np.abs(Y.astype(np.float32) - want).max() <= 2 * np.spacing(np.abs(want).max().astype(np.float16)).astype(np.float32)
+
+
 def test_residual_epilogue(bridge):
     M, K, N = 130, 512, 256
     g = o.RefLcg(4)
