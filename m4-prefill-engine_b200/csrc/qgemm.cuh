@@ -50,6 +50,9 @@ bool fast_path_ok(const GemmArgs& a);
 // Floats of split-K scratch the launch will use (0 when it does not split).
 size_t workspace_floats(const GemmArgs& a);
 // Enqueue on `stream`.  Returns cudaSuccess or the launch error.
+// Single-token path on CUDA cores (qgemv.cu): M == 1, plain standard-layout output, K % 256 == 0.
+bool gemv_path_ok(const GemmArgs& a);
+cudaError_t launch_gemv(const GemmArgs& a, cudaStream_t stream);
 cudaError_t launch(const GemmArgs& a, const Workspace& ws, cudaStream_t stream);
 // Number of kernels the last launch() enqueued (1, or 2 with the generic tail) -- for launch accounting.
 int last_launch_count();

@@ -227,10 +227,22 @@ def test_host_buffers_pipeline_in_order(bridge):
     assert np.array_equal(h1.numpy().view(np.uint16), want[3].view(np.uint16))
 
 
+@pytest.mark.parametrize("fmt", [o.Q4_0, o.MLX_4BIT, o.Q4_K, o.TERNARY_1_58, o.VAR_RATE_AFFINE, o.EXL3, o.MLX_4BIT_G64,
+                                 o.TERNARY_ROW])
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+def test_few_token_path(bridge, fmt, M):
+    """A single token runs on the CUDA-core streaming kernel (one lane per 256-element chunk of a weight row): 16
+    chunks per row (two rows per warp), 56 chunks per row (lanes loop), 1 chunk per row (32 rows per warp).  Two to
+    four tokens take the tensor-core path at the same shapes."""
+    for K, N in ((4096, 1000), (14336, 200), (256, 130)):
+        X, W = o.baseline_inputs(fmt, M, K, N, 30 + M)
+        check(run_gemm(bridge, fmt, X, W, N, ex=True), o.gemm_f64(fmt, X, W, N), f"fmt {fmt} M {M} K {K}")
+
+
 @pytest.mark.parametrize("fmt", [o.Q4_0, o.TERNARY_1_58])
-def test_residual_accumulator_preload(bridge, fmt):
-    """Residual projections that do not split K start their tensor-memory accumulators at the residual (loaded by
-    the epilogue warps two tiles ahead): ragged token and row tiles, several tiles per CTA."""
+def test_residual_unsplit_shape(bridge, fmt):
+    """Residual projections that do not split K (the residual is prefetched two batches ahead in the epilogue):
+    ragged token and row tiles, several tiles per CTA."""
     M, K, N = 1000, 512, 9000            # 4 token tiles x 71 row tiles = 284 work items on 148 CTAs
     g = o.RefLcg(12)
     W = g.weights(fmt, K, N)
@@ -238,7 +250,7 @@ def test_residual_accumulator_preload(bridge, fmt):
     R = g.activations(M, N)
     Y = run_gemm(bridge, fmt, X, W, N, residual=R)
     rows = np.r_[0:40, 250:262, 990:1000]
-    check(Y[rows], o.gemm_f64(fmt, X[rows], W, N) + R[rows].astype(np.float64), f"residual preload fmt {fmt}")
+    check(Y[rows], o.gemm_f64(fmt, X[rows], W, N) + R[rows].astype(np.float64), f"residual fmt {fmt}")
     plain = run_gemm(bridge, fmt, X, W, N)
     want = (plain.astype(np.float32) + R.astype(np.float32))
     assert np.abs(Y.astype(np.float32) - want).max() <= 2 * np.spacing(np.abs(want).max().astype(np.float16)).astype(np.float32)
