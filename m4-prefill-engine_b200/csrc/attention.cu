@@ -661,7 +661,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const Params p, 
     const uint32_t last_pos = min(p.pos0 + min(p0 + BP, p.M) - 1, p.Mkv - 1);
     const uint32_t n_ktiles = last_pos / TC_BK + 1;
 
-    if (tid == 0) {
+    // (initialised by the thread that later issues the first bulk copy onto bar_raw, before any CTA barrier)
+    if (tid == TC_WORKERS) {
         ptx::mbar_init(bar_s, 1); ptx::mbar_init(bar_o, 1); ptx::mbar_init(&bar_raw[0], 1); ptx::mbar_init(&bar_raw[1], 1);
         *abort_flag = 0u;
         ptx::fence_barrier_init();
