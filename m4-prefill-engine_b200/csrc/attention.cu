@@ -673,14 +673,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const Params p, 
     const bool worker = warp < 8u;
     if (warp == 8) { ptx::tmem_alloc(tmem_holder, 256); ptx::tmem_relinquish(); }
 
-    // ---- stage Q: row r = head (r / BP), position p0 + r % BP ----
-    for (uint32_t i = tid; i < TC_ROWS * (TC_D / 8); i += TC_THREADS) {
-        const uint32_t r = i / (TC_D / 8), c = i % (TC_D / 8);
-        const uint32_t h = hk * G + r / BP, pos = p0 + r % BP;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (pos < p.M) v = *reinterpret_cast<const uint4*>(p.Q + ((size_t)h * p.M + pos) * TC_D + c * 8);
-        *reinterpret_cast<uint4*>(sQ + tc_off(r, c * 8)) = v;
-    }
     const uint8_t* Kh = p.K + (size_t)hk * p.Mkv * TC_ROW_RAW;
     const uint8_t* Vh = p.V + (size_t)hk * p.Mkv * TC_ROW_RAW;
 
@@ -811,7 +803,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const Params p, 
         }
     };
 
-    issue(0);
+    issue(0);                                              // the first packed tile travels while Q is staged
+    // ---- stage Q: row r = head (r / BP), position p0 + r % BP ----
+    for (uint32_t i = tid; i < TC_ROWS * (TC_D / 8); i += TC_THREADS) {
+        const uint32_t r = i / (TC_D / 8), c = i % (TC_D / 8);
+        const uint32_t h = hk * G + r / BP, pos = p0 + r % BP;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (pos < p.M) v = *reinterpret_cast<const uint4*>(p.Q + ((size_t)h * p.M + pos) * TC_D + c * 8);
+        *reinterpret_cast<uint4*>(sQ + tc_off(r, c * 8)) = v;
+    }
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
