@@ -21,7 +21,7 @@ def _arr(xs):
     return (ctypes.c_void_p * len(xs))(*[int(x) for x in xs])
 
 
-@pytest.mark.parametrize("world,fmt", [(2, o.Q4_0), (4, o.Q4_0), (2, o.Q4_K), (2, o.TERNARY_1_58)])
+@pytest.mark.parametrize("world,fmt", [(2, o.Q4_0), (4, o.Q4_0), (8, o.Q4_0), (2, o.Q4_K), (2, o.TERNARY_1_58)])
 def test_scatter_reduce_broadcast_emulated_ranks(bridge, pkg, world, fmt):
     from m4_prefill_engine_b200.layer import _bind_layer, shard_cols
     L = bridge.lib
