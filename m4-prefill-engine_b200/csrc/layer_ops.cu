@@ -127,8 +127,66 @@ __global__ void add_residual_f32_kernel(const __half* __restrict__ A, const floa
     }
 }
 
+// Residual add fused into the normalisation that follows it: S = fp16(A + B) (the block's output, kept for the next
+// residual), Y = rmsnorm(S) * W.  One CTA of 256 threads per row; a thread reads back only the vectors it wrote itself,
+// and the barrier of the row reduction separates every read of A from the first write of Y, so Y may alias A.
+// Rows must be 16-byte aligned with K a multiple of 8 (checked by the launcher).
+__global__ void __launch_bounds__(256) rmsnorm_add_kernel(const __half* A, const __half* __restrict__ B,
+                                                          const __half* __restrict__ W, __half* __restrict__ S, __half* Y,
+                                                          uint32_t K, float eps) {
+    const size_t row = (size_t)blockIdx.x * K;
+    float ss = 0.0f;
+    for (uint32_t i = threadIdx.x; i < K / 8; i += blockDim.x) {
+        const uint4 a = reinterpret_cast<const uint4*>(A + row)[i], b = reinterpret_cast<const uint4*>(B + row)[i];
+        uint4 o;
+        const __half2* ah = reinterpret_cast<const __half2*>(&a);
+        const __half2* bh = reinterpret_cast<const __half2*>(&b);
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 fa = __half22float2(ah[j]), fb = __half22float2(bh[j]);
+            oh[j] = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);
+            const float2 f = __half22float2(oh[j]);
+            ss += f.x * f.x + f.y * f.y;
+        }
+        reinterpret_cast<uint4*>(S + row)[i] = o;
+    }
+    __shared__ float red[8];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += red[i];
+    const float r = 1.0f / sqrtf(tot / (float)K + eps);
+    for (uint32_t i = threadIdx.x; i < K / 8; i += blockDim.x) {
+        const uint4 v = reinterpret_cast<const uint4*>(S + row)[i], w = reinterpret_cast<const uint4*>(W)[i];
+        uint4 o;
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+        const __half2* wh = reinterpret_cast<const __half2*>(&w);
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 f = __half22float2(h[j]), g = __half22float2(wh[j]);
+            const __half2 n = __floats2half2_rn(f.x * r, f.y * r);            // rounded to fp16 first, as in rmsnorm_kernel
+            const float2 nf = __half22float2(n);
+            oh[j] = __floats2half2_rn(nf.x * g.x, nf.y * g.y);
+        }
+        reinterpret_cast<uint4*>(Y + row)[i] = o;
+    }
+}
+
 cudaError_t rmsnorm(const void* X, const void* weight, void* Y, uint32_t M, uint32_t K, float eps, cudaStream_t s) {
     rmsnorm_kernel<<<M, 256, 0, s>>>((const __half*)X, (const __half*)weight, (__half*)Y, K, eps);
+    return cudaGetLastError();
+}
+cudaError_t rmsnorm_add(const void* A, const void* B, const void* weight, void* S, void* Y, uint32_t M, uint32_t K, float eps,
+                        cudaStream_t s) {
+    if (K % 8 != 0 || ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(weight) |
+                        reinterpret_cast<uintptr_t>(S) | reinterpret_cast<uintptr_t>(Y)) & 15u))
+        return cudaErrorInvalidValue;
+    rmsnorm_add_kernel<<<M, 256, 0, s>>>((const __half*)A, (const __half*)B, (const __half*)weight, (__half*)S, (__half*)Y, K, eps);
     return cudaGetLastError();
 }
 cudaError_t rope(void* X, uint32_t H, uint32_t M, uint32_t D, float theta, uint32_t pos0, cudaStream_t s) {

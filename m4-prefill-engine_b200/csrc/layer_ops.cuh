@@ -7,6 +7,9 @@
 namespace lops {
 // Y[m][:] = fp16( fp16(x * rsqrt(mean(x^2) + eps)) * w ), sums in fp32.
 cudaError_t rmsnorm(const void* X, const void* weight, void* Y, uint32_t M, uint32_t K, float eps, cudaStream_t s);
+// S = fp16(A + B), Y = rmsnorm(S) * weight; Y may alias A; 16-byte aligned rows (else cudaErrorInvalidValue)
+cudaError_t rmsnorm_add(const void* A, const void* B, const void* weight, void* S, void* Y, uint32_t M, uint32_t K, float eps,
+                        cudaStream_t s);
 // Rotate-half rotary embedding in place on X [H][M][D]; positions pos0 .. pos0+M-1.
 cudaError_t rope(void* X, uint32_t H, uint32_t M, uint32_t D, float theta, uint32_t pos0, cudaStream_t s);
 // Y = fp16(float(A) + B) elementwise, A fp16, B fp32 (residual add after an fp32 all-reduce).
