@@ -127,6 +127,23 @@ __global__ void add_residual_f32_kernel(const __half* __restrict__ A, const floa
     }
 }
 
+// Y = fp16(A + B), eight elements per thread (16-byte accesses; the launcher checks alignment and n % 8)
+__global__ void add_residual_f16_kernel(const __half* __restrict__ A, const __half* __restrict__ B, __half* __restrict__ Y, size_t n8) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const uint4 a = reinterpret_cast<const uint4*>(A)[i], b = reinterpret_cast<const uint4*>(B)[i];
+    uint4 o;
+    const __half2* ah = reinterpret_cast<const __half2*>(&a);
+    const __half2* bh = reinterpret_cast<const __half2*>(&b);
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float2 fa = __half22float2(ah[j]), fb = __half22float2(bh[j]);
+        oh[j] = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);
+    }
+    reinterpret_cast<uint4*>(Y)[i] = o;
+}
+
 // Residual add fused into the normalisation that follows it: S = fp16(A + B) (the block's output, kept for the next
 // residual), Y = rmsnorm(S) * W.  One CTA of 256 threads per row; a thread reads back only the vectors it wrote itself,
 // and the barrier of the row reduction separates every read of A from the first write of Y, so Y may alias A.
@@ -202,6 +219,14 @@ cudaError_t rope(void* X, uint32_t H, uint32_t M, uint32_t D, float theta, uint3
 cudaError_t add_residual_f32(const void* A, const float* B, void* Y, size_t n, cudaStream_t s) {
     const size_t threads = (n + 3) / 4;
     add_residual_f32_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>((const __half*)A, B, (__half*)Y, n);
+    return cudaGetLastError();
+}
+
+cudaError_t add_residual_f16(const void* A, const void* B, void* Y, size_t n, cudaStream_t s) {
+    if (n % 8 != 0 || ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(Y)) & 15u))
+        return cudaErrorInvalidValue;
+    const size_t n8 = n / 8;
+    add_residual_f16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, s>>>((const __half*)A, (const __half*)B, (__half*)Y, n8);
     return cudaGetLastError();
 }
 

@@ -14,6 +14,8 @@ cudaError_t rmsnorm_add(const void* A, const void* B, const void* weight, void* 
 cudaError_t rope(void* X, uint32_t H, uint32_t M, uint32_t D, float theta, uint32_t pos0, cudaStream_t s);
 // Y = fp16(float(A) + B) elementwise, A fp16, B fp32 (residual add after an fp32 all-reduce).
 cudaError_t add_residual_f32(const void* A_f16, const float* B_f32, void* Y_f16, size_t n, cudaStream_t s);
+// Y = fp16(A + B), all fp16; n % 8 == 0 and 16-byte aligned pointers (else cudaErrorInvalidValue)
+cudaError_t add_residual_f16(const void* A, const void* B, void* Y, size_t n, cudaStream_t s);
 }  // namespace lops
 
 namespace attn {

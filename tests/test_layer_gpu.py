@@ -114,7 +114,7 @@ def test_layer_8b_full_size(bridge, pkg):
     n2 = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float16)
     kw = dict(M=M, K=K, H=H, D=D, N_mlp=F, attn_scale=D ** -0.5, num_kv_heads=Hkv, rms_eps=1e-5, rope_theta=500000.0, kv_q8_0=True)
     Y, n = run_layer(pkg, kw, X, w, (n1, n2))
-    assert n == 11 and np.all(np.isfinite(Y.astype(np.float32)))
+    assert n == 12 and np.all(np.isfinite(Y.astype(np.float32)))
     R = 48
     gold = o.layer(o.Q4_0, X[:R], w["q"], w["k"], w["v"], w["o"], w["gate"], w["up"], w["down"], H, Hkv, D, F, D ** -0.5,
                    rms_eps=1e-5, norm1=n1, norm2=n2, rope_theta=500000.0, kv_q8=True)
