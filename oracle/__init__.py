@@ -10,6 +10,7 @@ import this package.  The product package never does.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 import numpy as np
@@ -87,6 +88,19 @@ def lib() -> C.CDLL:
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+def set_num_threads(n: int = 0) -> int:
+    """Make the CPU checkers (restatement and, where built, the reference's own verifier) use n OpenMP threads
+    (0: every core this process may run on) and return the team size a parallel region really gets.  Needed under
+    launchers that export OMP_NUM_THREADS=1 to their children."""
+    if n <= 0:
+        n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    got = int(lib().orc_set_num_threads(int(n)))
+    r = ref_lib()
+    if r is not None and hasattr(r, "ref_set_threads"):
+        got = min(got, int(r.ref_set_threads(int(n))))
+    return got
 
 
 # ---------------------------------------------------------------------------------------

@@ -61,8 +61,15 @@ def _section(text: str, start: str, stop: str) -> str:
     return "\n".join(lines[i0:i1]) + "\n"
 
 
-def build_ref(reference_root: str | os.PathLike = "/root/reference", force: bool = False) -> Path | None:
-    ref = Path(reference_root)
+def reference_root() -> Path:
+    """Where the reference checkout lies: $M4_PREFILL_REFERENCE_ROOT, else a directory named `reference` beside this
+    repository.  It does not have to exist (then the previously built verifier, if any, is used as is)."""
+    env = os.environ.get("M4_PREFILL_REFERENCE_ROOT")
+    return Path(env) if env else HERE.parent.parent / "reference"
+
+
+def build_ref(ref_root: str | os.PathLike | None = None, force: bool = False) -> Path | None:
+    ref = Path(ref_root) if ref_root is not None else reference_root()
     out = REF_OUT / "libm4ref.so"
     gold = ref / "tests" / "e2e" / "cpu_gold_reference.h"
     if not gold.exists():

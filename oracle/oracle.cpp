@@ -679,6 +679,16 @@ uint32_t orc_gen_q4_0_affine_scale(uint32_t state, uint8_t* out, size_t num_bloc
     return g.s;
 }
 
+int orc_num_threads(void);
+// Sets the OpenMP team size of later calls (n <= 0: leave as is) and returns the size a parallel region then gets.
+// Launchers such as torchrun export OMP_NUM_THREADS=1 to their children; a caller that wants every host core says so here.
+int orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#endif
+    return orc_num_threads();
+}
+
 int orc_num_threads(void) {
     int n = 1;
 #ifdef _OPENMP

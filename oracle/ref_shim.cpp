@@ -34,7 +34,25 @@ namespace layer8b {
 #include REF_LAYER
 }
 
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
 extern "C" {
+
+// OpenMP team size used by the rewritten dispatch_apply loops: set it (n > 0) and report what a parallel region gets.
+int ref_set_threads(int n) {
+    int got = 1;
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#pragma omp parallel
+    {
+#pragma omp single
+        got = omp_get_num_threads();
+    }
+#endif
+    return got;
+}
 
 int ref_gemm(int format, const _Float16* A, const void* W, _Float16* C, uint32_t M, uint32_t N, uint32_t K,
              int direct_head, uint32_t H, uint32_t D) {

@@ -30,6 +30,30 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
+def pytest_terminal_summary(terminalreporter, exitstatus, config):
+    """Parity table of the GPU tests: per checked configuration the largest difference from the oracle's gold, the
+    number of outputs over the strict criterion max(1/128, one fp16 ulp) and by what factor, and (where the test
+    computed it) the same against the gold built from the exact fp16 weights the kernel uses."""
+    try:
+        import gpu_util
+    except Exception:
+        return
+    rows = gpu_util.PARITY_REPORT
+    if not rows:
+        return
+    gpu_util.write_report()
+    tr = terminalreporter
+    tr.section("parity against the CPU oracle (strict criterion: max(1/128, 1 fp16 ulp))")
+    for r in rows:
+        ob = r["over_by"]
+        line = (f"{r['what'][:44]:44s} n={r['outputs']:>9d} max|d|={r['max_abs']:.5f} rms={r['rms_gold']:.2f} "
+                f"over={r['over_strict']} [(1,2]x {ob['(1,2]x']}, (2,3]x {ob['(2,3]x']}, >3x {ob['>3x']}]")
+        if "vs_device_weights" in r:
+            d = r["vs_device_weights"]
+            line += f" | fp16-weight gold: max|d|={d['max_abs']:.5f} over={d['over_strict']}"
+        tr.write_line(line)
+
+
 @pytest.fixture(scope="session")
 def pkg():
     from __graft_entry__ import load_package

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import oracle as o
-from gpu_util import TOL, check, dev, run_gemm
+from gpu_util import TOL, check, dev, device_weight_gold, run_gemm
 
 pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).resolve().parent / "golden"
@@ -268,38 +268,60 @@ def test_residual_epilogue(bridge):
 
 
 # ---- benchmark shapes (K = N = 4096; the value distributions the benchmark contract names) ----
-@pytest.mark.parametrize("fmt", [o.Q4_0, o.MLX_4BIT, o.Q4_K, o.TERNARY_1_58, o.VAR_RATE_AFFINE, o.EXL3, o.MLX_4BIT_G64,
-                                 o.TERNARY_ROW])
+ALL_CODECS = [o.Q4_0, o.MLX_4BIT, o.Q4_K, o.TERNARY_1_58, o.VAR_RATE_AFFINE, o.EXL3, o.MLX_4BIT_G64, o.TERNARY_ROW]
+
+
+@pytest.mark.parametrize("fmt", ALL_CODECS)
 @pytest.mark.parametrize("M", [33, 128, 129])
 def test_8b_projection_small_m(bridge, fmt, M):
     K = N = 4096
     X, W = o.baseline_inputs(fmt, M, K, N, 100 + M)
-    check(run_gemm(bridge, fmt, X, W, N, ex=fmt > 5), o.gemm_f64(fmt, X, W, N), f"fmt {fmt} M {M}")
+    Y = run_gemm(bridge, fmt, X, W, N, ex=fmt > 5)
+    check(Y, o.gemm_f64(fmt, X, W, N), f"projection fmt {fmt} M={M} K=N=4096", dev_gold=device_weight_gold(fmt, X, W, N))
 
 
-@pytest.mark.parametrize("fmt", [o.Q4_0, o.MLX_4BIT, o.Q4_K, o.TERNARY_1_58])
+def sampled_rows(M):
+    """Both ragged ends of every 256-token tile plus 40 random rows."""
+    return np.unique(np.concatenate([np.arange(0, M, 256), np.arange(255, M, 256), np.random.default_rng(0).integers(0, M, 40)]))
+
+
+@pytest.mark.parametrize("fmt", ALL_CODECS)
 def test_8b_projection_m2048(bridge, fmt):
-    """Full size: sampled token rows (including both ragged ends of every 256-token tile) against the oracle,
-    plus two size-independent properties: runs are bit-reproducible, and permuting token rows permutes
-    output rows bit for bit (each output is an independent K-ordered sum)."""
+    """Full size, every codec of the tensor-core path: sampled token rows (including both ragged ends of every
+    256-token tile) against the oracle, and against the gold built from the kernel's exact fp16 weights under the
+    strict criterion; plus two size-independent properties: runs are bit-reproducible, and permuting token rows
+    permutes output rows bit for bit (each output is an independent K-ordered sum)."""
     M, K, N = 2048, 4096, 4096
     X, W = o.baseline_inputs(fmt, M, K, N, 7)
-    Y = run_gemm(bridge, fmt, X, W, N)
-    rows = np.unique(np.concatenate([np.arange(0, M, 256), np.arange(255, M, 256), np.random.default_rng(0).integers(0, M, 40)]))
-    check(Y[rows], o.gemm_f64(fmt, X[rows], W, N), f"fmt {fmt}")
-    assert np.array_equal(Y.view(np.uint16), run_gemm(bridge, fmt, X, W, N).view(np.uint16))
+    Y = run_gemm(bridge, fmt, X, W, N, ex=fmt > 5)
+    rows = sampled_rows(M)
+    check(Y[rows], o.gemm_f64(fmt, X[rows], W, N), f"projection fmt {fmt} M=2048 K=N=4096", dev_gold=device_weight_gold(fmt, X[rows], W, N))
+    assert np.array_equal(Y.view(np.uint16), run_gemm(bridge, fmt, X, W, N, ex=fmt > 5).view(np.uint16))
     perm = np.random.default_rng(1).permutation(M)
-    Yp = run_gemm(bridge, fmt, X[perm], W, N)
+    Yp = run_gemm(bridge, fmt, X[perm], W, N, ex=fmt > 5)
     assert np.array_equal(Yp.view(np.uint16), Y[perm].view(np.uint16))
 
 
 def test_1b_reference_config_q4_0(bridge):
     # the CPU-reference configuration: M=33, K=N=2048, d ~ U(0.005, 0.02), X ~ N(0,1)
     X, W = o.baseline_inputs(o.Q4_0, 33, 2048, 2048, 42)
-    check(run_gemm(bridge, o.Q4_0, X, W, 2048), o.gemm_f64(o.Q4_0, X, W, 2048), "config 1")
+    check(run_gemm(bridge, o.Q4_0, X, W, 2048), o.gemm_f64(o.Q4_0, X, W, 2048), "config 1: q4_0 M=33 K=N=2048",
+          dev_gold=device_weight_gold(o.Q4_0, X, W, 2048))
 
 
-def test_ternary_n14336(bridge):
-    for fmt in (o.TERNARY_1_58, o.TERNARY_ROW):
-        X, W = o.baseline_inputs(fmt, 128, 4096, 14336, 9)
-        check(run_gemm(bridge, fmt, X, W, 14336, ex=fmt > 5), o.gemm_f64(fmt, X, W, 14336), f"ternary fmt {fmt}")
+@pytest.mark.parametrize("fmt", [o.TERNARY_1_58, o.TERNARY_ROW])
+@pytest.mark.parametrize("M", [128, 2048])
+def test_ternary_n14336(bridge, fmt, M):
+    """The ternary up-projection shape (K=4096, N=14336) at both token counts, both ternary layouts; at M=2048 sampled
+    token rows.  Column shards of this projection are independent: rows [r*N/8, (r+1)*N/8) of the packed matrix give
+    columns of the same range of Y bit for bit (what the N-sharded multi-GPU run relies on)."""
+    K, N = 4096, 14336
+    X, W = o.baseline_inputs(fmt, M, K, N, 9)
+    Y = run_gemm(bridge, fmt, X, W, N, ex=fmt > 5)
+    rows = np.arange(M) if M <= 128 else sampled_rows(M)
+    check(Y[rows], o.gemm_f64(fmt, X[rows], W, N), f"ternary fmt {fmt} M={M} N=14336", dev_gold=device_weight_gold(fmt, X[rows], W, N))
+    from m4_prefill_engine_b200.layer import shard_rows_any
+    for r in (0, 5):
+        Ws = shard_rows_any(W, fmt, K, N, r, 8)
+        Ys = run_gemm(bridge, fmt, X, Ws, N // 8, ex=fmt > 5)
+        assert np.array_equal(Ys.view(np.uint16), Y[:, r * (N // 8):(r + 1) * (N // 8)].view(np.uint16))

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import oracle as o
-from gpu_util import TOL, dev
+from gpu_util import PARITY_REPORT, TOL, dev, parity_stats
 
 pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).resolve().parent / "golden"
@@ -32,6 +32,29 @@ def layer_weights(fmt, K, H, Hkv, D, F, seed=1337):
         blocks[:, :2 * nfields] = hdr.astype(np.float16).view(np.uint8)
         out[n] = blocks.reshape(-1)
     return out, g
+
+
+def layer_gold_rows(X, w, n1, n2, rows, H, Hkv, D, F, eps, theta):
+    """The oracle's Llama-style layer (Q4_0, RMSNorm, RoPE, Q8_0 KV) for selected token rows only: keys and values of
+    every token (they are needed by late queries), then per selected row the query projection, attention over keys
+    0..row, O projection + residual, and the MLP block, with the fp16 roundings of o.layer (oracle.cpp, orc_layer)."""
+    M, K = X.shape
+    fmt, scale = o.Q4_0, D ** -0.5
+    xn = o.rmsnorm(X, n1, eps)
+    kv = []
+    for name in ("k", "v"):
+        t = o.gemm(fmt, xn, w[name], Hkv * D, direct_head=True, H=Hkv, D=D)
+        if name == "k":
+            t = o.rope(t, theta, 0)
+        kv.append(o.dequantize_q8_0(o.quantize_q8_0(t), t.shape))
+    out = np.empty((len(rows), K), np.float16)
+    for i, r in enumerate(rows):
+        q = o.rope(o.gemm(fmt, xn[r:r + 1], w["q"], H * D, direct_head=True, H=H, D=D), theta, r)
+        a = o.attention(q, kv[0][:, :r + 1], kv[1][:, :r + 1], scale, pos0=r, tokens_major=True)
+        x_mid = (X[r:r + 1].astype(np.float64) + o.gemm_f64(fmt, a, w["o"], K)).astype(np.float16)
+        act = o.swiglu_fused(fmt, o.rmsnorm(x_mid, n2, eps), w["gate"], w["up"], F)
+        out[i] = (x_mid.astype(np.float64) + o.gemm_f64(fmt, act, w["down"], K)).astype(np.float16)[0]
+    return out
 
 
 def run_layer(pkg, cfg_kwargs, X, w, norms=None, host_io=False):
@@ -120,6 +143,14 @@ def test_layer_8b_full_size(bridge, pkg):
                    rms_eps=1e-5, norm1=n1, norm2=n2, rope_theta=500000.0, kv_q8=True)
     diff = np.abs(Y[:R].astype(np.float64) - gold.astype(np.float64))
     assert diff.max() <= 2 * TOL, f"max-abs {diff.max()}"
+    PARITY_REPORT.append(parity_stats(Y[:R], gold.astype(np.float64), "8B layer M=2048, rows [0,48)"))
+    # late rows: query positions that attend over up to 16 key tiles, each checked against the oracle run for that
+    # row over the full key/value cache
+    late = [2047, 2046, 1920, 1793, 1500, 1279, 1024, 1023, 777, 512, 300, 255, 129, 128, 127, 64]
+    gold_late = layer_gold_rows(X, w, n1, n2, late, H, Hkv, D, F, 1e-5, 500000.0)
+    dl = np.abs(Y[late].astype(np.float64) - gold_late.astype(np.float64))
+    PARITY_REPORT.append(parity_stats(Y[late], gold_late.astype(np.float64), "8B layer M=2048, 16 late rows"))
+    assert dl.max() <= 2 * TOL, f"late rows: max-abs {dl.max()} at row {late[int(dl.max(axis=1).argmax())]}"
     X2 = X.copy()
     X2[1500:] = (rng.standard_normal((M - 1500, K), dtype=np.float32) * 0.35).astype(np.float16)
     Y2, _ = run_layer(pkg, kw, X2, w, (n1, n2))

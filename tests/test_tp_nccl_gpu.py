@@ -1,6 +1,6 @@
-"""Tensor-parallel decoder layer on two GPUs (skipped where fewer are visible), with the row-split projections
-reduced either by NCCL or by the fused exchange over peer memory: both ranks must hold the same output, and it must
-match the CPU oracle's layer.  One process per GPU, 127.0.0.1 rendezvous."""
+"""Tensor-parallel decoder layer on 2, 4 and 8 GPUs (each skipped where fewer are visible), with the row-split
+projections reduced either by NCCL or by the fused exchange over peer memory: every rank must hold the same output,
+and it must match the CPU oracle's layer.  One process per GPU, 127.0.0.1 rendezvous."""
 import os
 import subprocess
 import sys
@@ -27,7 +27,9 @@ os.environ["NCCL_NVLS_ENABLE"] = "0"
 dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{sys.argv[2]}", rank=rank, world_size=world,
                         device_id=torch.device("cuda", rank))
 br = B200Bridge.get_instance(); assert br.init()
-M, K, H, Hkv, D, F = (70 if mode == "nccl" else 512), 512, 4, 2, 128, 1024
+# whole heads per rank at 8 ranks; F / world and H * D / world multiples of 256 (the row-split projections' K);
+# the fused exchange wants M / world to be a multiple of the 256-token tile
+M, K, H, Hkv, D, F = (70 if mode == "nccl" else 256 * world), 512, 16, 8, 128, 2048
 g = o.RefLcg(1337)
 shapes = {"q": (H * D, K), "k": (Hkv * D, K), "v": (Hkv * D, K), "o": (K, H * D), "gate": (F, K), "up": (F, K), "down": (K, F)}
 w = {n: g.q4_0_bench(k, r, 0.003, 0.0003) for n, (r, k) in shapes.items()}
@@ -45,6 +47,16 @@ else:
 Xd = torch.from_numpy(X).cuda(); Yd = torch.zeros_like(Xd)
 for _ in range(3):
     layer.forward(Xd, sw["q"], sw["k"], sw["v"], sw["o"], sw["gate"], sw["up"], sw["down"], Yd)
+if px is not None:
+    # a second layer on the same exchange buffers (the layers of a model share one exchange)
+    layer2 = TransformerLayerCoordinator(cfg, br)
+    layer2.attach_peer_exchange(px)
+    Y2 = torch.zeros_like(Xd)
+    layer2.forward(Xd, sw["q"], sw["k"], sw["v"], sw["o"], sw["gate"], sw["up"], sw["down"], Y2)
+    layer.forward(Xd, sw["q"], sw["k"], sw["v"], sw["o"], sw["gate"], sw["up"], sw["down"], Yd)
+    br.synchronize()
+    assert torch.equal(Y2, Yd), "second layer on the shared exchange disagrees"
+    layer2.close()
 br.synchronize(); torch.cuda.synchronize()
 assert br.device_error() == 0
 Y = Yd.cpu().numpy()
@@ -64,14 +76,16 @@ print("rank", rank, "ok maxdiff", diff)
 '''
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("mode", ["nccl", "peer"])
-def test_layer_tp2(tmp_path, mode):
+def test_layer_tp(tmp_path, mode, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     script = tmp_path / "tp_worker.py"
     script.write_text(WORKER)
-    port = 29600 + (os.getpid() % 300) + (0 if mode == "nccl" else 301)
-    procs = [subprocess.Popen([sys.executable, str(script), str(ROOT), str(port), str(r), "2", mode], stdout=subprocess.PIPE,
-                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    port = 29600 + (os.getpid() % 300) + (0 if mode == "nccl" else 301) + 700 * (world // 4)
+    procs = [subprocess.Popen([sys.executable, str(script), str(ROOT), str(port), str(r), str(world), mode], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(world)]
     outs = []
     for p in procs:
         try:
