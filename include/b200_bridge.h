@@ -111,8 +111,9 @@ int b200_bridge_rope(void* X, uint32_t H, uint32_t M, uint32_t D, float theta, u
  * only, and the split-K scratch lives in a 12 MiB device array inside the library image (held by every
  * GPU that loads the library until exit) instead of being allocated on demand.  Never calls cudaMalloc
  * or cudaFree.  Returns -7 (message in b200_bridge_last_error_string) when the shape needs more than
- * 3 Mi floats of scratch, -2 for host pointers.  The first call on a device looks up the array's address
- * and sets kernel attributes: make it before any stream capture.  All calls share the one array (tile
+ * 3 Mi floats of scratch, -2 for host pointers.  m4_bridge_init makes the array and the kernels resident on the
+ * bridge's GPU, so initialise the bridge at start-up, before the host application reserves the rest of the GPU's
+ * memory and before any stream capture.  All calls share the one array (tile
  * counters are cleared on the stream before each launch), so calls that overlap on the GPU would race. */
 int b200_bridge_gemm_scratch_static(void* X_ptr, size_t X_bytes, void* W_ptr, size_t W_bytes, void* Y_ptr, size_t Y_bytes,
                                     int format, uint32_t M, uint32_t K, uint32_t N);
@@ -135,8 +136,11 @@ uint64_t b200_bridge_kernel_launches(void);
 void* b200_bridge_stream(void);
 
 /* Testing hook: non-zero routes every GEMM through the CUDA-core fallback kernel. */
-/* Clears the device error word after the caller has read it with b200_bridge_device_error (waits for the streams). */
+/* Clears the device error word after the caller has read it with b200_bridge_device_error (waits for the streams),
+ * together with the split-K tile counters, which a launch that gave up on a bounded wait leaves part-way. */
 int b200_bridge_clear_device_error(void);
+/* Testing hook: writes `value` into split-K tile counter `index` (what an aborted split-K launch leaves behind). */
+int b200_bridge_debug_set_tile_counter(uint32_t index, uint32_t value);
 void b200_bridge_force_generic(int on);
 /* Up to three projections of the same activations in one launch (the Q, K and V projections of a layer): Y[i] =
  * X . W[i]^T with W[i] packed [N[i]][K/blk] in `format`, outputs in `layout` (LAYOUT_DIRECT_HEAD: [N[i]/D][M][D]).

@@ -20,6 +20,7 @@
 #include "quant_registry.h"
 
 typedef struct CUstream_st* cudaStream_t;
+namespace peer { struct Exchange; }
 
 namespace b200_llm {
 
@@ -64,6 +65,15 @@ public:
     // O and down projections), flags[o] 16 zero-initialised words.  Needs M / world to be a multiple of 256.
     bool set_peer_exchange(uint32_t rank, uint32_t world, void* const* recv, void* const* out0, void* const* out1,
                            void* const* flags);
+    // The same exchange shared with other layers (b200_peer_exchange_create): epoch, flags and counters belong to the
+    // buffers, so the layers of a model take turns on one set of buffers.  With RMSNorm enabled the owner of a row
+    // normalises it before sending it out, i.e. the residual stream is sharded by rows between the two reductions.
+    bool attach_peer_exchange(peer::Exchange* shared);
+
+    // Per-launch timing: with profiling on, forward() records a CUDA event after every launch; profile() returns, for
+    // the last forward, up to `cap` (label, microseconds) pairs in launch order (the caller synchronises first).
+    void set_profiling(bool on);
+    size_t profile(const char** labels, float* us, size_t cap) const;
 
     // Enqueue one layer on `stream`.  All pointers are device pointers.  Weight shapes for rank r of
     // tp_size: W_q [H/tp*D][K], W_k/W_v [Hkv/tp*D][K], W_o [K][H/tp*D], W_gate/W_up [N_mlp/tp][K],
@@ -121,6 +131,16 @@ int b200_peer_free(void* ptr);
 /* See TransformerLayerCoordinator::set_peer_exchange; arrays of `world` pointers indexed by rank. */
 int b200_layer_set_peer_exchange(void* layer, uint32_t rank, uint32_t world, void* const* recv, void* const* out0,
                                  void* const* out1, void* const* flags);
+/* One exchange for several layers (the layers of a model run one after the other on the same buffers): create it from
+ * the same pointer arrays, attach it to each layer, destroy it after the layers.  NULL / -4 on bad arguments. */
+void* b200_peer_exchange_create(uint32_t rank, uint32_t world, void* const* recv, void* const* out0, void* const* out1,
+                                void* const* flags);
+void b200_peer_exchange_destroy(void* exchange);
+int b200_layer_attach_peer_exchange(void* layer, void* exchange);
+/* Per-launch timing of the next forward calls (CUDA events between launches); b200_layer_profile waits for the stream
+ * and writes up to `cap` labels (label_bytes each, NUL-terminated) and durations in microseconds; returns the count. */
+int b200_layer_set_profiling(void* layer, int on);
+int b200_layer_profile(void* layer, char* labels, size_t label_bytes, float* us, size_t cap);
 /* The three steps on their own (device pointers): partial sums of Y = X.W^T scattered to the owners' receive
  * buffers; the owner's reduction + residual + broadcast into out[]; the wait for every rank's rows. */
 int b200_peer_gemm_scatter(const void* X, const void* W, int format, uint32_t M, uint32_t K, uint32_t N, uint32_t rank,
@@ -128,6 +148,11 @@ int b200_peer_gemm_scatter(const void* X, const void* W, int format, uint32_t M,
 int b200_peer_reduce_broadcast(uint32_t rank, uint32_t world, void* const* recv, void* const* out, void* const* flags,
                                uint32_t epoch, const void* residual, uint32_t M, uint32_t K);
 int b200_peer_wait_rows(uint32_t rank, uint32_t world, void* const* flags, uint32_t epoch);
+/* The owner's reduction with the normalisation that follows it fused in: this rank's rows of fp16(residual + sum) go to
+ * the local buffer `keep` ([M][K]), rmsnorm(those rows) * norm_w (fp16 [K]) to every rank's out[]. */
+int b200_peer_reduce_norm_broadcast(uint32_t rank, uint32_t world, void* const* recv, void* const* out, void* const* flags,
+                                    uint32_t epoch, const void* residual, uint32_t M, uint32_t K, const void* norm_w, float eps,
+                                    void* keep);
 /* Bound of the exchange's flag waits in milliseconds (0 restores the default of about ten seconds).  A wait that runs
  * out sets device error 301 (arrival flags) or 302 (result rows) and the kernel returns; later waits return at once
  * until the error word is cleared. */

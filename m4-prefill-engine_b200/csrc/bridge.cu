@@ -72,6 +72,7 @@ int copy_back(void* host_dst, const void* dev_src, size_t bytes) {
     g.d2h_bytes += bytes;
     cudaEventRecord(g.ev_main_d2h, g.stream);
     g.main_d2h_pending = true;
+    g.main_d2h_seq = ++g.dispatch_seq;
     return 0;
 }
 
@@ -183,6 +184,7 @@ int run_gemm(void* X, size_t Xb, void* W0, void* W1, size_t Wb, void* Y, size_t 
         if (cudaMemcpyAsync(host_dst, a.Y, y_bytes, cudaMemcpyDeviceToHost, g.stream_out) != cudaSuccess) { cudaGetLastError(); return -5; }
         cudaEventRecord(sl.ev_out, g.stream_out);
         sl.out_pending = true; sl.out_ptr = static_cast<const char*>(host_dst); sl.out_bytes = y_bytes;
+        sl.out_seq = ++g.dispatch_seq;
         g.d2h_bytes += y_bytes;
     }
     return 0;
@@ -234,7 +236,11 @@ bool m4_bridge_init(const char*) {
     cudaMemsetAsync(g.counters, 0, 4096 * sizeof(uint32_t) + 64, g.stream);
     g.err_word = reinterpret_cast<int*>(g.counters + 4096);
     cudaStreamSynchronize(g.stream);
-    g.launches = 0; g.h2d_bytes = 0; g.d2h_bytes = 0;
+    // everything that makes the driver load code or reserve memory happens here, not in a later dispatch: the kernels'
+    // shared-memory attributes (which load the module image) and the static scratch array of the allocation-free entry point
+    if (qg::prepare_device() != cudaSuccess) { cudaGetLastError(); set_error("setting kernel attributes failed"); return false; }
+    static_scratch_prepare(g.device);
+    g.launches = 0; g.h2d_bytes = 0; g.d2h_bytes = 0; g.dispatch_seq = 0;
     g.initialized = true;
     return true;
 }
@@ -341,17 +347,29 @@ int b200_bridge_unregister_weights(const void* host_ptr) {
 }
 
 void m4_bridge_synchronize(void) {
+    // The lock is not held while waiting (dispatches from other threads may go on), so the "copy pending" marks may
+    // only be cleared for copies that were already enqueued when the wait began: their events are recorded under the
+    // lock before the wait and queried afterwards.  A copy enqueued by another thread in between keeps its mark.
     cudaStream_t s, si, so;
+    uint64_t seq_before;
     {
         std::lock_guard<std::mutex> lock(g.mu);
         if (!g.initialized) return;
         s = g.stream; si = g.stream_in; so = g.stream_out;
+        seq_before = g.dispatch_seq;
     }
     cudaError_t e = sync_all_streams(s, si, so);
     {
         std::lock_guard<std::mutex> lock(g.mu);
-        for (StageSlot& sl : g.slots) { sl.out_pending = false; sl.out_ptr = nullptr; sl.out_bytes = 0; }
-        g.main_d2h_pending = false;
+        if (g.initialized) {
+            for (StageSlot& sl : g.slots)
+                if (sl.out_pending && (sl.out_seq <= seq_before || cudaEventQuery(sl.ev_out) == cudaSuccess)) {
+                    sl.out_pending = false; sl.out_ptr = nullptr; sl.out_bytes = 0;
+                }
+            if (g.main_d2h_pending && (g.main_d2h_seq <= seq_before || cudaEventQuery(g.ev_main_d2h) == cudaSuccess))
+                g.main_d2h_pending = false;
+            cudaGetLastError();     // cudaErrorNotReady from a query is not an error
+        }
     }
     if (e != cudaSuccess) {
         std::lock_guard<std::mutex> lock(g.mu);
@@ -389,6 +407,7 @@ void m4_bridge_shutdown(void) {
     g.registered.clear();
     cudaFree(g.counters); g.counters = nullptr; g.err_word = nullptr;
     cudaStreamDestroy(g.stream); g.stream = nullptr;
+    static_scratch_forget();
     g.initialized = false;
 }
 
@@ -405,7 +424,18 @@ int b200_bridge_clear_device_error(void) {
     std::lock_guard<std::mutex> lock(g.mu);
     if (!g.initialized) return -1;
     sync_all_streams(g.stream, g.stream_in, g.stream_out);
-    return cudaMemset(g.err_word, 0, sizeof(int)) == cudaSuccess ? 0 : -6;
+    // A split-K launch that gave up on a bounded wait leaves its tile counters part-way: the counters and the error
+    // word are one block and are cleared together, so the next split-K launch starts from zero again.
+    return cudaMemset(g.counters, 0, 4096 * sizeof(uint32_t) + 64) == cudaSuccess ? 0 : -6;
+}
+
+/* Testing hook: writes `value` into split-K tile counter `index` (what an aborted split-K launch leaves behind). */
+int b200_bridge_debug_set_tile_counter(uint32_t index, uint32_t value) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (index >= 4096) return -2;
+    cudaStreamSynchronize(g.stream);
+    return cudaMemcpy(g.counters + index, &value, sizeof(uint32_t), cudaMemcpyHostToDevice) == cudaSuccess ? 0 : -6;
 }
 
 const char* b200_bridge_last_error_string(void) { return g.last_error.c_str(); }

@@ -28,6 +28,7 @@ struct StageSlot {
     bool out_pending = false;        // a copy back from y has been enqueued since the last synchronize
     const char* out_ptr = nullptr;   // host range that copy writes
     size_t out_bytes = 0;
+    uint64_t out_seq = 0;            // State::dispatch_seq when that copy was enqueued
 };
 
 struct State {
@@ -41,6 +42,8 @@ struct State {
     uint64_t slot_seq = 0;
     cudaEvent_t ev_main_d2h = nullptr;   // last copy back issued on the main stream by another entry point
     bool main_d2h_pending = false;
+    uint64_t main_d2h_seq = 0;
+    uint64_t dispatch_seq = 0;           // counts device -> host copies enqueued; synchronize clears marks up to its snapshot
     DevBuf stage_x, stage_w0, stage_w1, stage_y, stage_res, stage_aux0, stage_aux1, stage_aux2;
     DevBuf ws_partial;          // split-K partial tiles
     uint32_t* counters = nullptr;  // 4096 tile counters (kept zero between launches) + error word
@@ -59,5 +62,8 @@ const void* resolve_in(const void* ptr, size_t bytes, DevBuf& stage, bool weight
 void* resolve_out(void* ptr, size_t bytes, DevBuf& stage, void** host_dst, int* rc);
 // Device -> host copy of a staged result on the main stream (entry points other than the projections).
 int copy_back(void* host_dst, const void* dev_src, size_t bytes);
+// Static split-K scratch of the allocation-free entry point (no_alloc.cu): made resident at init, forgotten at shutdown.
+bool static_scratch_prepare(int device);
+void static_scratch_forget();
 
 }  // namespace bridge

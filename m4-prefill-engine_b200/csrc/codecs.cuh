@@ -1,9 +1,10 @@
 // Per-format unpackers: packed weight bytes (held in registers) -> fp16 pairs.
 //
-// One thread owns one weight row.  For every 256-element K chunk it holds the row's packed
-// bytes (`ROW_BYTES`, a multiple of 16 for every format) in registers `r[]` and produces, for
-// each of the four 64-element sub-tiles `s`, 32 words `out[i]` = fp16 pair (k = 2i, 2i+1).  All
-// loops unroll so that register indices are compile-time constants.
+// One thread owns one weight row.  For every K chunk (`CHUNK` elements: 256, or 1024 for the
+// 34-byte Prism blocks, whose rows are a 16-byte multiple only every 1024 elements) it holds the
+// row's packed bytes (`ROW_BYTES`, a multiple of 16 for every format) in registers `r[]` and
+// produces, for each 64-element sub-tile `s` of the chunk, 32 words `out[i]` = fp16 pair
+// (k = 2i, 2i+1).  All loops unroll so that register indices are compile-time constants.
 //
 // Arithmetic follows the reference's device unpackers (quant_router_kernels.metal:111-436): the
 // integer code is turned into an exact fp16 value and one fused fp16 multiply-add applies the
@@ -11,8 +12,8 @@
 // does there.  Integer -> fp16 uses the mantissa trick: 0x6400|q is the fp16 number 1024+q and
 // 0x5400|(q<<4) is 64+q, so a nibble never needs a convert instruction.
 //
-// The same code compiles for the host (tests/test_codecs_host.py builds it with g++ through
-// nvcc -x cu host pass) with `prmt` and the fp16 pair arithmetic emulated, which lets the unpack
+// The same code compiles for the host (tests/codec_host_shim.cpp, built with g++ by
+// tests/test_host_cpu.py) with `prmt` and the fp16 pair arithmetic emulated, which lets the unpack
 // logic be checked bit-for-bit against the CPU oracle without a GPU.
 #pragma once
 #include <cstdint>
@@ -127,6 +128,7 @@ CDC_HD uint32_t lut8_pair(const uint32_t* L, uint32_t q0, uint32_t q1) {
 // HDR_WORDS / sub_lo / sub_hi describe which 32-bit words of the packed row dequant64(r, s, ...) reads: the
 // header words [0, HDR_WORDS) plus the words [sub_lo(s), sub_hi(s)).  The unpack thread loads only those.
 struct CodecDefaults {
+    static constexpr int CHUNK = 256;     // K elements per packed stage (ROW_BYTES bytes of a row)
     static constexpr int HDR_WORDS = 0;
     static constexpr int META_WORDS = 0;
     static constexpr bool ROW_SCALE = false;
@@ -391,6 +393,37 @@ template <> struct Codec<QUANT_TERNARY_ROW> : CodecDefaults {
                 const uint32_t t = q >> (4 * i);
                 const uint32_t x = (t & 3u) | ((t << 14) & 0x30000u) | H2_1024;
                 out[8 * wi + i] = h2sub(x, H2_1025);
+            }
+        }
+    }
+};
+
+// ---- Prism Q2_0, 34 B / 128 (quant_router_kernels.metal:414-436; gold cpu_gold_reference.h:402-440) ------------
+// Block = fp16 d + 32 bytes of 2-bit codes, element 4b+j = (qs[b] >> 2j) & 3, value = (code - 1) * d (code 3 gives
+// +2d, as in the reference on both its paths).  34-byte blocks make a row a 16-byte multiple only every 8 blocks,
+// so the packed stage of this format is 1024 elements = 272 bytes and holds 16 sub-tiles.  Sub-tile s lies in block
+// b = s / 2: its 16 code bytes start at byte 34b + 2 + 16 (s % 2), which is 2 (mod 4) for even b: those are read as
+// five words and shifted by 16 bits.  (code - 1) * d is exact in fp16, so the weights carry no rounding at all.
+template <> struct Codec<QUANT_PRISM_Q2_0> : CodecDefaults {
+    static constexpr int CHUNK = 1024;
+    static constexpr int ROW_BYTES = 272;
+    static constexpr int GROUPS = 3;
+    CDC_HD static constexpr int d_byte(int s) { return 34 * (s / 2); }
+    CDC_HD static constexpr int code_byte(int s) { return 34 * (s / 2) + 2 + 16 * (s % 2); }
+    CDC_HD static constexpr int sub_lo(int s) { return d_byte(s) / 4; }
+    CDC_HD static constexpr int sub_hi(int s) { return (code_byte(s) + 16 + 3) / 4; }
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* = nullptr) {
+        const uint32_t d2 = bcast16(r, d_byte(s));
+        const int c0 = code_byte(s), w0 = c0 / 4;
+#pragma unroll
+        for (int wi = 0; wi < 4; wi++) {
+            // 16 codes of elements 16wi .. 16wi+15 of the sub-tile
+            const uint32_t q = (c0 & 2) ? prmt(r[w0 + wi], r[w0 + wi + 1], 0x5432u) : r[w0 + wi];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t t = q >> (4 * i);
+                const uint32_t x = (t & 3u) | ((t << 14) & 0x30000u) | H2_1024;
+                out[8 * wi + i] = h2mul(h2sub(x, H2_1025), d2);
             }
         }
     }

@@ -14,9 +14,12 @@
 // Limits and rules.
 //   * The split-K scratch a launch needs (k_splits x tiles x tokens-per-tile x 128 floats) must fit
 //     B200_STATIC_SCRATCH_FLOATS; larger requests are refused with -7 and a message, nothing runs.
-//   * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
-//     that device current) and sets the kernel's shared-memory attribute; make that first call
-//     before any stream capture begins.
+//   * m4_bridge_init looks up the array's device address (cudaGetSymbolAddress, with the bridge's
+//     device current) and sets the kernels' shared-memory attributes, so the module image and the
+//     array are resident on the GPU before the host application reserves the rest of its memory:
+//     initialise the bridge first.  A first call on another device does the same look-up itself;
+//     make it at start-up too, and before any stream capture begins.  m4_bridge_shutdown forgets
+//     the cached addresses.
 //   * All calls share the one array.  It keeps whatever the previous call left in it; the tile
 //     counters, which must start at zero, are cleared on the stream before every launch.  Two calls
 //     that overlap on the GPU (different streams, threads or processes sharing the device context)
@@ -65,6 +68,21 @@ cudaError_t scratch_address(int device, StaticScratch** out) {
 }
 
 }  // namespace
+
+namespace bridge {
+// Called by m4_bridge_init (device current): materialises the module image with its scratch array on the GPU and
+// caches the array's address, so that no later call of the entry point below makes the driver reserve memory.
+bool static_scratch_prepare(int device) {
+    StaticScratch* sc = nullptr;
+    if (scratch_address(device, &sc) != cudaSuccess) { cudaGetLastError(); return false; }
+    return true;
+}
+// Called by m4_bridge_shutdown: addresses looked up under a context that may be torn down are not kept.
+void static_scratch_forget() {
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    for (int i = 0; i < MAX_DEVICES; i++) g_scratch_addr[i] = nullptr;
+}
+}  // namespace bridge
 
 using namespace bridge;
 

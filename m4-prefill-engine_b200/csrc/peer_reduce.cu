@@ -45,6 +45,9 @@ struct ReduceParams {
     uint32_t world, rank, rows, K, epoch;
     const float* recv;            // this rank's receive buffer [world][rows][K]
     const __half* residual;       // [M][K], this rank's rows are read
+    const __half* norm_w;         // [K] RMSNorm weights: the rows written to every rank are normalised (nullptr: plain sum)
+    __half* keep;                 // [M][K] local buffer that receives this rank's un-normalised rows (required with norm_w)
+    float eps;
     __half* out[8];
     uint32_t* flags[8];
     const uint32_t* my_flags;
@@ -90,6 +93,77 @@ __global__ void __launch_bounds__(256) reduce_broadcast_kernel(const ReduceParam
     }
 }
 
+// The same reduction for a row-sharded residual stream: one CTA per owned row computes s = fp16(residual + sum of the
+// partial rows), keeps it in the local `keep` buffer (the residual of the block after this one), and writes
+// rmsnorm(s) * w into every rank's copy of the output, so the normalisation runs once per row on its owner instead of
+// on every rank for all rows.  Arithmetic of the normalisation as in lops::rmsnorm_add_kernel.
+__global__ void __launch_bounds__(256) reduce_norm_broadcast_kernel(const ReduceParams p) {
+    __shared__ uint32_t ok_s;
+    __shared__ float red[8];
+    if (threadIdx.x == 0) ok_s = wait_flags(p.my_flags, p.world, p.epoch, p.err, 301, p.wait_limit) ? 1u : 0u;
+    __syncthreads();
+    if (ok_s) {
+        const uint32_t K4 = p.K / 4;
+        const size_t src_stride4 = (size_t)p.rows * K4;
+        const float4* recv4 = reinterpret_cast<const float4*>(p.recv);
+        for (uint32_t r = blockIdx.x; r < p.rows; r += gridDim.x) {
+            const size_t row_el = ((size_t)p.rank * p.rows + r) * p.K;      // first element of the row in [M][K]
+            float ss = 0.0f;
+            for (uint32_t i = threadIdx.x; i < K4; i += blockDim.x) {
+                float4 acc = __ldcg(recv4 + (size_t)r * K4 + i);
+                for (uint32_t s = 1; s < p.world; s++) {
+                    const float4 v = __ldcg(recv4 + s * src_stride4 + (size_t)r * K4 + i);
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                }
+                const uint2 rs = *reinterpret_cast<const uint2*>(p.residual + row_el + i * 4);
+                const __half2 r01 = *reinterpret_cast<const __half2*>(&rs.x), r23 = *reinterpret_cast<const __half2*>(&rs.y);
+                const __half2 h01 = __floats2half2_rn(acc.x + __low2float(r01), acc.y + __high2float(r01));
+                const __half2 h23 = __floats2half2_rn(acc.z + __low2float(r23), acc.w + __high2float(r23));
+                const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+                ss += f01.x * f01.x + f01.y * f01.y + f23.x * f23.x + f23.y * f23.y;
+                uint2 w;
+                w.x = *reinterpret_cast<const uint32_t*>(&h01); w.y = *reinterpret_cast<const uint32_t*>(&h23);
+                *reinterpret_cast<uint2*>(p.keep + row_el + i * 4) = w;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            __syncthreads();                      // the previous row's readers of red[] are done
+            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+            __syncthreads();
+            float tot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) tot += red[i];
+            const float rn = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+            for (uint32_t i = threadIdx.x; i < K4; i += blockDim.x) {
+                const uint2 v = *reinterpret_cast<const uint2*>(p.keep + row_el + i * 4);      // this thread's own stores
+                const uint2 wv = *reinterpret_cast<const uint2*>(p.norm_w + i * 4);
+                const __half2* h = reinterpret_cast<const __half2*>(&v);
+                const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+                uint2 o;
+                __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const float2 f = __half22float2(h[j]), g = __half22float2(wh[j]);
+                    const __half2 n = __floats2half2_rn(f.x * rn, f.y * rn);          // rounded to fp16 first, as the reference does
+                    const float2 nf = __half22float2(n);
+                    oh[j] = __floats2half2_rn(nf.x * g.x, nf.y * g.y);
+                }
+                for (uint32_t d = 0; d < p.world; d++) *reinterpret_cast<uint2*>(p.out[d] + row_el + i * 4) = o;
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t old = atomicAdd(p.done_counter, 1u);
+        if (old == gridDim.x - 1u) {
+            *p.done_counter = 0u;
+            __threadfence_system();
+            for (uint32_t o = 0; o < p.world; o++) st_release_sys(p.flags[o] + 8 + p.rank, p.epoch);
+        }
+    }
+}
+
 __global__ void wait_rows_kernel(const uint32_t* my_flags, uint32_t world, uint32_t epoch, int* err, long long limit) {
     if (threadIdx.x == 0) wait_flags(my_flags + 8, world, epoch, err, 302, limit);
 }
@@ -97,9 +171,11 @@ __global__ void wait_rows_kernel(const uint32_t* my_flags, uint32_t world, uint3
 }  // namespace
 
 cudaError_t reduce_broadcast(const Exchange& x, int which_out, const void* residual, uint32_t M, uint32_t K, int* err,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, const void* norm_w, float eps, void* keep) {
     if (x.world == 0 || x.world > 8 || M % x.world != 0 || K % 4 != 0) return cudaErrorInvalidValue;
+    if (norm_w && (!keep || eps <= 0.0f)) return cudaErrorInvalidValue;
     ReduceParams p;
+    p.norm_w = (const __half*)norm_w; p.keep = (__half*)keep; p.eps = eps;
     p.world = x.world; p.rank = x.rank; p.rows = M / x.world; p.K = K; p.epoch = x.epoch;
     p.recv = x.recv[x.rank];
     p.residual = (const __half*)residual;
@@ -111,7 +187,12 @@ cudaError_t reduce_broadcast(const Exchange& x, int which_out, const void* resid
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    reduce_broadcast_kernel<<<sms * 4, 256, 0, stream>>>(p);
+    if (norm_w) {
+        const uint32_t rows = M / x.world;
+        reduce_norm_broadcast_kernel<<<rows < (uint32_t)sms * 8u ? rows : (uint32_t)sms * 8u, 256, 0, stream>>>(p);
+    } else {
+        reduce_broadcast_kernel<<<sms * 4, 256, 0, stream>>>(p);
+    }
     return cudaGetLastError();
 }
 

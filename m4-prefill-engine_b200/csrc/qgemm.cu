@@ -33,6 +33,7 @@
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
+#include <utility>
 
 #include "codecs.cuh"
 #include "ptx.cuh"
@@ -65,7 +66,7 @@ __device__ __forceinline__ unsigned long long gtimer() { unsigned long long t; a
 
 constexpr int W_TILE = 128;     // weight rows per tile = UMMA M
 constexpr int KSTEP = 64;       // fp16 elements per 128-byte swizzled row
-constexpr int KCHUNK = 256;     // K elements per packed-weight stage
+constexpr int KCHUNK = 256;     // K elements per packed-weight stage (cdc::Codec<FMT>::CHUNK; 1024 for the Prism blocks)
 constexpr int MAX_RAW_STAGES = 6;   // packed-weight ring depth is chosen per launch from the shared memory left over
 constexpr int SMEM_BYTES = 226 * 1024;  // dynamic shared memory of every launch
 constexpr int STAGES = 3;       // ring of unpacked weight tiles (one 64-element K step each)
@@ -84,7 +85,9 @@ template <int FMT> struct Cfg {
     // two phases ahead, which holds when its own previous wait already implied the phase before.
     static constexpr int DQ_GROUPS = cdc::Codec<FMT>::GROUPS;
     static_assert(DQ_GROUPS >= 1 && DQ_GROUPS <= STAGES, "unpack groups are bounded by the operand ring depth");
-    static_assert(STAGES == 3 && KCHUNK / KSTEP == 4, "the unpack loop's ownership counter relies on 4 = 1 (mod STAGES)");
+    static constexpr int CHUNK = cdc::Codec<FMT>::CHUNK;          // K elements per packed stage
+    static constexpr int SUBS = CHUNK / KSTEP;                    // 64-element sub-tiles (MMA steps) per packed stage
+    static_assert(STAGES == 3 && SUBS % STAGES == 1, "the unpack loop's ownership counter relies on SUBS = 1 (mod STAGES)");
     static constexpr int DQ_THREADS = 128 * DQ_GROUPS;   // arrivals that release a packed stage
     static constexpr int FILL_THREADS = 128;             // arrivals that publish an unpacked stage
     // Warp placement.  A warp's scheduler is warp % 4.  The MMA-issuing thread is back-pressured by the tensor
@@ -117,6 +120,8 @@ struct Params {
     uint32_t groups, grp_tiles[3], grp_N[3];
     __half* grp_Y[3];
     GemmArgs::Scatter scatter;   // fused reduce-scatter of fp32 partial sums to peer ranks (world == 0: off)
+    uint32_t tt_shift;           // rotation of the token-tile order (fused reduce-scatter only, else 0)
+    uint32_t tiles_per_owner;    // output tiles whose token rows belong to one rank (fused reduce-scatter only)
     uint32_t swiglu;             // 1: tiles are 64 gate rows (matrix 0) + their 64 up rows (matrix 1); output = silu(g) * u
     const uint8_t* meta0;
     const uint8_t* meta1;
@@ -161,6 +166,9 @@ __device__ __forceinline__ void ld_words(const uint8_t* rowp, uint32_t xr, uint3
     }
 }
 template <int S> struct IntC { static constexpr int value = S; };
+// calls f(IntC<0>{}), f(IntC<1>{}), ... in order: the sub-tiles of one packed stage, each with a compile-time index
+template <class F, int... S>
+__device__ __forceinline__ void for_each_sub(F& f, std::integer_sequence<int, S...>) { (f(IntC<S>{}), ...); }
 
 struct Tile { uint32_t wt, tt, ks, id; };
 __device__ __forceinline__ Tile decode_tile(uint32_t idx, const Params& p) {
@@ -169,14 +177,20 @@ __device__ __forceinline__ Tile decode_tile(uint32_t idx, const Params& p) {
     uint32_t rest = idx / p.k_splits;
     t.wt = rest % p.n_w_tiles;
     t.tt = rest / p.n_w_tiles;
-    t.id = rest;
+    // fused reduce-scatter: rank r starts with the token rows of owner r + 1 and ends with its own, so that at any
+    // time the ranks send to different owners (all ranks walking the owners in the same order would converge on one
+    // owner's NVLink port at a time) and the last, local tiles overlap the tail of the remote transfers
+    if (p.tt_shift) { t.tt += p.tt_shift; if (t.tt >= p.n_tok_tiles) t.tt -= p.n_tok_tiles; }
+    t.id = t.tt * p.n_w_tiles + t.wt;
     return t;
 }
 
-__device__ __forceinline__ size_t out_index(const Params& p, uint32_t tok, uint32_t n) {
+// element (tok, n) of an output of width N_out (p.N, or the width of one matrix of a grouped launch)
+__device__ __forceinline__ size_t out_index(const Params& p, uint32_t tok, uint32_t n, uint32_t N_out) {
     if (p.layout == 1) return ((size_t)(n / p.D) * p.M + tok) * p.D + (n % p.D);
-    return (size_t)tok * p.N + n;
+    return (size_t)tok * N_out + n;
 }
+__device__ __forceinline__ size_t out_index(const Params& p, uint32_t tok, uint32_t n) { return out_index(p, tok, n, p.N); }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
@@ -191,7 +205,15 @@ __device__ __forceinline__ void splitk_fixup(const Params& p, const Tile& t, uin
     const uint32_t total4 = valid * (W_TILE / 4);
     const size_t split_stride = (size_t)(p.n_w_tiles * p.n_tok_tiles) * p.T * W_TILE;
     const float4* base = reinterpret_cast<const float4*>(p.ws_partial + (size_t)t.id * p.T * W_TILE);
-    const bool vec_ok = (p.layout == 1) ? (p.D % 4u == 0u) : (p.N % 4u == 0u);
+    // grouped launch: the matrix this tile belongs to decides the output buffer and its width
+    uint32_t wt_l = t.wt, Ng = p.N;
+    __half* Yg = p.Y;
+    if (p.groups > 1u) {
+        uint32_t gi = 0;
+        if (wt_l >= p.grp_tiles[0]) { wt_l -= p.grp_tiles[0]; gi = 1; if (wt_l >= p.grp_tiles[1]) { wt_l -= p.grp_tiles[1]; gi = 2; } }
+        Ng = p.grp_N[gi]; Yg = p.grp_Y[gi];
+    }
+    const bool vec_ok = (p.layout == 1) ? (p.D % 4u == 0u) : (Ng % 4u == 0u);
     for (uint32_t i0 = tid; i0 < total4; i0 += nthreads * U) {
         float4 v[U][S];
 #pragma unroll
@@ -208,15 +230,15 @@ __device__ __forceinline__ void splitk_fixup(const Params& p, const Tile& t, uin
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int sp = 0; sp < S; sp++) { acc[0] += v[u][sp].x; acc[1] += v[u][sp].y; acc[2] += v[u][sp].z; acc[3] += v[u][sp].w; }
-            const uint32_t tok = tok0 + (i >> 5), n0 = t.wt * W_TILE + (i & 31u) * 4u;
-            if (n0 >= p.N) continue;
+            const uint32_t tok = tok0 + (i >> 5), n0 = wt_l * W_TILE + (i & 31u) * 4u;
+            if (n0 >= Ng) continue;
             if (p.partial_out) {
-                float* dst = p.partial_out + (size_t)tok * p.N + n0;
-                if (vec_ok && n0 + 3u < p.N) *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                float* dst = p.partial_out + (size_t)tok * Ng + n0;
+                if (vec_ok && n0 + 3u < Ng) *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
                 else
-                    for (uint32_t e = 0; e < 4u && n0 + e < p.N; e++) dst[e] = acc[e];
-            } else if (vec_ok && n0 + 3u < p.N) {
-                const size_t o = out_index(p, tok, n0);            // n0 % 4 == 0: the four outputs are contiguous
+                    for (uint32_t e = 0; e < 4u && n0 + e < Ng; e++) dst[e] = acc[e];
+            } else if (vec_ok && n0 + 3u < Ng) {
+                const size_t o = out_index(p, tok, n0, Ng);        // n0 % 4 == 0: the four outputs are contiguous
                 if (p.residual) {
                     const uint2 r = *reinterpret_cast<const uint2*>(p.residual + o);
                     const __half2 r01 = *reinterpret_cast<const __half2*>(&r.x), r23 = *reinterpret_cast<const __half2*>(&r.y);
@@ -226,11 +248,11 @@ __device__ __forceinline__ void splitk_fixup(const Params& p, const Tile& t, uin
                 const __half2 h23 = __halves2half2(__float2half_rn(acc[2]), __float2half_rn(acc[3]));
                 uint2 w;
                 w.x = *reinterpret_cast<const uint32_t*>(&h01); w.y = *reinterpret_cast<const uint32_t*>(&h23);
-                *reinterpret_cast<uint2*>(p.Y + o) = w;
+                *reinterpret_cast<uint2*>(Yg + o) = w;
             } else {
-                for (uint32_t e = 0; e < 4u && n0 + e < p.N; e++) {
-                    const size_t o = out_index(p, tok, n0 + e);
-                    p.Y[o] = __float2half_rn(p.residual ? acc[e] + __half2float(p.residual[o]) : acc[e]);
+                for (uint32_t e = 0; e < 4u && n0 + e < Ng; e++) {
+                    const size_t o = out_index(p, tok, n0 + e, Ng);
+                    Yg[o] = __float2half_rn(p.residual ? acc[e] + __half2float(p.residual[o]) : acc[e]);
                 }
             }
         }
@@ -274,7 +296,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t total_tiles = p.n_w_tiles * p.n_tok_tiles * p.k_splits;
-    const uint32_t ksteps = p.kchunks * (KCHUNK / KSTEP);
+    const uint32_t ksteps = p.kchunks * (uint32_t)C::SUBS;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < MAX_RAW_STAGES; i++) { ptx::mbar_init(&raw_full[i], 1); ptx::mbar_init(&raw_empty[i], C::DQ_THREADS / 32); }
@@ -351,7 +373,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         bool ok = true;
         for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
             const Tile t = decode_tile(idx, p);
-            const uint32_t k0 = t.ks * p.kchunks * KCHUNK;
+            const uint32_t k0 = t.ks * p.kchunks * (uint32_t)C::CHUNK;
             for (uint32_t ks = 0; ks < ksteps; ks++) {
                 ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&b_empty[bs], bph ^ 1u, abort_flag, p.err, 102));
                 if (!ok) break;
@@ -456,7 +478,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 auto sub_tile = [&](auto S) {
                     constexpr int s = decltype(S)::value;
                     // owner of this 64-element step: with G == STAGES the group that owns operand stage
-                    // (step % STAGES); the chunk counter km = (kn / 4) % 3 stands in for kn % 3 (4 = 1 mod 3)
+                    // (step % STAGES); the chunk counter km = (kn / SUBS) % 3 stands in for kn % 3 (SUBS = 1 mod 3)
                     uint32_t own = (G == STAGES) ? km + (uint32_t)(s % STAGES) : (uint32_t)(s % G);
                     if (G == STAGES && own >= (uint32_t)STAGES) own -= (uint32_t)STAGES;
                     if (own == grp) {
@@ -481,9 +503,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                         }
                     }
                 };
-                sub_tile(IntC<0>{}); sub_tile(IntC<1>{}); sub_tile(IntC<2>{}); sub_tile(IntC<3>{});
+                for_each_sub(sub_tile, std::make_integer_sequence<int, C::SUBS>{});
                 km = (km == (uint32_t)STAGES - 1u) ? 0u : km + 1u;
-                kn += KCHUNK / KSTEP;
+                kn += (uint32_t)C::SUBS;
                 // Release the packed stage only now: the stores above consumed every register loaded
                 // from it, so the loads have certainly returned.  (An arrive issued right after the
                 // loads let the next TMA write overtake reads that were still in flight.)
@@ -498,6 +520,29 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         const uint32_t q = warp - C::EPI_WARP0;               // == warp % 4: the TMEM lane quadrant
         const uint32_t et = threadIdx.x - C::EPI_WARP0 * 32;  // 0..127
         uint32_t it = 0, xb_i = 0;
+        // Fused reduce-scatter: tiles this warp has finished for the owner it is currently sending to.  When the owner
+        // changes (and at the end) every lane fences its peer stores at system scope once, the warp adds its count to
+        // the rank-wide counter of that owner, and the warp that completes it (tiles x 4 epilogue warps) raises this
+        // rank's arrival flag on the owner: the owner may reduce its rows while this rank still computes tiles for the
+        // others.  Counting per warp needs no barrier among the epilogue warps, so a warp that gave up on a wait cannot
+        // strand the others.
+        uint32_t sc_owner = 0xffffffffu, sc_count = 0;
+        bool sc_ok = true;
+        auto scatter_flush = [&]() {
+            if (sc_count == 0u) return;
+            __threadfence_system();
+            __syncwarp();
+            if (lane == 0) {
+                const uint32_t old = atomicAdd(p.scatter.done_counter + 4 + sc_owner, sc_count);
+                if (old + sc_count == 4u * p.tiles_per_owner) {
+                    p.scatter.done_counter[4 + sc_owner] = 0u;
+                    __threadfence_system();
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.scatter.flags[sc_owner] + p.scatter.rank), "r"(p.scatter.epoch) : "memory");
+                }
+            }
+            __syncwarp();
+            sc_count = 0u;
+        };
         for (uint32_t idx = blockIdx.x; idx < total_tiles; idx += gridDim.x, it++) {
             const Tile t = decode_tile(idx, p);
             const uint32_t buf = it & 1u;
@@ -512,7 +557,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                     if (n0 + 64u < p.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(line + 128));
                 }
             }
-            if (!ptx::mbar_wait<256>(&tm_full[buf], (it >> 1) & 1u, abort_flag, p.err, 108)) break;
+            if (!ptx::mbar_wait<256>(&tm_full[buf], (it >> 1) & 1u, abort_flag, p.err, 108)) { sc_ok = false; break; }
             if (et == 0) QTRC(6, it, 0);
             ptx::tc_fence_after_sync();
             // grouped launch: the matrix this tile belongs to decides the output buffer and its width
@@ -541,6 +586,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             if (p.scatter.world) {
                 const uint32_t owner = tok0 / p.scatter.rows;
                 partial_dst = p.scatter.recv[owner] + ((ptrdiff_t)p.scatter.rank - (ptrdiff_t)owner) * (ptrdiff_t)p.scatter.rows * (ptrdiff_t)p.N;
+                if (owner != sc_owner) { scatter_flush(); sc_owner = owner; }
+                sc_count++;
             }
             const int mode = p.k_splits > 1 ? 0 : (partial_dst ? 1 : ((RESID && p.residual) ? 2 : 3));
             // integer-valued codecs: the row's scale multiplies the fp32 accumulator (before SiLU, before split-K sums)
@@ -673,6 +720,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 }
             }
         }
+        if (p.scatter.world && sc_ok) scatter_flush();
     }
 
     // ---------------- teardown ----------------
@@ -689,21 +737,6 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     if (warp == 2) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, TMEM_COLS);
-    }
-    if (p.scatter.world) {
-        // every thread's peer stores are fenced at system scope before this CTA is counted; the CTA that completes
-        // the count tells every rank that this rank's partial sums have arrived
-        __threadfence_system();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            const uint32_t old = atomicAdd(p.scatter.done_counter, 1u);
-            if (old == gridDim.x - 1u) {
-                *p.scatter.done_counter = 0u;
-                __threadfence_system();
-                for (uint32_t o = 0; o < p.scatter.world; o++)
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.scatter.flags[o] + p.scatter.rank), "r"(p.scatter.epoch) : "memory");
-            }
-        }
     }
     if (p.k_splits > 1 && *last_flag && !*abort_flag) {
         // Split-K fix-up by the whole CTA: the partial tiles of this output tile are complete (this CTA's arrival
@@ -874,8 +907,10 @@ bool make_map_2d(CUtensorMap* m, CUtensorMapDataType dt, size_t elem, const void
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// bytes of one row of one packed stage (CHUNK elements), 0 for formats without a tensor-core codec
 int row_bytes_256(int fmt) {
     switch (fmt) {
+        case QUANT_PRISM_Q2_0: return 272;       // 8 blocks of 34 bytes per 1024 elements
         case QUANT_Q4_0: return 144;
         case QUANT_MLX_4BIT: return 160;
         case QUANT_Q4_K: return 144;
@@ -887,6 +922,8 @@ int row_bytes_256(int fmt) {
         default: return 0;
     }
 }
+
+uint32_t chunk_elems(int fmt) { return fmt == QUANT_PRISM_Q2_0 ? 1024u : (uint32_t)KCHUNK; }
 
 int g_sm_count = 0;
 int sm_count() {
@@ -910,7 +947,7 @@ Plan make_plan(const GemmArgs& a) {
     const uint32_t rows_per_tile = a.W1 ? GATE_ROWS : W_TILE;    // output features per tile
     pl.n_w_tiles = (a.N + rows_per_tile - 1) / rows_per_tile;
     for (uint32_t e = 0; e < a.n_extra && e < 2u; e++) pl.n_w_tiles += (a.N_extra[e] + W_TILE - 1) / W_TILE;   // grouped launch
-    const uint32_t chunks = a.K / KCHUNK;
+    const uint32_t chunks = a.K / chunk_elems(a.format);
     pl.k_splits = 1;
     if (!a.W1 && !a.scatter.world) {       // (the fused reduce-scatter epilogue writes whole tiles: no K split)
         // split K while the grid would leave most SMs idle and every split keeps >= 2 chunks
@@ -926,12 +963,27 @@ Plan make_plan(const GemmArgs& a) {
     return pl;
 }
 
+// The dynamic shared-memory attribute is per device: set once for every device a launch (or prepare_device) sees.
+template <int FMT>
+cudaError_t set_kernel_attributes() {
+    static uint64_t done_mask = 0;          // bit d: set on device d
+    static std::mutex mu;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && (done_mask >> dev) & 1u) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(qgemm_kernel<FMT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(qgemm_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e == cudaSuccess && dev >= 0 && dev < 64) done_mask |= 1ull << dev;
+    return e;
+}
+
 template <int FMT>
 cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t stream) {
     using C = Cfg<FMT>;
     const Plan pl = make_plan(a);
     const int rb = cdc::Codec<FMT>::ROW_BYTES;
-    const uint64_t w_row_bytes = (uint64_t)(a.K / KCHUNK) * rb;
+    const uint64_t w_row_bytes = (uint64_t)(a.K / C::CHUNK) * rb;
     CUtensorMap tmX, tmW0, tmW1, tmW2;
     if (!make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.X, a.K, a.M, (uint64_t)a.K * 2, KSTEP, pl.T,
                      CU_TENSOR_MAP_SWIZZLE_128B))
@@ -942,7 +994,7 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
         return cudaErrorInvalidValue;
     // second / third map: the up matrix of a SwiGLU launch, or the extra matrices of a grouped launch
     const bool grouped = a.n_extra > 0;
-    if (grouped && (a.n_extra > 2 || a.W1 || a.residual || a.partial_out || a.scatter.world || pl.k_splits != 1 ||
+    if (grouped && (a.n_extra > 2 || a.W1 || a.residual || a.partial_out || a.scatter.world ||
                     cdc::Codec<FMT>::META_WORDS != 0 || cdc::Codec<FMT>::ROW_SCALE))
         return cudaErrorInvalidValue;
     const void* w1 = a.W1 ? a.W1 : (grouped ? a.W_extra[0] : a.W0);
@@ -970,6 +1022,11 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
         p.grp_N[1 + e] = on ? a.N_extra[e] : 0u; p.grp_Y[1 + e] = on ? (__half*)a.Y_extra[e] : nullptr;
     }
     if (a.scatter.world && (pl.k_splits != 1 || a.W1 || a.scatter.rows % pl.T != 0 || a.scatter.rows * a.scatter.world != a.M)) return cudaErrorInvalidValue;
+    p.tt_shift = 0; p.tiles_per_owner = 0;
+    if (a.scatter.world) {
+        p.tiles_per_owner = pl.n_w_tiles * (a.scatter.rows / pl.T);
+        p.tt_shift = ((a.scatter.rank + 1u) % a.scatter.world) * (a.scatter.rows / pl.T);
+    }
     p.layout = (uint32_t)a.layout; p.H = a.H; p.D = a.D ? a.D : 1;
     p.ws_partial = ws.partial; p.ws_counters = ws.counters; p.err = ws.err;
     // planar layouts: everything behind the N x (K/256 * ROW_BYTES) plane of packed values
@@ -984,15 +1041,7 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     }
 
     constexpr size_t smem = SMEM_BYTES;
-    static int attr_device = -1;            // the attribute is per device; one device per process is the normal case
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (attr_device != dev) {
-        cudaError_t e = cudaFuncSetAttribute(qgemm_kernel<FMT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(qgemm_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        attr_device = dev;
-    }
+    { cudaError_t e = set_kernel_attributes<FMT>(); if (e != cudaSuccess) return e; }
     const uint32_t total = pl.n_tok_tiles * pl.n_w_tiles * pl.k_splits;
     const uint32_t grid = total < (uint32_t)sm_count() ? total : (uint32_t)sm_count();
     // Programmatic stream serialization: this grid's CTAs may be placed (and run their prologue up to
@@ -1020,6 +1069,7 @@ cudaError_t dispatch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t s
         case QUANT_EXL3: return launch_fast<QUANT_EXL3>(a, ws, s);
         case QUANT_MLX_4BIT_G64: return launch_fast<QUANT_MLX_4BIT_G64>(a, ws, s);
         case QUANT_TERNARY_ROW: return launch_fast<QUANT_TERNARY_ROW>(a, ws, s);
+        case QUANT_PRISM_Q2_0: return launch_fast<QUANT_PRISM_Q2_0>(a, ws, s);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -1028,10 +1078,23 @@ thread_local int g_last_launches = 0;
 
 }  // namespace
 
+cudaError_t prepare_device() {
+    cudaError_t e = set_kernel_attributes<QUANT_Q4_0>();
+    if (e == cudaSuccess) e = set_kernel_attributes<QUANT_MLX_4BIT>();
+    if (e == cudaSuccess) e = set_kernel_attributes<QUANT_Q4_K>();
+    if (e == cudaSuccess) e = set_kernel_attributes<QUANT_TERNARY_1_58>();
+    if (e == cudaSuccess) e = set_kernel_attributes<QUANT_VAR_RATE_AFFINE>();
+    if (e == cudaSuccess) e = set_kernel_attributes<QUANT_EXL3>();
+    if (e == cudaSuccess) e = set_kernel_attributes<QUANT_MLX_4BIT_G64>();
+    if (e == cudaSuccess) e = set_kernel_attributes<QUANT_TERNARY_ROW>();
+    if (e == cudaSuccess) e = set_kernel_attributes<QUANT_PRISM_Q2_0>();
+    return e;
+}
+
 bool fast_path_ok(const GemmArgs& a) {
     if (a.force_generic) return false;
     if (row_bytes_256(a.format) == 0) return false;
-    if (a.K == 0 || a.K % KCHUNK != 0) return false;
+    if (a.K == 0 || a.K % chunk_elems(a.format) != 0) return false;
     if (((uintptr_t)a.X & 15u) || ((uintptr_t)a.W0 & 15u) || (a.W1 && ((uintptr_t)a.W1 & 15u))) return false;
     for (uint32_t e = 0; e < a.n_extra && e < 2u; e++)
         if (!a.W_extra[e] || ((uintptr_t)a.W_extra[e] & 15u) || !a.Y_extra[e] || a.N_extra[e] == 0) return false;

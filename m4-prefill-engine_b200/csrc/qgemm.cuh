@@ -27,14 +27,15 @@ struct GemmArgs {
     uint32_t N_extra[2];
     // Tensor-parallel reduce-scatter fused into the epilogue (row-split projections): instead of one local fp32
     // [M][N] buffer, token rows [o * rows, (o + 1) * rows) go to rank o's receive buffer, slot `rank`, through
-    // peer-mapped pointers.  When the grid's last CTA is done it raises flag `rank` in every rank's flag array to
-    // `epoch` (stores fenced at system scope).  world == 0: off.
+    // peer-mapped pointers.  Rank r works through the owners in the order r + 1, r + 2, ..., r (its own rows last);
+    // when all tiles of owner o are stored and fenced at system scope, flag `rank` in rank o's flag array is raised
+    // to `epoch`.  world == 0: off.
     struct Scatter {
         uint32_t world, rank, rows;      // rows = M / world token rows owned by each rank (a multiple of the token tile)
         float* recv[8];                  // recv[o]: rank o's buffer, fp32 [world][rows][N]
         uint32_t* flags[8];              // flags[o]: rank o's arrival flags, one word per source rank
         uint32_t epoch;
-        uint32_t* done_counter;          // device-local word, zero between launches
+        uint32_t* done_counter;          // 16 device-local words, zero between launches (words 4..11: one tile counter per owner)
     } scatter;
 };
 
@@ -45,6 +46,9 @@ struct Workspace {            // split-K scratch, owned by the caller
     int* err = nullptr;       // device error word (0 = ok)
 };
 
+// Sets the dynamic shared-memory attribute of every kernel instantiation on the current device (which also loads the
+// module image there).  Called once per device at initialisation; launches repeat it only for a device they have not seen.
+cudaError_t prepare_device();
 // True if (format, shape, pointers) can take the TMA + tcgen05 path.
 bool fast_path_ok(const GemmArgs& a);
 // Floats of split-K scratch the launch will use (0 when it does not split).

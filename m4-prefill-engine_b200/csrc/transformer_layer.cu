@@ -7,6 +7,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "../../include/b200_bridge.h"
 #include "../../include/transformer_layer.h"
@@ -30,9 +31,15 @@ struct TransformerLayerCoordinator::Impl {
     AllReduceFn allreduce = nullptr;
     void* allreduce_ctx = nullptr;
     KernelBinding gemm_binding, head_binding;
-    peer::Exchange px;               // fused tensor-parallel reduction over peer memory (world == 0: not set)
+    peer::Exchange own_px;           // exchange attached with set_peer_exchange (buffers of this layer alone)
+    peer::Exchange* px = nullptr;    // the exchange in use: &own_px, or one shared by the layers of a model (nullptr: none)
     bool bound = false;
     cudaStream_t stream = nullptr;
+    // per-launch timing of one forward (profile_forward): an event after every launch
+    bool profiling = false;
+    std::vector<cudaEvent_t> events;
+    std::vector<std::string> labels;
+    size_t n_marks = 0;
 };
 
 static bool dev_alloc(void** p, size_t bytes) {
@@ -49,8 +56,9 @@ TransformerLayerCoordinator::TransformerLayerCoordinator(int device, cudaStream_
 
 TransformerLayerCoordinator::~TransformerLayerCoordinator() {
     void* bufs[] = {impl_->xn, impl_->q, impl_->k, impl_->v, impl_->kq, impl_->vq, impl_->attn, impl_->x_mid, impl_->act,
-                    impl_->partial, impl_->ws, impl_->counters, impl_->px.done_counter};
+                    impl_->partial, impl_->ws, impl_->counters, impl_->own_px.done_counter};
     for (void* b : bufs) if (b) cudaFree(b);
+    for (cudaEvent_t e : impl_->events) cudaEventDestroy(e);
     delete impl_;
 }
 
@@ -113,17 +121,49 @@ bool TransformerLayerCoordinator::set_peer_exchange(uint32_t rank, uint32_t worl
                                                     void* const* out1, void* const* flags) {
     const TransformerLayerConfig& c = config_;
     if (world != c.tp_size || world < 2 || world > 8 || rank >= world || c.M % world != 0 || (c.M / world) % 256 != 0) return false;
-    peer::Exchange& x = impl_->px;
+    peer::Exchange& x = impl_->own_px;
     if (!x.done_counter) {
-        if (!dev_alloc((void**)&x.done_counter, 16)) return false;
-        cudaMemset(x.done_counter, 0, 16);
+        if (!dev_alloc((void**)&x.done_counter, 64)) return false;
+        cudaMemset(x.done_counter, 0, 64);
     }
     for (uint32_t o = 0; o < world; o++) {
         if (!recv[o] || !out0[o] || !out1[o] || !flags[o]) return false;
         x.recv[o] = (float*)recv[o]; x.out[0][o] = out0[o]; x.out[1][o] = out1[o]; x.flags[o] = (uint32_t*)flags[o];
     }
-    x.rank = rank; x.world = world; x.epoch = 0;
+    x.rank = rank; x.world = world;
+    // The epoch belongs to the buffers, not to the layer: flags only grow, and buffers that have been used before
+    // (by this layer or another one) hold the last epoch of that use.  An idle exchange has the same value in every
+    // flag word of every rank, so this rank's own word tells where to continue.
+    uint32_t seen = 0;
+    cudaStreamSynchronize(impl_->stream);
+    if (cudaMemcpy(&seen, x.flags[rank] + rank, sizeof(uint32_t), cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return false; }
+    x.epoch = seen;
+    impl_->px = &x;
     return true;
+}
+
+bool TransformerLayerCoordinator::attach_peer_exchange(peer::Exchange* shared) {
+    const TransformerLayerConfig& c = config_;
+    if (!shared || shared->world != c.tp_size || shared->world < 2 || c.M % shared->world != 0 || (c.M / shared->world) % 256 != 0 ||
+        !shared->done_counter)
+        return false;
+    impl_->px = shared;       // epoch, flags and counters live with the buffers: any number of layers may take turns on them
+    return true;
+}
+
+void TransformerLayerCoordinator::set_profiling(bool on) { impl_->profiling = on; }
+
+size_t TransformerLayerCoordinator::profile(const char** labels, float* us, size_t cap) const {
+    const Impl& im = *impl_;
+    if (im.n_marks < 2) return 0;
+    size_t n = 0;
+    for (size_t i = 1; i < im.n_marks && n < cap; i++, n++) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, im.events[i - 1], im.events[i]) != cudaSuccess) { cudaGetLastError(); ms = -1.0f; }
+        us[n] = ms * 1000.0f;
+        labels[n] = im.labels[i].c_str();
+    }
+    return n;
 }
 
 void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in, const void* W_q, const void* W_k,
@@ -135,7 +175,7 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
     if (!im.bound) { status_ = -1; return; }
     if (!X_in || !W_q || !W_k || !W_v || !W_o || !W_gate || !W_up || !W_down || !X_out) { status_ = -2; return; }
     if (c.rms_eps > 0.0f && (!im.norm1 || !im.norm2)) { status_ = -2; return; }
-    if (c.tp_size > 1 && !im.allreduce && !im.px.world) { status_ = -2; return; }
+    if (c.tp_size > 1 && !im.allreduce && !im.px) { status_ = -2; return; }
     status_ = 0;
     const uint32_t hq = c.H / c.tp_size, hkv = c.num_kv_heads / c.tp_size, f = c.N_mlp / c.tp_size;
     qg::Workspace ws;
@@ -151,10 +191,23 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
         launches_ += (uint32_t)qg::last_launch_count();
     };
     auto check = [&](cudaError_t e) { if (e != cudaSuccess && !status_) status_ = -6; else launches_++; };
+    // profiling: an event after every step; label i names what ran between event i-1 and event i
+    im.n_marks = 0;
+    auto mark = [&](const char* what) {
+        if (!im.profiling) return;
+        if (im.n_marks == im.events.size()) {
+            cudaEvent_t e = nullptr;
+            if (cudaEventCreate(&e) != cudaSuccess) { cudaGetLastError(); return; }
+            im.events.push_back(e); im.labels.emplace_back();
+        }
+        im.labels[im.n_marks] = what;
+        cudaEventRecord(im.events[im.n_marks++], stream);
+    };
+    mark("start");
 
     // 1. attention block
     const void* x_attn = X_in;
-    if (c.rms_eps > 0.0f) { check(lops::rmsnorm(X_in, im.norm1, im.xn, c.M, c.K, c.rms_eps, stream)); x_attn = im.xn; }
+    if (c.rms_eps > 0.0f) { check(lops::rmsnorm(X_in, im.norm1, im.xn, c.M, c.K, c.rms_eps, stream)); x_attn = im.xn; mark("rmsnorm 1"); }
     // Q, K and V read the same activations: one grouped launch (their weight tiles share the persistent grid, so
     // the two narrow projections do not each leave most SMs idle); separate launches where that is not available
     bool qkv_done = false;
@@ -164,31 +217,38 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
         a.layout = im.head_binding.layout; a.H = hq; a.D = c.D;
         a.n_extra = 2; a.W_extra[0] = W_k; a.W_extra[1] = W_v; a.Y_extra[0] = im.k; a.Y_extra[1] = im.v;
         a.N_extra[0] = a.N_extra[1] = hkv * c.D;
-        if (qg::launch(a, ws, stream) == cudaSuccess) { qkv_done = true; launches_ += (uint32_t)qg::last_launch_count(); }
+        if (qg::launch(a, ws, stream) == cudaSuccess) { qkv_done = true; launches_ += (uint32_t)qg::last_launch_count(); mark("q+k+v projections (grouped)"); }
         else cudaGetLastError();
     }
     if (!qkv_done) {
         gemm(im.head_binding, x_attn, W_q, nullptr, im.q, hq * c.D, c.K, hq, nullptr, nullptr);
         gemm(im.head_binding, x_attn, W_k, nullptr, im.k, hkv * c.D, c.K, hkv, nullptr, nullptr);
         gemm(im.head_binding, x_attn, W_v, nullptr, im.v, hkv * c.D, c.K, hkv, nullptr, nullptr);
+        mark("q, k, v projections (3 launches)");
     }
     if (c.rope_theta > 0.0f) {
         check(lops::rope(im.q, hq, c.M, c.D, c.rope_theta, 0, stream));
         check(lops::rope(im.k, hkv, c.M, c.D, c.rope_theta, 0, stream));
+        mark("rope q, k");
     }
     const void *kk = im.k, *vv = im.v;
     if (c.kv_q8_0) {
         check(attn::launch_quantize(im.k, im.kq, (size_t)hkv * c.M * c.D, stream));
         check(attn::launch_quantize(im.v, im.vq, (size_t)hkv * c.M * c.D, stream));
         kk = im.kq; vv = im.vq;
+        mark("quantize k, v to q8_0");
     }
     check(attn::launch_attention_simple(im.q, kk, vv, im.attn, hq, hkv, c.M, c.M, c.D, c.attn_scale, 0, 1, c.kv_q8_0 ? 0 : 1, stream));
+    mark("attention");
     // 2. O projection + first residual
     const void* x_mid = im.x_mid;
     // row-split projection with the reduction fused in: scatter in the epilogue, owner reduces and broadcasts
-    auto reduced_gemm = [&](const void* X, const void* W, uint32_t Kin, const void* residual, int which_out) {
+    // `norm_w` != nullptr: the owner normalises its rows before writing them to every rank and keeps the plain rows
+    // (the next block's residual) in `keep`.
+    auto reduced_gemm = [&](const void* X, const void* W, uint32_t Kin, const void* residual, int which_out, const void* norm_w,
+                            void* keep, const char* what) {
         if (status_) return;
-        peer::Exchange& x = im.px;
+        peer::Exchange& x = *im.px;
         x.epoch++;
         qg::GemmArgs a; memset(&a, 0, sizeof(a));
         a.format = im.gemm_binding.format; a.X = X; a.W0 = W; a.M = c.M; a.N = c.K; a.K = Kin; a.layout = im.gemm_binding.layout;
@@ -197,47 +257,69 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
         for (uint32_t o = 0; o < x.world; o++) { a.scatter.recv[o] = x.recv[o]; a.scatter.flags[o] = x.flags[o]; }
         if (qg::launch(a, ws, stream) != cudaSuccess) { status_ = -6; return; }
         launches_ += (uint32_t)qg::last_launch_count();
-        check(peer::reduce_broadcast(x, which_out, residual, c.M, c.K, im.err, stream));
+        mark(what);
+        check(peer::reduce_broadcast(x, which_out, residual, c.M, c.K, im.err, stream, norm_w, c.rms_eps, keep));
+        mark(norm_w ? "owner: sum + residual + rmsnorm -> all ranks" : "owner: sum + residual -> all ranks");
         check(peer::wait_rows(x, im.err, stream));
+        mark("wait for all ranks' rows");
     };
     // One GPU with a normalisation after the attention block: the O projection writes its plain fp16 output and the
     // residual add rides on the RMSNorm kernel that has to read that output anyway (the projection's residual epilogue
     // costs about 20 us per launch at M=2048; the extra operand of the normalisation about 3 us).  The block output is
     // fp16(fp16(attn * Wo) + x), the rounding of an unfused add.
     const bool fuse_add_norm = c.tp_size == 1 && c.rms_eps > 0.0f && c.K % 8u == 0u && (reinterpret_cast<uintptr_t>(X_in) & 15u) == 0;
+    // fused exchange with a normalisation behind it: the residual stream stays sharded by rows between the two
+    // reductions (x_mid holds this rank's rows only) and the rows every rank receives are already normalised
+    const bool px_norm = im.px && c.rms_eps > 0.0f && c.K % 4u == 0u;
     if (fuse_add_norm) {
         gemm(im.gemm_binding, im.attn, W_o, nullptr, im.xn, c.K, hq * c.D, 0, nullptr, nullptr);
+        mark("o projection");
     } else if (c.tp_size == 1) {
         gemm(im.gemm_binding, im.attn, W_o, nullptr, im.x_mid, c.K, hq * c.D, 0, X_in, nullptr);
-    } else if (im.px.world) {
-        reduced_gemm(im.attn, W_o, hq * c.D, X_in, 0);
-        x_mid = im.px.out[0][im.px.rank];
+        mark("o projection + residual");
+    } else if (im.px) {
+        reduced_gemm(im.attn, W_o, hq * c.D, X_in, 0, px_norm ? im.norm2 : nullptr, px_norm ? im.x_mid : nullptr,
+                     "o projection, partial rows scattered to their owners");
+        if (!px_norm) x_mid = im.px->out[0][im.px->rank];
     } else {
         gemm(im.gemm_binding, im.attn, W_o, nullptr, nullptr, c.K, hq * c.D, 0, nullptr, im.partial);
         if (!status_) im.allreduce(im.allreduce_ctx, im.partial, (size_t)c.M * c.K, stream);
         check(lops::add_residual_f32(X_in, im.partial, im.x_mid, (size_t)c.M * c.K, stream));
+        mark("o projection + all-reduce + residual");
     }
     // 3. MLP
     const void* x_mlp = x_mid;
-    if (fuse_add_norm) { check(lops::rmsnorm_add(im.xn, X_in, im.norm2, im.x_mid, im.xn, c.M, c.K, c.rms_eps, stream)); x_mlp = im.xn; }
-    else if (c.rms_eps > 0.0f) { check(lops::rmsnorm(x_mid, im.norm2, im.xn, c.M, c.K, c.rms_eps, stream)); x_mlp = im.xn; }
+    if (fuse_add_norm) { check(lops::rmsnorm_add(im.xn, X_in, im.norm2, im.x_mid, im.xn, c.M, c.K, c.rms_eps, stream)); x_mlp = im.xn; mark("residual + rmsnorm 2"); }
+    else if (px_norm) x_mlp = im.px->out[0][im.px->rank];
+    else if (c.rms_eps > 0.0f) { check(lops::rmsnorm(x_mid, im.norm2, im.xn, c.M, c.K, c.rms_eps, stream)); x_mlp = im.xn; mark("rmsnorm 2"); }
     gemm(im.gemm_binding, x_mlp, W_gate, W_up, im.act, f, c.K, 0, nullptr, nullptr);
+    mark("gate/up SwiGLU");
     // Same trade for the MLP block's residual: with no kernel behind it to carry the add, a 16-byte-wide add kernel
     // (about 5 us with its launch) replaces the projection's residual epilogue (about 20 us).  im.xn is free again
     // once the gate/up launch has been queued (stream order).
     const bool split_add = fuse_add_norm && ((size_t)c.M * c.K) % 8u == 0u && (reinterpret_cast<uintptr_t>(X_out) & 15u) == 0;
     if (split_add) {
         gemm(im.gemm_binding, im.act, W_down, nullptr, im.xn, c.K, f, 0, nullptr, nullptr);
+        mark("down projection");
         check(lops::add_residual_f16(im.x_mid, im.xn, X_out, (size_t)c.M * c.K, stream));
+        mark("residual add");
     } else if (c.tp_size == 1) {
         gemm(im.gemm_binding, im.act, W_down, nullptr, X_out, c.K, f, 0, im.x_mid, nullptr);
-    } else if (im.px.world) {
-        reduced_gemm(im.act, W_down, f, x_mid, 1);
-        if (!status_) check(cudaMemcpyAsync(X_out, im.px.out[1][im.px.rank], (size_t)c.M * c.K * 2, cudaMemcpyDeviceToDevice, stream));
+        mark("down projection + residual");
+    } else if (im.px) {
+        // (x_mid: this rank's rows are all the owner's reduction reads)
+        reduced_gemm(im.act, W_down, f, x_mid, 1, nullptr, nullptr, "down projection, partial rows scattered to their owners");
+        // the result sits in this rank's copy of the second result buffer; a caller that hands that very buffer in as
+        // X_out (the layers of a model do) needs no copy
+        if (!status_ && X_out != im.px->out[1][im.px->rank]) {
+            check(cudaMemcpyAsync(X_out, im.px->out[1][im.px->rank], (size_t)c.M * c.K * 2, cudaMemcpyDeviceToDevice, stream));
+            mark("copy result out of the exchange buffer");
+        }
     } else {
         gemm(im.gemm_binding, im.act, W_down, nullptr, nullptr, c.K, f, 0, nullptr, im.partial);
         if (!status_) im.allreduce(im.allreduce_ctx, im.partial, (size_t)c.M * c.K, stream);
         check(lops::add_residual_f32(im.x_mid, im.partial, X_out, (size_t)c.M * c.K, stream));
+        mark("down projection + all-reduce + residual");
     }
 }
 
@@ -345,6 +427,63 @@ int b200_layer_set_peer_exchange(void* layer, uint32_t rank, uint32_t world, voi
     return ((LayerHandle*)layer)->layer->set_peer_exchange(rank, world, recv, out0, out1, flags) ? 0 : -4;
 }
 
+void* b200_peer_exchange_create(uint32_t rank, uint32_t world, void* const* recv, void* const* out0, void* const* out1,
+                                void* const* flags) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized || !recv || !out0 || !out1 || !flags || world < 2 || world > 8 || rank >= world) return nullptr;
+    peer::Exchange* x = new peer::Exchange;
+    for (uint32_t o = 0; o < world; o++) {
+        if (!recv[o] || !out0[o] || !out1[o] || !flags[o]) { delete x; return nullptr; }
+        x->recv[o] = (float*)recv[o]; x->out[0][o] = out0[o]; x->out[1][o] = out1[o]; x->flags[o] = (uint32_t*)flags[o];
+    }
+    x->rank = rank; x->world = world;
+    if (cudaMalloc((void**)&x->done_counter, 64) != cudaSuccess) { cudaGetLastError(); delete x; return nullptr; }
+    cudaMemset(x->done_counter, 0, 64);
+    uint32_t seen = 0;                         // buffers that were used before continue from their last epoch
+    cudaStreamSynchronize(g.stream);
+    if (cudaMemcpy(&seen, x->flags[rank] + rank, sizeof(uint32_t), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError(); cudaFree(x->done_counter); delete x; return nullptr;
+    }
+    x->epoch = seen;
+    return x;
+}
+
+void b200_peer_exchange_destroy(void* exchange) {
+    if (!exchange) return;
+    std::lock_guard<std::mutex> lock(g.mu);
+    peer::Exchange* x = (peer::Exchange*)exchange;
+    if (g.initialized) cudaStreamSynchronize(g.stream);
+    if (x->done_counter) cudaFree(x->done_counter);
+    delete x;
+}
+
+int b200_layer_attach_peer_exchange(void* layer, void* exchange) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!layer || !exchange) return -2;
+    return ((LayerHandle*)layer)->layer->attach_peer_exchange((peer::Exchange*)exchange) ? 0 : -4;
+}
+
+int b200_layer_set_profiling(void* layer, int on) {
+    if (!layer) return -2;
+    ((LayerHandle*)layer)->layer->set_profiling(on != 0);
+    return 0;
+}
+
+int b200_layer_profile(void* layer, char* labels, size_t label_bytes, float* us, size_t cap) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!layer || !labels || !us || label_bytes == 0) return -2;
+    cudaStreamSynchronize(g.stream);
+    std::vector<const char*> names(cap);
+    const size_t n = ((LayerHandle*)layer)->layer->profile(names.data(), us, cap);
+    for (size_t i = 0; i < n; i++) {
+        strncpy(labels + i * label_bytes, names[i], label_bytes - 1);
+        labels[i * label_bytes + label_bytes - 1] = 0;
+    }
+    return (int)n;
+}
+
 int b200_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64) {
     std::lock_guard<std::mutex> lock(g.mu);
     if (!g.initialized) return -1;
@@ -381,8 +520,8 @@ namespace {
 uint32_t* g_peer_counter = nullptr;      // two words for the primitive entry points below
 bool peer_counter_ready() {
     if (g_peer_counter) return true;
-    if (cudaMalloc((void**)&g_peer_counter, 16) != cudaSuccess) { cudaGetLastError(); g_peer_counter = nullptr; return false; }
-    cudaMemsetAsync(g_peer_counter, 0, 16, g.stream);
+    if (cudaMalloc((void**)&g_peer_counter, 64) != cudaSuccess) { cudaGetLastError(); g_peer_counter = nullptr; return false; }
+    cudaMemsetAsync(g_peer_counter, 0, 64, g.stream);
     return true;
 }
 }  // namespace
@@ -417,6 +556,21 @@ int b200_peer_reduce_broadcast(uint32_t rank, uint32_t world, void* const* recv,
     x.world = world; x.rank = rank; x.epoch = epoch; x.done_counter = g_peer_counter;
     for (uint32_t o = 0; o < world; o++) { x.recv[o] = (float*)recv[o]; x.out[0][o] = out[o]; x.flags[o] = (uint32_t*)flags[o]; }
     if (peer::reduce_broadcast(x, 0, residual, M, K, g.err_word, g.stream) != cudaSuccess) { cudaGetLastError(); return -4; }
+    g.launches++;
+    return 0;
+}
+
+int b200_peer_reduce_norm_broadcast(uint32_t rank, uint32_t world, void* const* recv, void* const* out, void* const* flags,
+                                    uint32_t epoch, const void* residual, uint32_t M, uint32_t K, const void* norm_w, float eps,
+                                    void* keep) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!recv || !out || !flags || !residual || !norm_w || !keep || world < 1 || world > 8 || rank >= world) return -2;
+    if (!peer_counter_ready()) return -5;
+    peer::Exchange x;
+    x.world = world; x.rank = rank; x.epoch = epoch; x.done_counter = g_peer_counter;
+    for (uint32_t o = 0; o < world; o++) { x.recv[o] = (float*)recv[o]; x.out[0][o] = out[o]; x.flags[o] = (uint32_t*)flags[o]; }
+    if (peer::reduce_broadcast(x, 0, residual, M, K, g.err_word, g.stream, norm_w, eps, keep) != cudaSuccess) { cudaGetLastError(); return -4; }
     g.launches++;
     return 0;
 }

@@ -70,8 +70,18 @@ def _bind_layer(lib) -> None:
     lib.b200_peer_gemm_scatter.argtypes = [vp, vp, ctypes.c_int, u32, u32, u32, u32, u32, pp, pp, u32]
     lib.b200_peer_reduce_broadcast.argtypes = [u32, u32, pp, pp, pp, u32, vp, u32, u32]
     lib.b200_peer_wait_rows.argtypes = [u32, u32, pp, u32]
+    lib.b200_peer_reduce_norm_broadcast.argtypes = [u32, u32, pp, pp, pp, u32, vp, u32, u32, vp, ctypes.c_float, vp]
+    lib.b200_peer_reduce_norm_broadcast.restype = ctypes.c_int
+    lib.b200_peer_exchange_create.argtypes = [u32, u32, pp, pp, pp, pp]
+    lib.b200_peer_exchange_create.restype = vp
+    lib.b200_peer_exchange_destroy.argtypes = [vp]
+    lib.b200_peer_exchange_destroy.restype = None
+    lib.b200_layer_attach_peer_exchange.argtypes = [vp, vp]
+    lib.b200_layer_set_profiling.argtypes = [vp, ctypes.c_int]
+    lib.b200_layer_profile.argtypes = [vp, ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_float), ctypes.c_size_t]
     for f in ("b200_peer_alloc", "b200_peer_open", "b200_peer_close", "b200_peer_free", "b200_layer_set_peer_exchange",
-              "b200_peer_gemm_scatter", "b200_peer_reduce_broadcast", "b200_peer_wait_rows"):
+              "b200_peer_gemm_scatter", "b200_peer_reduce_broadcast", "b200_peer_wait_rows", "b200_layer_attach_peer_exchange",
+              "b200_layer_set_profiling", "b200_layer_profile"):
         getattr(lib, f).restype = ctypes.c_int
     lib._layer_bound = True
 
@@ -123,6 +133,29 @@ class TransformerLayerCoordinator:
             raise RuntimeError(f"b200_layer_set_peer_exchange failed with status code {rc} "
                                "(needs tp_size == world and M / world a multiple of 256)")
 
+    def attach_peer_exchange(self, px: "PeerExchange") -> None:
+        """Use an exchange that other layers use as well (the layers of a model take turns on one set of buffers)."""
+        rc = self.lib.b200_layer_attach_peer_exchange(self._h, px.handle)
+        if rc:
+            raise RuntimeError(f"b200_layer_attach_peer_exchange failed with status code {rc} "
+                               "(needs tp_size == world and M / world a multiple of 256)")
+
+    def profile_forward(self, *tensors) -> list:
+        """One forward with a CUDA event after every launch: [(what ran, microseconds), ...] in launch order."""
+        self.lib.b200_layer_set_profiling(self._h, 1)
+        try:
+            self.forward(*tensors)
+            cap, lb = 64, 96
+            labels = ctypes.create_string_buffer(cap * lb)
+            us = (ctypes.c_float * cap)()
+            n = self.lib.b200_layer_profile(self._h, labels, lb, us, cap)
+        finally:
+            self.lib.b200_layer_set_profiling(self._h, 0)
+        if n < 0:
+            raise RuntimeError(f"b200_layer_profile failed with status code {n}")
+        raw = labels.raw
+        return [(raw[i * lb:(i + 1) * lb].split(b"\0", 1)[0].decode(), round(float(us[i]), 2)) for i in range(n)]
+
     def forward(self, X_in, W_q, W_k, W_v, W_o, W_gate, W_up, W_down, X_out) -> None:
         ts = (X_in, W_q, W_k, W_v, W_o, W_gate, W_up, W_down, X_out)
         if any(t.is_cuda for t in ts):
@@ -147,9 +180,10 @@ class TransformerLayerCoordinator:
 
 
 class PeerExchange:
-    """Buffers of the tensor-parallel reduction over peer memory (one instance per rank and layer shape): this rank's
-    receive buffer, two result buffers and flag words, allocated so that the other processes of the node can map them,
-    plus the mappings of every other rank's buffers.  Handles travel through torch.distributed (any backend)."""
+    """Buffers of the tensor-parallel reduction over peer memory (one instance per rank and layer shape, shared by
+    every layer of that shape: the epoch counter lives with the buffers): this rank's receive buffer, two result
+    buffers and flag words, allocated so that the other processes of the node can map them, plus the mappings of every
+    other rank's buffers.  Handles travel through torch.distributed (any backend)."""
 
     KINDS = ("recv", "out0", "out1", "flags")
 
@@ -161,6 +195,7 @@ class PeerExchange:
         self.handles: dict = {}
         self.ptrs: dict = {k: [0] * world for k in self.KINDS}
         self._opened: list = []
+        self.handle = None
         for kind in self.KINDS:
             p = ctypes.c_void_p()
             h = ctypes.create_string_buffer(64)
@@ -184,6 +219,11 @@ class PeerExchange:
                                        (self.bridge.lib.b200_bridge_last_error_string() or b"").decode())
                 self.ptrs[kind][r] = p.value
                 self._opened.append(p.value)
+        arr = lambda xs: (ctypes.c_void_p * self.world)(*xs)
+        self.handle = self.bridge.lib.b200_peer_exchange_create(self.rank, self.world, arr(self.ptrs["recv"]), arr(self.ptrs["out0"]),
+                                                                arr(self.ptrs["out1"]), arr(self.ptrs["flags"]))
+        if not self.handle:
+            raise RuntimeError("b200_peer_exchange_create failed")
 
     @classmethod
     def setup(cls, layer: "TransformerLayerCoordinator", group=None) -> Optional["PeerExchange"]:
@@ -202,7 +242,7 @@ class PeerExchange:
         if err is None and all(h is not None for h in gathered):
             try:
                 px.connect(gathered)
-                layer.set_peer_exchange(rank, world, px.ptrs["recv"], px.ptrs["out0"], px.ptrs["out1"], px.ptrs["flags"])
+                layer.attach_peer_exchange(px)
             except Exception as e:                  # noqa: BLE001
                 err = repr(e)
         else:
@@ -216,6 +256,9 @@ class PeerExchange:
         return px
 
     def close(self) -> None:
+        if self.handle:
+            self.bridge.lib.b200_peer_exchange_destroy(self.handle)
+            self.handle = None
         for p in self._opened:
             self.bridge.lib.b200_peer_close(p)
         self._opened = []

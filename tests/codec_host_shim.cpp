@@ -8,10 +8,11 @@
 template <int FMT>
 static void run(const uint8_t* W, uint16_t* out, uint32_t N, uint32_t K) {
     constexpr int RB = cdc::Codec<FMT>::ROW_BYTES;
-    const size_t row_bytes = (size_t)(K / 256) * RB;
+    constexpr int CH = cdc::Codec<FMT>::CHUNK;                  // K elements per packed stage
+    const size_t row_bytes = (size_t)(K / CH) * RB;
     const uint8_t* plane2 = W + (size_t)N * row_bytes;          // metadata planes of the planar layouts
     for (uint32_t n = 0; n < N; n++)
-        for (uint32_t kc = 0; kc < K / 256; kc++) {
+        for (uint32_t kc = 0; kc < K / CH; kc++) {
             uint32_t r[RB / 4];
             std::memcpy(r, W + n * row_bytes + (size_t)kc * RB, RB);
             uint32_t meta[4] = {0, 0, 0, 0};
@@ -19,10 +20,10 @@ static void run(const uint8_t* W, uint16_t* out, uint32_t N, uint32_t K) {
                 std::memcpy(meta, plane2 + ((size_t)n * (K / 64) + kc * 4) * 2, 8);
                 std::memcpy(meta + 2, plane2 + (size_t)N * (K / 64) * 2 + ((size_t)n * (K / 64) + kc * 4) * 2, 8);
             }
-            for (int s = 0; s < 4; s++) {
+            for (int s = 0; s < CH / 64; s++) {
                 uint32_t o[32];
                 cdc::Codec<FMT>::dequant64(r, s, o, meta);
-                std::memcpy(out + (size_t)n * K + kc * 256 + s * 64, o, 128);
+                std::memcpy(out + (size_t)n * K + kc * CH + s * 64, o, 128);
             }
         }
 }
@@ -35,6 +36,7 @@ extern "C" int codec_host_dequant(int fmt, const uint8_t* W, uint16_t* out, uint
         case QUANT_TERNARY_1_58: run<QUANT_TERNARY_1_58>(W, out, N, K); return 0;
         case QUANT_VAR_RATE_AFFINE: run<QUANT_VAR_RATE_AFFINE>(W, out, N, K); return 0;
         case QUANT_EXL3: run<QUANT_EXL3>(W, out, N, K); return 0;
+        case QUANT_PRISM_Q2_0: run<QUANT_PRISM_Q2_0>(W, out, N, K); return 0;
         case QUANT_MLX_4BIT_G64: run<QUANT_MLX_4BIT_G64>(W, out, N, K); return 0;
         case QUANT_TERNARY_ROW: run<QUANT_TERNARY_ROW>(W, out, N, K); return 0;   // integers code-1: the row scale is applied later
         default: return -3;

@@ -268,7 +268,33 @@ def test_residual_epilogue(bridge):
 
 
 # ---- benchmark shapes (K = N = 4096; the value distributions the benchmark contract names) ----
-ALL_CODECS = [o.Q4_0, o.MLX_4BIT, o.Q4_K, o.TERNARY_1_58, o.VAR_RATE_AFFINE, o.EXL3, o.MLX_4BIT_G64, o.TERNARY_ROW]
+ALL_CODECS = [o.Q4_0, o.MLX_4BIT, o.Q4_K, o.TERNARY_1_58, o.VAR_RATE_AFFINE, o.EXL3, o.PRISM_Q2_0, o.MLX_4BIT_G64, o.TERNARY_ROW]
+
+
+@pytest.mark.parametrize("shape", [(33, 1024, 256), (127, 2048, 130), (129, 1024, 65), (512, 3072, 300), (2, 4096, 200)])
+def test_prism_q2_0_tensor_core_path(bridge, shape):
+    """Prism Q2_0 (34-byte blocks of 128 two-bit codes, code 3 = +2d; the reference's quant_router_gemm_prism_q2_0_64x64,
+    quant_router_kernels.metal:726-747) on the tcgen05 path: packed stages of 1024 elements, so K % 1024 == 0 here; the
+    reference's own generator (codes 0..3 uniform) and tolerance, ragged row and token tiles, split K, and agreement with
+    the CUDA-core kernel, which serves the other K."""
+    M, K, N = shape
+    g = o.RefLcg(1337)
+    W = g.weights(o.PRISM_Q2_0, K, N)
+    X = g.activations(M, K)
+    gold = o.gemm_f64(o.PRISM_Q2_0, X, W, N)
+    Y = run_gemm(bridge, o.PRISM_Q2_0, X, W, N, ex=True)
+    assert np.abs(Y.astype(np.float64) - gold).max() <= TOL
+    check(Y, gold, f"prism q2_0 {shape}", dev_gold=device_weight_gold(o.PRISM_Q2_0, X, W, N))
+    bridge.lib.b200_bridge_force_generic(1)
+    try:
+        Yg = run_gemm(bridge, o.PRISM_Q2_0, X, W, N, ex=True)
+    finally:
+        bridge.lib.b200_bridge_force_generic(0)
+    assert np.abs(Yg.astype(np.float64) - gold).max() <= TOL
+    Yh = run_gemm(bridge, o.PRISM_Q2_0, X, W, N if N % 64 else N, ex=True) if N % 64 else \
+        run_gemm(bridge, o.PRISM_Q2_0, X, W, N, layout=1, H=N // 64, D=64)
+    if N % 64 == 0:          # head-major output is the standard output re-laid out, bit for bit
+        assert np.array_equal(Yh.view(np.uint16), Y.reshape(M, N // 64, 64).transpose(1, 0, 2).copy().view(np.uint16))
 
 
 @pytest.mark.parametrize("fmt", ALL_CODECS)

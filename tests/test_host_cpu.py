@@ -22,7 +22,7 @@ def declared_symbols():
     for hdr in (ROOT / "include").glob("*.h"):
         text = hdr.read_text()
         for block in re.findall(r'extern "C" \{(.*?)\n\}', text, flags=re.S):
-            names.update(re.findall(r"\b((?:m4_bridge|b200_bridge|b200_layer|b200_registry)_\w+)\s*\(", block))
+            names.update(re.findall(r"\b((?:m4_bridge|b200_bridge|b200_layer|b200_registry|b200_model|b200_peer|b200_gguf)_\w+)\s*\(", block))
     return names
 
 
@@ -114,7 +114,7 @@ def codec_lib(tmp_path_factory):
 
 
 @pytest.mark.parametrize("fmt,exact", [(o.Q4_0, True), (o.MLX_4BIT, True), (o.Q4_K, False), (o.TERNARY_1_58, True),
-                                       (o.VAR_RATE_AFFINE, False), (o.EXL3, True)])
+                                       (o.VAR_RATE_AFFINE, False), (o.EXL3, True), (o.PRISM_Q2_0, True)])
 def test_unpackers_match_oracle(codec_lib, fmt, exact):
     K, N = 1024, 48
     for seed in (1337, 7):

@@ -57,6 +57,54 @@ def test_scatter_reduce_broadcast_emulated_ranks(bridge, pkg, world, fmt):
         assert all(torch.equal(out[0], out[r]) for r in range(1, world))     # every rank holds the same bits
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_reduction_with_fused_rmsnorm_emulated_ranks(bridge, pkg, world):
+    """Row-sharded residual stream: the owner of a row adds the partial rows and the residual, keeps the fp16 sum for
+    itself and sends rmsnorm(sum) * w to every rank.  Ranks emulated phase by phase on one GPU; several token tiles per
+    rank, so the rotated owner order of the scatter epilogue (rank r sends to r+1 first, to itself last) is exercised."""
+    from m4_prefill_engine_b200.layer import _bind_layer, shard_cols
+    L = bridge.lib
+    _bind_layer(L)
+    fmt = o.Q4_0
+    M, K_total, N = 512 * world, 256 * world, 512            # two token tiles per rank, four weight tiles
+    g = o.RefLcg(40 + world)
+    W = g.weights(fmt, K_total, N)
+    X = (g.activations(M, K_total).astype(np.float32) * 0.5).astype(np.float16)
+    R = g.activations(M, N)
+    wn = (1.0 + 0.1 * np.random.default_rng(3).standard_normal(N)).astype(np.float16)
+    gold_mid = (o.gemm_f64(fmt, X, W, N) + R.astype(np.float64))
+    k_loc = K_total // world
+    Xs = [dev(np.ascontiguousarray(X[:, r * k_loc:(r + 1) * k_loc])) for r in range(world)]
+    Ws = [dev(shard_cols(W, fmt, K_total, N, r, world)) for r in range(world)]
+    Rd, wd = dev(R), dev(wn)
+    rows = M // world
+    recv = [torch.full((world, rows, N), float("nan"), dtype=torch.float32, device="cuda") for _ in range(world)]
+    out = [torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda") for _ in range(world)]
+    keep = [torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(world)]
+    torch.cuda.synchronize()
+    recv_p, out_p, flag_p = _arr([t.data_ptr() for t in recv]), _arr([t.data_ptr() for t in out]), _arr([t.data_ptr() for t in flags])
+    for epoch in (1, 2):
+        for r in range(world):
+            assert L.b200_peer_gemm_scatter(Xs[r].data_ptr(), Ws[r].data_ptr(), fmt, M, k_loc, N, r, world, recv_p, flag_p, epoch) == 0
+        for r in range(world):
+            assert L.b200_peer_reduce_norm_broadcast(r, world, recv_p, out_p, flag_p, epoch, Rd.data_ptr(), M, N, wd.data_ptr(),
+                                                     ctypes.c_float(1e-5), keep[r].data_ptr()) == 0
+        for r in range(world):
+            assert L.b200_peer_wait_rows(r, world, flag_p, epoch) == 0
+        bridge.synchronize()
+        assert bridge.device_error() == 0
+        mid = np.concatenate([keep[r][r * rows:(r + 1) * rows].cpu().numpy() for r in range(world)])    # each rank kept its own rows
+        check(mid, gold_mid, f"kept rows, world {world}")
+        want = o.rmsnorm(mid, wn, 1e-5)                        # the normalisation of exactly the rows that were kept
+        got = out[0].cpu().numpy()
+        assert np.abs(got.astype(np.float32) - want.astype(np.float32)).max() <= 2 * np.spacing(np.float16(np.abs(want).max())).astype(np.float32)
+        assert all(torch.equal(out[0], out[r]) for r in range(1, world))
+        for r in range(world):                                 # nothing outside a rank's own rows was written to its keep buffer
+            other = torch.cat([keep[r][:r * rows], keep[r][(r + 1) * rows:]])
+            assert bool(torch.isnan(other).all().item())
+
+
 def test_scatter_rejects_unsupported_shapes(bridge, pkg):
     from m4_prefill_engine_b200.layer import _bind_layer
     L = bridge.lib
