@@ -129,6 +129,7 @@ CDC_HD uint32_t lut8_pair(const uint32_t* L, uint32_t q0, uint32_t q1) {
 // header words [0, HDR_WORDS) plus the words [sub_lo(s), sub_hi(s)).  The unpack thread loads only those.
 struct CodecDefaults {
     static constexpr int CHUNK = 256;     // K elements per packed stage (ROW_BYTES bytes of a row)
+    static constexpr int TMA_ELEM_BYTES = 1;   // element size of the TMA map over the packed bytes (a box side holds at most 256 elements)
     static constexpr int HDR_WORDS = 0;
     static constexpr int META_WORDS = 0;
     static constexpr bool ROW_SCALE = false;
@@ -407,6 +408,7 @@ template <> struct Codec<QUANT_TERNARY_ROW> : CodecDefaults {
 template <> struct Codec<QUANT_PRISM_Q2_0> : CodecDefaults {
     static constexpr int CHUNK = 1024;
     static constexpr int ROW_BYTES = 272;
+    static constexpr int TMA_ELEM_BYTES = 2;   // 272 bytes per box row exceed 256 one-byte elements: the map counts 16-bit words
     static constexpr int GROUPS = 3;
     CDC_HD static constexpr int d_byte(int s) { return 34 * (s / 2); }
     CDC_HD static constexpr int code_byte(int s) { return 34 * (s / 2) + 2 + 16 * (s % 2); }

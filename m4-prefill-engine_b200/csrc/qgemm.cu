@@ -345,7 +345,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 if (lane == 0) {
                     QTR(0, wtr, 0);
                     ptx::mbar_arrive_expect_tx(&raw_full[rs], RAW_TILE_BYTES);
-                    const int x = (int)((t.ks * p.kchunks + kc) * ROW_BYTES);
+                    const int x = (int)((t.ks * p.kchunks + kc) * (ROW_BYTES / Cd::TMA_ELEM_BYTES));    // in elements of the map
                     if (p.swiglu) {     // the maps of a SwiGLU launch have 64-row boxes: gate rows, then the same rows of up
                         const int y = (int)(t.wt * GATE_ROWS);
                         ptx::tma_load_2d(sRaw + rs * RAW_TILE_BYTES, &tmW0, &raw_full[rs], x, y);
@@ -990,7 +990,9 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
         return cudaErrorInvalidValue;
     const CUtensorMapSwizzle wsw = cdc::Codec<FMT>::RAW_SWIZZLE_128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;
     const uint32_t box_rows = a.W1 ? GATE_ROWS : W_TILE;
-    if (!make_map_2d(&tmW0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.W0, w_row_bytes, a.N, w_row_bytes, rb, box_rows, wsw))
+    constexpr int EB = cdc::Codec<FMT>::TMA_ELEM_BYTES;
+    const CUtensorMapDataType wdt = EB == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    if (!make_map_2d(&tmW0, wdt, EB, a.W0, w_row_bytes / EB, a.N, w_row_bytes, rb / EB, box_rows, wsw))
         return cudaErrorInvalidValue;
     // second / third map: the up matrix of a SwiGLU launch, or the extra matrices of a grouped launch
     const bool grouped = a.n_extra > 0;
@@ -1001,9 +1003,9 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     const uint32_t n1 = grouped ? a.N_extra[0] : a.N;
     const void* w2 = a.n_extra > 1 ? a.W_extra[1] : a.W0;
     const uint32_t n2 = a.n_extra > 1 ? a.N_extra[1] : a.N;
-    if (!make_map_2d(&tmW1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w1, w_row_bytes, n1, w_row_bytes, rb, box_rows, wsw))
+    if (!make_map_2d(&tmW1, wdt, EB, w1, w_row_bytes / EB, n1, w_row_bytes, rb / EB, box_rows, wsw))
         return cudaErrorInvalidValue;
-    if (!make_map_2d(&tmW2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2, w_row_bytes, n2, w_row_bytes, rb, box_rows, wsw))
+    if (!make_map_2d(&tmW2, wdt, EB, w2, w_row_bytes / EB, n2, w_row_bytes, rb / EB, box_rows, wsw))
         return cudaErrorInvalidValue;
 
     Params p;

@@ -47,6 +47,35 @@ def test_static_scratch_matches_regular_entry_point(bridge):
     assert np.array_equal(first.view(np.uint16), b.view(np.uint16))      # same inputs again: same bits
 
 
+def test_static_scratch_calls_leave_device_memory_alone(bridge):
+    """What the entry point is for: from the second call on (the first one may still make the driver load code), a
+    call changes the amount of free device memory by nothing, whatever the split shape -- the regular entry point, by
+    contrast, grows its scratch on demand.  cudaMemGetInfo is read straight from the runtime, with no torch
+    allocation between the readings."""
+    import ctypes
+    L = bridge.lib
+    rt = ctypes.CDLL("libcudart.so.12")
+    K = N = 4096
+    sets = []
+    for M, fmt, seed in ((33, o.Q4_0, 1), (129, o.MLX_4BIT, 2), (65, o.Q4_K, 3)):
+        X, W = o.baseline_inputs(fmt, M, K, N, seed)
+        sets.append((dev(X), dev(W), torch.zeros(M, N, dtype=torch.float16, device="cuda"), fmt, M))
+    torch.cuda.synchronize()
+
+    def free_bytes():
+        f, t = ctypes.c_size_t(), ctypes.c_size_t()
+        assert rt.cudaMemGetInfo(ctypes.byref(f), ctypes.byref(t)) == 0
+        return f.value
+    for Xd, Wd, Yd, fmt, M in sets:                        # first round: warm
+        assert _call(bridge, L.b200_bridge_gemm_scratch_static, Xd, Wd, Yd, fmt, M, K, N) == 0
+    before = free_bytes()
+    for _ in range(3):
+        for Xd, Wd, Yd, fmt, M in sets:
+            assert _call(bridge, L.b200_bridge_gemm_scratch_static, Xd, Wd, Yd, fmt, M, K, N) == 0
+            assert free_bytes() == before
+    assert bridge.device_error() == 0
+
+
 def test_static_scratch_limits(bridge):
     L = bridge.lib
     K = N = 4096
