@@ -543,10 +543,18 @@ def time_layer(br, pkg, world: int, rank: int, steps: int, warmup: int, collecti
             gold = o.layer(0, X[:R].cpu().numpy(), full["q"], full["k"], full["v"], full["o"], full["gate"], full["up"], full["down"],
                            c["H"], c["Hkv"], c["D"], c["F"], c["D"] ** -0.5, rms_eps=1e-5, norm1=n1.cpu().numpy(), norm2=n2.cpu().numpy(),
                            rope_theta=500000.0, kv_q8=True)
-            d = np.abs(Y[:R].cpu().numpy().astype(np.float64) - gold.astype(np.float64))
-            parity = {"rows": "first 48 of 2048 against the CPU verifier's layer", "max_abs": float(d.max()),
-                      "over_1_128": int((d > TOL).sum()), "outputs": int(d.size), "ok": bool(d.max() <= 2 * TOL),
-                      "ranks_bit_identical": same}
+            g64 = gold.astype(np.float64)
+            d = np.abs(Y[:R].cpu().numpy().astype(np.float64) - g64)
+            # A layer output passes through six fp16 roundings of intermediates, each 2^-11 relative, so the bound scales
+            # with the magnitude of the token row: |d| <= max(2/128, 2^-7 * rms(row)).  (Token 0 attends to itself only,
+            # its attention output is one un-averaged value row and its outputs are an order of magnitude larger.)
+            row_rms = np.sqrt(np.mean(g64 ** 2, axis=1, keepdims=True))
+            tol = np.maximum(2 * TOL, 2.0 ** -7 * row_rms)
+            worst = int(np.argmax(d.max(axis=1)))
+            parity = {"rows": "first 48 of 2048 against the CPU verifier's layer", "max_abs": float(d.max()), "max_abs_row": worst,
+                      "rms_of_that_row": float(row_rms[worst, 0]), "max_abs_rows_1_to_47": float(d[1:].max()),
+                      "over_1_128": int((d > TOL).sum()), "outputs": int(d.size), "criterion": "max(2/128, 2^-7 * rms(row))",
+                      "ok": bool(np.all(d <= tol)), "ranks_bit_identical": same}
         full.clear()
         if world > 1:
             dist.barrier()

@@ -144,9 +144,9 @@ int b200_bridge_debug_set_tile_counter(uint32_t index, uint32_t value);
 void b200_bridge_force_generic(int on);
 /* Up to three projections of the same activations in one launch (the Q, K and V projections of a layer): Y[i] =
  * X . W[i]^T with W[i] packed [N[i]][K/blk] in `format`, outputs in `layout` (LAYOUT_DIRECT_HEAD: [N[i]/D][M][D]).
- * Device pointers only.  Needs enough tiles to fill the GPU without splitting K (ceil(M/256) * sum(ceil(N[i]/128)) above
- * the SM count) and K % 256 == 0; returns -4 where a grouped launch is not available (the caller then dispatches
- * the projections one by one).  Results are bit-identical to separate dispatches.  No counterpart in the reference. */
+ * Device pointers only, K % 256 == 0, formats 0..5; returns -4 where a grouped launch is not available (the caller then
+ * dispatches the projections one by one).  Few-token launches split K as a single projection would.  Results are
+ * bit-identical to separate dispatches that run the same split.  No counterpart in the reference. */
 int b200_bridge_dispatch_gemm_grouped(const void* X, const void* const* W, void* const* Y, const uint32_t* N, uint32_t count,
                                       int format, uint32_t M, uint32_t K, int layout, uint32_t D);
 /* Testing hook: != 0 routes head-dim-128 Q8_0 attention to the warp-level MMA kernels instead of the

@@ -132,9 +132,11 @@ int b200_peer_free(void* ptr);
 int b200_layer_set_peer_exchange(void* layer, uint32_t rank, uint32_t world, void* const* recv, void* const* out0,
                                  void* const* out1, void* const* flags);
 /* One exchange for several layers (the layers of a model run one after the other on the same buffers): create it from
- * the same pointer arrays, attach it to each layer, destroy it after the layers.  NULL / -4 on bad arguments. */
+ * the same pointer arrays, attach it to each layer, destroy it after the layers.  NULL / -4 on bad arguments.
+ * partial_fp16 != 0: the partial sums of a row-split projection cross NVLink as fp16 instead of fp32 (half the bytes; each
+ * rank's partial is rounded to fp16 once before the owner adds them in fp32); every rank of a group must pass the same value. */
 void* b200_peer_exchange_create(uint32_t rank, uint32_t world, void* const* recv, void* const* out0, void* const* out1,
-                                void* const* flags);
+                                void* const* flags, int partial_fp16);
 void b200_peer_exchange_destroy(void* exchange);
 int b200_layer_attach_peer_exchange(void* layer, void* exchange);
 /* Per-launch timing of the next forward calls (CUDA events between launches); b200_layer_profile waits for the stream
@@ -157,4 +159,7 @@ int b200_peer_reduce_norm_broadcast(uint32_t rank, uint32_t world, void* const* 
  * out sets device error 301 (arrival flags) or 302 (result rows) and the kernel returns; later waits return at once
  * until the error word is cleared. */
 void b200_peer_set_wait_limit_ms(unsigned ms);
+/* Partial-sum type of the three primitive entry points above: 0 fp32 (default), != 0 fp16 (the receive buffers then hold
+ * fp16 [world][M / world][N]). */
+void b200_peer_set_partial_fp16(int on);
 }

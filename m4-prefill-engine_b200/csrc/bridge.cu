@@ -311,6 +311,7 @@ int b200_bridge_dispatch_gemm_grouped(const void* X, const void* const* W, void*
     a.n_extra = count - 1;
     for (uint32_t i = 1; i < count; i++) { a.W_extra[i - 1] = W[i]; a.Y_extra[i - 1] = Y[i]; a.N_extra[i - 1] = N[i]; }
     a.force_generic = g.force_generic;
+    if (!ensure_workspace(qg::workspace_floats(a))) return -5;      // few-token grouped launches split K
     qg::Workspace ws;
     ws.partial = (float*)g.ws_partial.p; ws.partial_floats = g.ws_partial.cap / sizeof(float);
     ws.counters = g.counters; ws.err = g.err_word;

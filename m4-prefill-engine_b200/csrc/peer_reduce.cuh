@@ -9,11 +9,13 @@ namespace peer {
 
 struct Exchange {
     uint32_t world = 0, rank = 0;
-    float* recv[8] = {};          // recv[o]: rank o's receive buffer, fp32 [world][M / world][K]  (peer-mapped)
+    float* recv[8] = {};          // recv[o]: rank o's receive buffer, fp32 (or fp16) [world][M / world][K]  (peer-mapped)
     void* out[2][8] = {};         // out[b][o]: rank o's copy of result buffer b, fp16 [M][K]      (peer-mapped)
     uint32_t* flags[8] = {};      // flags[o]: rank o's flag words: [0..7] partial sums arrived, [8..15] result rows written
     uint32_t* done_counter = nullptr;   // 16 device-local words, zero between launches (1: reduction kernel, 4..11: projection epilogue)
     uint32_t epoch = 0;           // raised once per reduced projection; flags only ever grow
+    bool partial_fp16 = false;    // partial sums travel (and sit in recv[]) as fp16 instead of fp32: half the NVLink bytes, one
+                                  // extra fp16 rounding per rank and output before the fp32 sum
 };
 
 // Rows [rank * rows, (rank + 1) * rows) of  residual + sum over sources  -> fp16, written to out[o] of every rank o;

@@ -75,7 +75,9 @@ constexpr int A_TILE_BYTES = W_TILE * 128;
 constexpr int TMEM_COLS = 512;
 constexpr int ACC_STRIDE = 256; // tensor-memory columns per accumulator buffer
 
-constexpr int XCHG_BYTES = 2 * 128 * 32;   // SwiGLU epilogue: two buffers of 8 floats per epilogue thread
+constexpr int XCHG_BYTES = 2 * 128 * 32;   // epilogue exchange area: two buffers of 16 tokens x 128 features of fp16 (row-wise
+                                           // epilogue), or of 8 floats per epilogue thread (SwiGLU)
+constexpr int XCHG_BYTES_F32 = 2 * XCHG_BYTES;   // row-wise epilogue of fp32 partial sums: 16 tokens x 128 features x 4 bytes, twice
 constexpr int GATE_ROWS = W_TILE / 2;      // SwiGLU tile: 64 gate rows on TMEM lanes 0..63, their 64 up rows on lanes 64..127
 
 template <int FMT> struct Cfg {
@@ -123,6 +125,7 @@ struct Params {
     uint32_t tt_shift;           // rotation of the token-tile order (fused reduce-scatter only, else 0)
     uint32_t tiles_per_owner;    // output tiles whose token rows belong to one rank (fused reduce-scatter only)
     uint32_t swiglu;             // 1: tiles are 64 gate rows (matrix 0) + their 64 up rows (matrix 1); output = silu(g) * u
+    uint32_t row_epi;            // 1: outputs leave through the row-wise epilogue (16-byte stores of whole token rows)
     const uint8_t* meta0;
     const uint8_t* meta1;
     const __half* row_scale0;
@@ -130,19 +133,23 @@ struct Params {
 };
 
 // Packed-weight stages that fit beside the operand ring for a given activation-tile height.
-template <int FMT> inline long raw_stages_fit(uint32_t T, bool swiglu, uint32_t b_stages) {
-    const long avail = (long)SMEM_BYTES - 1024 /*alignment slack*/ - 512 /*barriers*/ - (swiglu ? XCHG_BYTES : 0) -
+template <int FMT> inline long raw_stages_fit(uint32_t T, long xchg_bytes, uint32_t b_stages) {
+    const long avail = (long)SMEM_BYTES - 1024 /*alignment slack*/ - 512 /*barriers*/ - xchg_bytes -
                        (long)STAGES * A_TILE_BYTES - (long)b_stages * T * 128;
     return avail / ((long)cdc::Codec<FMT>::ROW_BYTES * W_TILE);
 }
 // Activation ring depth: four stages when two packed-weight stages still fit beside them, else three.
-template <int FMT> inline uint32_t b_stages_for(uint32_t T, bool swiglu) {
-    return raw_stages_fit<FMT>(T, swiglu, MAX_B_STAGES) >= 2 ? MAX_B_STAGES : STAGES;
+template <int FMT> inline uint32_t b_stages_for(uint32_t T, long xchg_bytes) {
+    return raw_stages_fit<FMT>(T, xchg_bytes, MAX_B_STAGES) >= 2 ? MAX_B_STAGES : STAGES;
 }
-template <int FMT> inline uint32_t raw_stages_for(uint32_t T, bool swiglu) {
-    const long n = raw_stages_fit<FMT>(T, swiglu, b_stages_for<FMT>(T, swiglu));
-    return (uint32_t)(n < 2 ? 2 : (n > MAX_RAW_STAGES ? MAX_RAW_STAGES : n));
+template <int FMT> inline uint32_t raw_stages_for(uint32_t T, long xchg_bytes) {
+    const long n = raw_stages_fit<FMT>(T, xchg_bytes, b_stages_for<FMT>(T, xchg_bytes));
+    // (every codec fits at least one stage beside three activation stages of 256 tokens and the largest exchange area;
+    // with a single stage the copy of the next chunk cannot overlap the unpacking, which only the 272-byte rows reach)
+    return (uint32_t)(n < 1 ? 1 : (n > MAX_RAW_STAGES ? MAX_RAW_STAGES : n));
 }
+static_assert(SMEM_BYTES - 1024 - 512 - XCHG_BYTES_F32 - STAGES * A_TILE_BYTES - STAGES * 256 * 128 >= 272 * W_TILE,
+              "one packed stage of the widest codec must fit in the tightest configuration");
 
 // Loads the words [W, HI) of a packed row from shared memory into r[] with the widest aligned loads.  SW: the row
 // was staged with the 128-byte TMA swizzle (16-byte chunk index ^ row % 8); such rows are read in whole chunks.
@@ -259,6 +266,81 @@ __device__ __forceinline__ void splitk_fixup(const Params& p, const Tile& t, uin
     }
 }
 
+// Row-wise epilogue of one output tile.  The accumulator comes out of tensor memory with one thread per feature (16
+// token columns at a time); written out like that, a warp's store covers 32 features of one token (64 bytes of fp16) and
+// a residual would be read with strided 2-byte loads.  Instead each batch of 16 tokens x 128 features is turned over
+// through shared memory: the feature-owning threads deposit their values, and after one barrier among the 128 epilogue
+// threads each thread moves 16-byte chunks of whole token rows -- a warp's store covers two full 256-byte rows of fp16 (or
+// one 512-byte row of fp32 partial sums), which is what both HBM and NVLink want, and a residual is read the same way.
+// Two buffers alternate, so one barrier per batch suffices (a buffer is rewritten only after the barrier of the batch in
+// between, which every thread reaches after its reads of that buffer).
+//   KIND 0: fp16 to Y            KIND 1: fp16(acc + residual) to Y
+//   KIND 2: fp32 partial sums    KIND 3: fp16 partial sums          (both to `partial`, standard layout of width p.N)
+template <int KIND>
+__device__ __forceinline__ void row_epilogue(const Params& p, uint8_t* stage, uint32_t& batch_ctr, uint32_t taddr, uint32_t et,
+                                             uint32_t tok0, uint32_t valid, float rsc, bool row_scale, uint32_t n_tile0, uint32_t Ng,
+                                             __half* Yg, void* partial) {
+    constexpr bool F32 = KIND == 1 || KIND == 2;    // staged as fp32 (the residual is added before the one fp16 rounding)
+    constexpr int CH = F32 ? 4 : 8;                 // elements per 16-byte chunk of the staging buffer
+    constexpr int CPR = W_TILE / CH;                // chunks per token row of the tile
+    constexpr int ROWS = 128 / CPR;                 // token rows the 128 threads cover per pass
+    constexpr int PASSES = 16 / ROWS;
+    constexpr int BUF = 16 * W_TILE * (F32 ? 4 : 2);
+    const uint32_t chunk = et % CPR, jrow = et / CPR;
+    const uint32_t n = n_tile0 + chunk * CH;
+    const bool n_ok = n < Ng;
+    size_t col_base, tok_stride;
+    if (KIND >= 2) { col_base = n; tok_stride = p.N; }
+    else if (p.layout == 1) { col_base = (size_t)(n / p.D) * p.M * p.D + (n % p.D); tok_stride = p.D; }
+    else { col_base = n; tok_stride = Ng; }
+    col_base += (size_t)tok0 * tok_stride;
+    for (uint32_t c0 = 0; c0 < p.T; c0 += 16, batch_ctr++) {
+        uint8_t* buf = stage + (batch_ctr & 1u) * BUF;
+        uint2 res[PASSES];
+        if (KIND == 1) {             // requested before the accumulator is read: the latency hides behind the turn-over
+#pragma unroll
+            for (int h = 0; h < PASSES; h++) {
+                const uint32_t tok = c0 + jrow + h * ROWS;
+                res[h] = (n_ok && tok < valid) ? __ldg(reinterpret_cast<const uint2*>(p.residual + col_base + (size_t)tok * tok_stride))
+                                               : make_uint2(0u, 0u);
+            }
+        }
+        uint32_t v[16];
+        ptx::tmem_ld_x16(taddr + c0, v);
+        ptx::tmem_ld_wait();
+        if (F32) {
+            float* b = reinterpret_cast<float*>(buf) + et;
+#pragma unroll
+            for (int j = 0; j < 16; j++) b[j * W_TILE] = row_scale ? __uint_as_float(v[j]) * rsc : __uint_as_float(v[j]);
+        } else {
+            __half* b = reinterpret_cast<__half*>(buf) + et;
+#pragma unroll
+            for (int j = 0; j < 16; j++) b[j * W_TILE] = __float2half_rn(row_scale ? __uint_as_float(v[j]) * rsc : __uint_as_float(v[j]));
+        }
+        ptx::bar_sync(2, 128);
+#pragma unroll
+        for (int h = 0; h < PASSES; h++) {
+            const uint32_t j = jrow + h * ROWS, tok = c0 + j;
+            if (!n_ok || tok >= valid) continue;
+            const uint4 w = reinterpret_cast<const uint4*>(buf)[j * CPR + chunk];
+            if (KIND == 2) {
+                *reinterpret_cast<uint4*>(reinterpret_cast<float*>(partial) + col_base + (size_t)tok * tok_stride) = w;
+            } else if (KIND == 3) {
+                *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(partial) + col_base + (size_t)tok * tok_stride) = w;
+            } else if (KIND == 1) {
+                const __half2 r01 = *reinterpret_cast<const __half2*>(&res[h].x), r23 = *reinterpret_cast<const __half2*>(&res[h].y);
+                const __half2 h01 = __floats2half2_rn(__uint_as_float(w.x) + __low2float(r01), __uint_as_float(w.y) + __high2float(r01));
+                const __half2 h23 = __floats2half2_rn(__uint_as_float(w.z) + __low2float(r23), __uint_as_float(w.w) + __high2float(r23));
+                uint2 o;
+                o.x = *reinterpret_cast<const uint32_t*>(&h01); o.y = *reinterpret_cast<const uint32_t*>(&h23);
+                *reinterpret_cast<uint2*>(Yg + col_base + (size_t)tok * tok_stride) = o;
+            } else {
+                *reinterpret_cast<uint4*>(Yg + col_base + (size_t)tok * tok_stride) = w;
+            }
+        }
+    }
+}
+
 // RESID: the launch adds a residual in the epilogue (its prefetch ring costs registers the plain launch should not pay for)
 template <int FMT, bool RESID>
 __global__ void __launch_bounds__(Cfg<FMT>::THREADS, 1)
@@ -292,7 +374,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tm_empty + 2);
     volatile uint32_t* abort_flag = tmem_holder + 1;
     volatile uint32_t* last_flag = tmem_holder + 2;
-    float4* xchg = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(bars) + 512);   // SwiGLU launches only
+    float4* xchg = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(bars) + 512);   // epilogue exchange area (16-byte aligned)
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t total_tiles = p.n_w_tiles * p.n_tok_tiles * p.k_splits;
@@ -585,7 +667,11 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             float* partial_dst = p.partial_out;
             if (p.scatter.world) {
                 const uint32_t owner = tok0 / p.scatter.rows;
-                partial_dst = p.scatter.recv[owner] + ((ptrdiff_t)p.scatter.rank - (ptrdiff_t)owner) * (ptrdiff_t)p.scatter.rows * (ptrdiff_t)p.N;
+                // slot `rank` of the owner's buffer, offset so that (tok * N + n) addresses this tile's rows; in elements of the
+                // partial type (fp16 partials: the same arithmetic in halves, hence the division by two of the float pointer offset)
+                const ptrdiff_t off = ((ptrdiff_t)p.scatter.rank - (ptrdiff_t)owner) * (ptrdiff_t)p.scatter.rows * (ptrdiff_t)p.N;
+                partial_dst = p.scatter.fp16 ? reinterpret_cast<float*>(reinterpret_cast<__half*>(p.scatter.recv[owner]) + off)
+                                             : p.scatter.recv[owner] + off;
                 if (owner != sc_owner) { scatter_flush(); sc_owner = owner; }
                 sc_count++;
             }
@@ -593,7 +679,18 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             // integer-valued codecs: the row's scale multiplies the fp32 accumulator (before SiLU, before split-K sums)
             float rsc0 = 1.0f;
             if (Cd::ROW_SCALE && !p.swiglu) rsc0 = n_ok ? __half2float(p.row_scale0[n]) : 0.0f;
-            if (p.swiglu) {
+            if (p.row_epi) {
+                // row-wise epilogue (everything but SwiGLU tiles, split-K partial tiles and outputs that cannot take 16-byte stores)
+                uint8_t* stage = reinterpret_cast<uint8_t*>(xchg);
+                if (mode == 1) {
+                    if (p.scatter.world && p.scatter.fp16) row_epilogue<3>(p, stage, xb_i, taddr, et, tok0, valid, rsc0, Cd::ROW_SCALE, wt_l * W_TILE, Ng, Yg, partial_dst);
+                    else row_epilogue<2>(p, stage, xb_i, taddr, et, tok0, valid, rsc0, Cd::ROW_SCALE, wt_l * W_TILE, Ng, Yg, partial_dst);
+                } else if (mode == 2) {
+                    row_epilogue<1>(p, stage, xb_i, taddr, et, tok0, valid, rsc0, Cd::ROW_SCALE, wt_l * W_TILE, Ng, Yg, nullptr);
+                } else {
+                    row_epilogue<0>(p, stage, xb_i, taddr, et, tok0, valid, rsc0, Cd::ROW_SCALE, wt_l * W_TILE, Ng, Yg, nullptr);
+                }
+            } else if (p.swiglu) {
                 // SwiGLU tile: lanes 0..63 (warps 0,1) hold the gate projection of 64 features, lanes 64..127
                 // (warps 2,3) the up projection of the same features.  Thread et and thread et ^ 64 own the two
                 // halves of one feature: per batch of 16 token columns they swap 8 values through shared memory,
@@ -1012,8 +1109,27 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     p.M = a.M; p.N = a.N; p.K = a.K;
     p.T = pl.T; p.n_tok_tiles = pl.n_tok_tiles; p.n_w_tiles = pl.n_w_tiles; p.k_splits = pl.k_splits; p.kchunks = pl.kchunks;
     p.swiglu = a.W1 ? 1u : 0u;
-    p.raw_stages = raw_stages_for<FMT>(pl.T, a.W1 != nullptr); p.b_stage_bytes = pl.T * 128u;
-    p.b_stages = b_stages_for<FMT>(pl.T, a.W1 != nullptr);
+    // Row-wise epilogue: wherever every output row can take 16-byte stores (and, with a residual, 8-byte loads).  SwiGLU
+    // tiles and split-K partial tiles have their own paths.
+    const bool partial_f32 = (a.partial_out != nullptr) || (a.scatter.world && !a.scatter.fp16);
+    bool row_ok = !a.W1 && pl.k_splits == 1;
+    auto aligned16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    if (row_ok) {
+        if (a.partial_out) row_ok = aligned16(a.partial_out) && a.N % 4u == 0u;
+        else if (a.scatter.world) {
+            row_ok = a.N % 8u == 0u;
+            for (uint32_t o = 0; o < a.scatter.world; o++) row_ok = row_ok && aligned16(a.scatter.recv[o]);
+        } else {
+            row_ok = aligned16(a.Y) && a.N % 8u == 0u && (a.layout != 1 || (a.D % 8u == 0u));
+            if (a.residual) row_ok = row_ok && (reinterpret_cast<uintptr_t>(a.residual) & 7u) == 0;
+            for (uint32_t e = 0; e < a.n_extra && e < 2u; e++) row_ok = row_ok && aligned16(a.Y_extra[e]) && a.N_extra[e] % 8u == 0u;
+        }
+    }
+    if (a.scatter.world && a.scatter.fp16 && !row_ok) return cudaErrorInvalidValue;     // fp16 partial sums exist on the row-wise epilogue only
+    p.row_epi = row_ok ? 1u : 0u;
+    const long xchg_bytes = a.W1 ? XCHG_BYTES : (row_ok ? ((partial_f32 || a.residual) ? XCHG_BYTES_F32 : XCHG_BYTES) : 0);
+    p.raw_stages = raw_stages_for<FMT>(pl.T, xchg_bytes); p.b_stage_bytes = pl.T * 128u;
+    p.b_stages = b_stages_for<FMT>(pl.T, xchg_bytes);
     p.Y = (__half*)a.Y; p.residual = (const __half*)a.residual; p.partial_out = a.partial_out;
     p.scatter = a.scatter;
     p.groups = 1u + a.n_extra;

@@ -35,6 +35,7 @@ struct GemmArgs {
         float* recv[8];                  // recv[o]: rank o's buffer, fp32 [world][rows][N]
         uint32_t* flags[8];              // flags[o]: rank o's arrival flags, one word per source rank
         uint32_t epoch;
+        uint32_t fp16;                   // != 0: partial sums travel as fp16 (recv[o] then holds fp16 [world][rows][N]), else fp32
         uint32_t* done_counter;          // 16 device-local words, zero between launches (words 4..11: one tile counter per owner)
     } scatter;
 };

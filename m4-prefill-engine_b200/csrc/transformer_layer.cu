@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -96,6 +97,15 @@ bool TransformerLayerCoordinator::initialize_pipelines(const void*) {
             a.format = c.weight_format; a.M = c.M; a.N = ns[i]; a.K = ks[i];
             a.X = (const void*)16; a.W0 = (const void*)16; a.Y = (void*)16;   // alignment probes only
             size_t w = qg::workspace_floats(a);
+            if (w > need) need = w;
+        }
+        {   // the grouped Q + K + V launch
+            qg::GemmArgs a; memset(&a, 0, sizeof(a));
+            a.format = c.weight_format; a.M = c.M; a.N = hq * c.D; a.K = c.K; a.layout = LAYOUT_DIRECT_HEAD; a.H = hq; a.D = c.D;
+            a.X = (const void*)16; a.W0 = (const void*)16; a.Y = (void*)16;
+            a.n_extra = 2; a.W_extra[0] = a.W_extra[1] = (const void*)16; a.Y_extra[0] = a.Y_extra[1] = (void*)16;
+            a.N_extra[0] = a.N_extra[1] = hkv * c.D;
+            const size_t w = qg::workspace_floats(a);
             if (w > need) need = w;
         }
         { qg::GemmArgs a; memset(&a, 0, sizeof(a)); a.format = c.weight_format; a.M = c.M; a.N = c.K; a.K = f;
@@ -253,7 +263,7 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
         qg::GemmArgs a; memset(&a, 0, sizeof(a));
         a.format = im.gemm_binding.format; a.X = X; a.W0 = W; a.M = c.M; a.N = c.K; a.K = Kin; a.layout = im.gemm_binding.layout;
         a.scatter.world = x.world; a.scatter.rank = x.rank; a.scatter.rows = c.M / x.world; a.scatter.epoch = x.epoch;
-        a.scatter.done_counter = x.done_counter;
+        a.scatter.done_counter = x.done_counter; a.scatter.fp16 = x.partial_fp16 ? 1u : 0u;
         for (uint32_t o = 0; o < x.world; o++) { a.scatter.recv[o] = x.recv[o]; a.scatter.flags[o] = x.flags[o]; }
         if (qg::launch(a, ws, stream) != cudaSuccess) { status_ = -6; return; }
         launches_ += (uint32_t)qg::last_launch_count();
@@ -270,7 +280,7 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
     const bool fuse_add_norm = c.tp_size == 1 && c.rms_eps > 0.0f && c.K % 8u == 0u && (reinterpret_cast<uintptr_t>(X_in) & 15u) == 0;
     // fused exchange with a normalisation behind it: the residual stream stays sharded by rows between the two
     // reductions (x_mid holds this rank's rows only) and the rows every rank receives are already normalised
-    const bool px_norm = im.px && c.rms_eps > 0.0f && c.K % 4u == 0u;
+    const bool px_norm = im.px && c.rms_eps > 0.0f && c.K % 1024u == 0u && c.K <= 8192u;
     if (fuse_add_norm) {
         gemm(im.gemm_binding, im.attn, W_o, nullptr, im.xn, c.K, hq * c.D, 0, nullptr, nullptr);
         mark("o projection");
@@ -294,10 +304,11 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
     else if (c.rms_eps > 0.0f) { check(lops::rmsnorm(x_mid, im.norm2, im.xn, c.M, c.K, c.rms_eps, stream)); x_mlp = im.xn; mark("rmsnorm 2"); }
     gemm(im.gemm_binding, x_mlp, W_gate, W_up, im.act, f, c.K, 0, nullptr, nullptr);
     mark("gate/up SwiGLU");
-    // Same trade for the MLP block's residual: with no kernel behind it to carry the add, a 16-byte-wide add kernel
-    // (about 5 us with its launch) replaces the projection's residual epilogue (about 20 us).  im.xn is free again
-    // once the gate/up launch has been queued (stream order).
-    const bool split_add = fuse_add_norm && ((size_t)c.M * c.K) % 8u == 0u && (reinterpret_cast<uintptr_t>(X_out) & 15u) == 0;
+    // The MLP block's residual rides in the down projection's epilogue (row-wise: the residual row is read with the same
+    // 16-byte-granular accesses the output row is written with).  B200_LAYER_SPLIT_ADD=1 selects the older arrangement, a
+    // plain projection followed by a 16-byte-wide add kernel, for comparison.
+    static const bool split_add_env = [] { const char* e = getenv("B200_LAYER_SPLIT_ADD"); return e && e[0] == '1'; }();
+    const bool split_add = split_add_env && fuse_add_norm && ((size_t)c.M * c.K) % 8u == 0u && (reinterpret_cast<uintptr_t>(X_out) & 15u) == 0;
     if (split_add) {
         gemm(im.gemm_binding, im.act, W_down, nullptr, im.xn, c.K, f, 0, nullptr, nullptr);
         mark("down projection");
@@ -428,7 +439,7 @@ int b200_layer_set_peer_exchange(void* layer, uint32_t rank, uint32_t world, voi
 }
 
 void* b200_peer_exchange_create(uint32_t rank, uint32_t world, void* const* recv, void* const* out0, void* const* out1,
-                                void* const* flags) {
+                                void* const* flags, int partial_fp16) {
     std::lock_guard<std::mutex> lock(g.mu);
     if (!g.initialized || !recv || !out0 || !out1 || !flags || world < 2 || world > 8 || rank >= world) return nullptr;
     peer::Exchange* x = new peer::Exchange;
@@ -436,7 +447,7 @@ void* b200_peer_exchange_create(uint32_t rank, uint32_t world, void* const* recv
         if (!recv[o] || !out0[o] || !out1[o] || !flags[o]) { delete x; return nullptr; }
         x->recv[o] = (float*)recv[o]; x->out[0][o] = out0[o]; x->out[1][o] = out1[o]; x->flags[o] = (uint32_t*)flags[o];
     }
-    x->rank = rank; x->world = world;
+    x->rank = rank; x->world = world; x->partial_fp16 = partial_fp16 != 0;
     if (cudaMalloc((void**)&x->done_counter, 64) != cudaSuccess) { cudaGetLastError(); delete x; return nullptr; }
     cudaMemset(x->done_counter, 0, 64);
     uint32_t seen = 0;                         // buffers that were used before continue from their last epoch
@@ -517,7 +528,8 @@ int b200_peer_close(void* ptr) { return ptr && cudaIpcCloseMemHandle(ptr) == cud
 int b200_peer_free(void* ptr) { return ptr && cudaFree(ptr) == cudaSuccess ? 0 : -2; }
 
 namespace {
-uint32_t* g_peer_counter = nullptr;      // two words for the primitive entry points below
+uint32_t* g_peer_counter = nullptr;      // counter words for the primitive entry points below
+bool g_peer_partial_fp16 = false;        // partial-sum type of the primitive entry points (b200_peer_set_partial_fp16)
 bool peer_counter_ready() {
     if (g_peer_counter) return true;
     if (cudaMalloc((void**)&g_peer_counter, 64) != cudaSuccess) { cudaGetLastError(); g_peer_counter = nullptr; return false; }
@@ -536,7 +548,7 @@ int b200_peer_gemm_scatter(const void* X, const void* W, int format, uint32_t M,
     qg::GemmArgs a; memset(&a, 0, sizeof(a));
     a.format = format; a.X = X; a.W0 = W; a.M = M; a.N = N; a.K = K; a.layout = LAYOUT_STANDARD;
     a.scatter.world = world; a.scatter.rank = rank; a.scatter.rows = M / world; a.scatter.epoch = epoch;
-    a.scatter.done_counter = g_peer_counter;
+    a.scatter.done_counter = g_peer_counter; a.scatter.fp16 = g_peer_partial_fp16 ? 1u : 0u;
     for (uint32_t o = 0; o < world; o++) { a.scatter.recv[o] = (float*)recv[o]; a.scatter.flags[o] = (uint32_t*)flags[o]; }
     qg::Workspace ws;
     ws.partial = (float*)g.ws_partial.p; ws.partial_floats = g.ws_partial.cap / sizeof(float); ws.counters = g.counters; ws.err = g.err_word;
@@ -553,7 +565,7 @@ int b200_peer_reduce_broadcast(uint32_t rank, uint32_t world, void* const* recv,
     if (!recv || !out || !flags || !residual || world < 1 || world > 8 || rank >= world) return -2;
     if (!peer_counter_ready()) return -5;
     peer::Exchange x;
-    x.world = world; x.rank = rank; x.epoch = epoch; x.done_counter = g_peer_counter;
+    x.world = world; x.rank = rank; x.epoch = epoch; x.done_counter = g_peer_counter; x.partial_fp16 = g_peer_partial_fp16;
     for (uint32_t o = 0; o < world; o++) { x.recv[o] = (float*)recv[o]; x.out[0][o] = out[o]; x.flags[o] = (uint32_t*)flags[o]; }
     if (peer::reduce_broadcast(x, 0, residual, M, K, g.err_word, g.stream) != cudaSuccess) { cudaGetLastError(); return -4; }
     g.launches++;
@@ -568,7 +580,7 @@ int b200_peer_reduce_norm_broadcast(uint32_t rank, uint32_t world, void* const* 
     if (!recv || !out || !flags || !residual || !norm_w || !keep || world < 1 || world > 8 || rank >= world) return -2;
     if (!peer_counter_ready()) return -5;
     peer::Exchange x;
-    x.world = world; x.rank = rank; x.epoch = epoch; x.done_counter = g_peer_counter;
+    x.world = world; x.rank = rank; x.epoch = epoch; x.done_counter = g_peer_counter; x.partial_fp16 = g_peer_partial_fp16;
     for (uint32_t o = 0; o < world; o++) { x.recv[o] = (float*)recv[o]; x.out[0][o] = out[o]; x.flags[o] = (uint32_t*)flags[o]; }
     if (peer::reduce_broadcast(x, 0, residual, M, K, g.err_word, g.stream, norm_w, eps, keep) != cudaSuccess) { cudaGetLastError(); return -4; }
     g.launches++;
@@ -576,6 +588,7 @@ int b200_peer_reduce_norm_broadcast(uint32_t rank, uint32_t world, void* const* 
 }
 
 void b200_peer_set_wait_limit_ms(unsigned ms) { peer::set_wait_limit_ms(ms); }
+void b200_peer_set_partial_fp16(int on) { g_peer_partial_fp16 = on != 0; }
 
 int b200_peer_wait_rows(uint32_t rank, uint32_t world, void* const* flags, uint32_t epoch) {
     std::lock_guard<std::mutex> lock(g.mu);

@@ -72,7 +72,7 @@ def _bind_layer(lib) -> None:
     lib.b200_peer_wait_rows.argtypes = [u32, u32, pp, u32]
     lib.b200_peer_reduce_norm_broadcast.argtypes = [u32, u32, pp, pp, pp, u32, vp, u32, u32, vp, ctypes.c_float, vp]
     lib.b200_peer_reduce_norm_broadcast.restype = ctypes.c_int
-    lib.b200_peer_exchange_create.argtypes = [u32, u32, pp, pp, pp, pp]
+    lib.b200_peer_exchange_create.argtypes = [u32, u32, pp, pp, pp, pp, ctypes.c_int]
     lib.b200_peer_exchange_create.restype = vp
     lib.b200_peer_exchange_destroy.argtypes = [vp]
     lib.b200_peer_exchange_destroy.restype = None
@@ -141,9 +141,12 @@ class TransformerLayerCoordinator:
                                "(needs tp_size == world and M / world a multiple of 256)")
 
     def profile_forward(self, *tensors) -> list:
-        """One forward with a CUDA event after every launch: [(what ran, microseconds), ...] in launch order."""
+        """A forward with a CUDA event after every launch: [(what ran, microseconds), ...] in launch order.  Two forwards
+        run back to back and the second one is reported: in a tensor-parallel group the first one's exchanges bring the
+        ranks into step, so the second one's waits show the exchange itself rather than the ranks' start-up skew."""
         self.lib.b200_layer_set_profiling(self._h, 1)
         try:
+            self.forward(*tensors)
             self.forward(*tensors)
             cap, lb = 64, 96
             labels = ctypes.create_string_buffer(cap * lb)
@@ -187,8 +190,14 @@ class PeerExchange:
 
     KINDS = ("recv", "out0", "out1", "flags")
 
-    def __init__(self, bridge: B200Bridge, M: int, K: int, rank: int, world: int) -> None:
+    def __init__(self, bridge: B200Bridge, M: int, K: int, rank: int, world: int, partial_fp16: Optional[bool] = None) -> None:
         self.bridge, self.rank, self.world = bridge, rank, world
+        # Partial sums cross NVLink as fp16 by default (the exchange is bound by NVLink bytes at 4 and 8 ranks); fp32
+        # with B200_EXCHANGE_FP32=1 or partial_fp16=False.  Every rank of a group must choose the same.
+        if partial_fp16 is None:
+            import os
+            partial_fp16 = os.environ.get("B200_EXCHANGE_FP32", "0") != "1"
+        self.partial_fp16 = bool(partial_fp16)
         _bind_layer(bridge.lib)
         self.sizes = {"recv": M * K * 4, "out0": M * K * 2, "out1": M * K * 2, "flags": 64}
         self.own: dict = {}
@@ -221,7 +230,7 @@ class PeerExchange:
                 self._opened.append(p.value)
         arr = lambda xs: (ctypes.c_void_p * self.world)(*xs)
         self.handle = self.bridge.lib.b200_peer_exchange_create(self.rank, self.world, arr(self.ptrs["recv"]), arr(self.ptrs["out0"]),
-                                                                arr(self.ptrs["out1"]), arr(self.ptrs["flags"]))
+                                                                arr(self.ptrs["out1"]), arr(self.ptrs["flags"]), int(self.partial_fp16))
         if not self.handle:
             raise RuntimeError("b200_peer_exchange_create failed")
 

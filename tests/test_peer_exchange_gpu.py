@@ -57,16 +57,19 @@ def test_scatter_reduce_broadcast_emulated_ranks(bridge, pkg, world, fmt):
         assert all(torch.equal(out[0], out[r]) for r in range(1, world))     # every rank holds the same bits
 
 
+@pytest.mark.parametrize("partial_fp16", [False, True])
 @pytest.mark.parametrize("world", [2, 8])
-def test_reduction_with_fused_rmsnorm_emulated_ranks(bridge, pkg, world):
+def test_reduction_with_fused_rmsnorm_emulated_ranks(bridge, pkg, world, partial_fp16):
     """Row-sharded residual stream: the owner of a row adds the partial rows and the residual, keeps the fp16 sum for
     itself and sends rmsnorm(sum) * w to every rank.  Ranks emulated phase by phase on one GPU; several token tiles per
     rank, so the rotated owner order of the scatter epilogue (rank r sends to r+1 first, to itself last) is exercised."""
     from m4_prefill_engine_b200.layer import _bind_layer, shard_cols
     L = bridge.lib
     _bind_layer(L)
+    L.b200_peer_set_partial_fp16.argtypes = [ctypes.c_int]
+    L.b200_peer_set_partial_fp16.restype = None
     fmt = o.Q4_0
-    M, K_total, N = 512 * world, 256 * world, 512            # two token tiles per rank, four weight tiles
+    M, K_total, N = 512 * world, 256 * world, 1024           # two token tiles per rank, eight weight tiles
     g = o.RefLcg(40 + world)
     W = g.weights(fmt, K_total, N)
     X = (g.activations(M, K_total).astype(np.float32) * 0.5).astype(np.float16)
@@ -85,13 +88,17 @@ def test_reduction_with_fused_rmsnorm_emulated_ranks(bridge, pkg, world):
     torch.cuda.synchronize()
     recv_p, out_p, flag_p = _arr([t.data_ptr() for t in recv]), _arr([t.data_ptr() for t in out]), _arr([t.data_ptr() for t in flags])
     for epoch in (1, 2):
-        for r in range(world):
-            assert L.b200_peer_gemm_scatter(Xs[r].data_ptr(), Ws[r].data_ptr(), fmt, M, k_loc, N, r, world, recv_p, flag_p, epoch) == 0
-        for r in range(world):
-            assert L.b200_peer_reduce_norm_broadcast(r, world, recv_p, out_p, flag_p, epoch, Rd.data_ptr(), M, N, wd.data_ptr(),
-                                                     ctypes.c_float(1e-5), keep[r].data_ptr()) == 0
-        for r in range(world):
-            assert L.b200_peer_wait_rows(r, world, flag_p, epoch) == 0
+        L.b200_peer_set_partial_fp16(int(partial_fp16))      # partial sums as fp16 in the (fp32-sized) receive buffers, or as fp32
+        try:
+            for r in range(world):
+                assert L.b200_peer_gemm_scatter(Xs[r].data_ptr(), Ws[r].data_ptr(), fmt, M, k_loc, N, r, world, recv_p, flag_p, epoch) == 0
+            for r in range(world):
+                assert L.b200_peer_reduce_norm_broadcast(r, world, recv_p, out_p, flag_p, epoch, Rd.data_ptr(), M, N, wd.data_ptr(),
+                                                         ctypes.c_float(1e-5), keep[r].data_ptr()) == 0
+            for r in range(world):
+                assert L.b200_peer_wait_rows(r, world, flag_p, epoch) == 0
+        finally:
+            L.b200_peer_set_partial_fp16(0)
         bridge.synchronize()
         assert bridge.device_error() == 0
         mid = np.concatenate([keep[r][r * rows:(r + 1) * rows].cpu().numpy() for r in range(world)])    # each rank kept its own rows
