@@ -149,6 +149,17 @@ void b200_bridge_force_generic(int on);
  * bit-identical to separate dispatches that run the same split.  No counterpart in the reference. */
 int b200_bridge_dispatch_gemm_grouped(const void* X, const void* const* W, void* const* Y, const uint32_t* N, uint32_t count,
                                       int format, uint32_t M, uint32_t K, int layout, uint32_t D);
+/* Q, K and V projections of one block in one launch with the K/V-cache work fused into the epilogue: head-major outputs
+ * (the reference's LAYOUT_DIRECT_HEAD scatter, quant_router_kernels.metal:570-575), rotary embedding on Q and K at
+ * positions pos0 .. pos0+M-1 (rope_theta > 0; src/engine/model.py:218-226) and, with kv_q8_0 != 0, K and V written straight
+ * into a Q8_0 cache (quantize_kv_to_q8_0, unified_8b_kernels.metal:118-145; cache update of src/engine/modules.py:628-729):
+ * Kc / Vc are then block_q8_0 [Hkv][kv_tokens][D/32] and this call fills tokens pos0 .. pos0+M-1 of every head (kv_tokens
+ * == 0 means M).  Without kv_q8_0, Kc / Vc are fp16 [Hkv][M][D].  Q is fp16 [Hq][M][D].  Device pointers, formats 0..5,
+ * D 64 or 128, K % 256 == 0.  Bit-identical to the projections followed by b200_bridge_rope and
+ * b200_bridge_quantize_kv_q8_0.  Returns -4 where the fused launch is not available (few tokens: the planner splits K). */
+int b200_bridge_dispatch_qkv_fused(const void* X, const void* Wq, const void* Wk, const void* Wv, void* Q, void* Kc, void* Vc, int format,
+                                   uint32_t M, uint32_t K, uint32_t Hq, uint32_t Hkv, uint32_t D, float rope_theta, uint32_t pos0,
+                                   int kv_q8_0, uint32_t kv_tokens);
 /* Testing hook: != 0 routes head-dim-128 Q8_0 attention to the warp-level MMA kernels instead of the
  * tensor-memory kernel, so the two can be compared on the same inputs. */
 void b200_bridge_force_legacy_attention(int on);

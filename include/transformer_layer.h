@@ -73,6 +73,10 @@ public:
     // Per-launch timing: with profiling on, forward() records a CUDA event after every launch; profile() returns, for
     // the last forward, up to `cap` (label, microseconds) pairs in launch order (the caller synchronises first).
     void set_profiling(bool on);
+    // Rotary embedding and Q8_0 K/V compression in the epilogue of the grouped Q/K/V projection (taken where that launch
+    // runs without a K split) instead of one pass over Q, K and V behind the projection (the default, which measures
+    // faster).  The results are bit-identical either way.
+    void set_fused_kv_epilogue(bool on);
     size_t profile(const char** labels, float* us, size_t cap) const;
 
     // Enqueue one layer on `stream`.  All pointers are device pointers.  Weight shapes for rank r of
@@ -142,6 +146,7 @@ int b200_layer_attach_peer_exchange(void* layer, void* exchange);
 /* Per-launch timing of the next forward calls (CUDA events between launches); b200_layer_profile waits for the stream
  * and writes up to `cap` labels (label_bytes each, NUL-terminated) and durations in microseconds; returns the count. */
 int b200_layer_set_profiling(void* layer, int on);
+int b200_layer_set_fused_kv_epilogue(void* layer, int on);
 int b200_layer_profile(void* layer, char* labels, size_t label_bytes, float* us, size_t cap);
 /* The three steps on their own (device pointers): partial sums of Y = X.W^T scattered to the owners' receive
  * buffers; the owner's reduction + residual + broadcast into out[]; the wait for every rank's rows. */

@@ -108,6 +108,7 @@ _OPTIONAL = {
     "b200_bridge_rmsnorm": ([_vp, _vp, _vp, _u32, _u32, _f], _i),
     "b200_bridge_rope": ([_vp, _u32, _u32, _u32, _f, _u32], _i),
     "b200_bridge_gemm_scratch_static": ([_vp, _sz, _vp, _sz, _vp, _sz, _i, _u32, _u32, _u32], _i),
+    "b200_bridge_dispatch_qkv_fused": ([_vp] * 7 + [_i] + [_u32] * 5 + [_f, _u32, _i, _u32], _i),
 }
 
 

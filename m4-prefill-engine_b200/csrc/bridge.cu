@@ -14,6 +14,7 @@
 #include "../../include/b200_bridge.h"
 #include "../../include/quant_router.h"
 #include "bridge_state.cuh"
+#include "layer_ops.cuh"
 #include "qgemm.cuh"
 
 namespace bridge {
@@ -322,6 +323,49 @@ int b200_bridge_dispatch_gemm_grouped(const void* X, const void* const* W, void*
     return 0;
 }
 
+int b200_bridge_dispatch_qkv_fused(const void* X, const void* Wq, const void* Wk, const void* Wv, void* Q, void* Kc, void* Vc, int format,
+                                   uint32_t M, uint32_t K, uint32_t Hq, uint32_t Hkv, uint32_t D, float rope_theta, uint32_t pos0,
+                                   int kv_q8_0, uint32_t kv_tokens) {
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.initialized) return -1;
+    if (!X || !Wq || !Wk || !Wv || !Q || !Kc || !Vc) return -2;
+    const void* ptrs[7] = {X, Wq, Wk, Wv, Q, Kc, Vc};
+    for (const void* q : ptrs) if (!is_device_ptr(q)) return -2;
+    if (format < 0 || format >= 6) return -3;
+    if (M == 0 || K == 0 || Hq == 0 || Hkv == 0 || (D != 64 && D != 128) || K % 256 != 0 || Hq % Hkv != 0) return -4;
+    if (kv_tokens == 0) kv_tokens = M;
+    if (kv_q8_0 ? ((uint64_t)pos0 + M > kv_tokens) : (pos0 != 0 && kv_tokens != M)) return -4;
+    if (!kv_q8_0 && kv_tokens != M) return -4;                 // fp16 K/V come out as [Hkv][M][D] of this call only
+    qg::GemmArgs a;
+    memset(&a, 0, sizeof(a));
+    a.format = format; a.X = X; a.W0 = Wq; a.Y = Q; a.M = M; a.N = Hq * D; a.K = K; a.layout = LAYOUT_DIRECT_HEAD; a.H = Hq; a.D = D;
+    a.n_extra = 2; a.W_extra[0] = Wk; a.W_extra[1] = Wv; a.Y_extra[0] = Kc; a.Y_extra[1] = Vc; a.N_extra[0] = a.N_extra[1] = Hkv * D;
+    const uint32_t rope = rope_theta > 0.0f ? 1u : 0u, q8 = kv_q8_0 ? 2u : 0u;
+    a.post[0] = rope; a.post[1] = rope | q8; a.post[2] = q8;
+    a.kv_tokens = kv_tokens; a.kv_pos0 = kv_q8_0 ? pos0 : 0u;
+    if (rope) {
+        // (cos, sin) of positions pos0 .. pos0 + M - 1, rebuilt only when the request changes
+        if (g.rope_M != M || g.rope_D != D || g.rope_theta != rope_theta || g.rope_pos0 != pos0 || !g.rope_table.p) {
+            cudaStreamSynchronize(g.stream);                  // the table may still be in use by the previous launch
+            if (!g.rope_table.ensure((size_t)M * (D / 2) * 8)) return -5;
+            if (lops::build_rope_table(g.rope_table.p, M, D, rope_theta, pos0, g.stream) != cudaSuccess) { cudaGetLastError(); return -6; }
+            g.rope_M = M; g.rope_D = D; g.rope_theta = rope_theta; g.rope_pos0 = pos0;
+            g.launches++;
+        }
+        a.rope_table = g.rope_table.p;
+    }
+    if (!a.post[0] && !a.post[1] && !a.post[2]) {}            // nothing to fuse: a plain grouped launch
+    if (!ensure_workspace(qg::workspace_floats(a))) return -5;
+    qg::Workspace ws;
+    ws.partial = (float*)g.ws_partial.p; ws.partial_floats = g.ws_partial.cap / sizeof(float);
+    ws.counters = g.counters; ws.err = g.err_word;
+    cudaError_t e = qg::launch(a, ws, g.stream);
+    if (e == cudaErrorInvalidValue) { cudaGetLastError(); return -4; }
+    if (e != cudaSuccess) { set_error(std::string("kernel launch failed: ") + cudaGetErrorString(e)); return -6; }
+    g.launches += (uint64_t)qg::last_launch_count();
+    return 0;
+}
+
 int b200_bridge_register_weights(const void* host_ptr, size_t bytes) {
     std::lock_guard<std::mutex> lock(g.mu);
     if (!g.initialized) return -1;
@@ -404,6 +448,7 @@ void m4_bridge_shutdown(void) {
     g.stage_x.release(); g.stage_w0.release(); g.stage_w1.release(); g.stage_y.release(); g.stage_res.release();
     g.stage_aux0.release(); g.stage_aux1.release(); g.stage_aux2.release();
     g.ws_partial.release();
+    g.rope_table.release(); g.rope_M = g.rope_D = 0;
     for (auto& kv : g.registered) cudaFree(kv.second.dev);
     g.registered.clear();
     cudaFree(g.counters); g.counters = nullptr; g.err_word = nullptr;

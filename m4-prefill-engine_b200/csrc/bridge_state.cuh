@@ -46,6 +46,9 @@ struct State {
     uint64_t dispatch_seq = 0;           // counts device -> host copies enqueued; synchronize clears marks up to its snapshot
     DevBuf stage_x, stage_w0, stage_w1, stage_y, stage_res, stage_aux0, stage_aux1, stage_aux2;
     DevBuf ws_partial;          // split-K partial tiles
+    DevBuf rope_table;          // (cos, sin) table of the last fused Q/K/V dispatch, and the request it was built for
+    uint32_t rope_M = 0, rope_D = 0, rope_pos0 = 0;
+    float rope_theta = 0.0f;
     uint32_t* counters = nullptr;  // 4096 tile counters (kept zero between launches) + error word
     int* err_word = nullptr;
     std::unordered_map<const void*, Registered> registered;

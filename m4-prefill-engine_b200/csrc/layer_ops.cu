@@ -76,8 +76,21 @@ __global__ void rope_kernel(__half* __restrict__ X, uint32_t M, uint32_t D, floa
     sincosf(ang, &s, &c);
     __half* x = X + row * D;
     const float a = __half2float(x[j]), b = __half2float(x[j + half]);
-    x[j] = __float2half_rn(a * c - b * s);
-    x[j + half] = __float2half_rn(b * c + a * s);
+    x[j] = __float2half_rn(__fmaf_rn(a, c, -__fmul_rn(b, s)));
+    x[j + half] = __float2half_rn(__fmaf_rn(b, c, __fmul_rn(a, s)));
+}
+
+// (cos, sin) of every (position, frequency) of a launch, for the projection epilogue that applies the rotation itself:
+// table[m][j] = sincos((pos0 + m) * theta^(-2j/D)), the very expression of the kernels above, so a fused rotation and a
+// separate one agree bit for bit.
+__global__ void rope_table_kernel(float2* __restrict__ table, uint32_t M, uint32_t D, float log2_theta, uint32_t pos0) {
+    const uint32_t half = D / 2;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)M * half) return;
+    const uint32_t m = (uint32_t)(i / half), j = (uint32_t)(i % half);
+    float s, c;
+    sincosf((float)(pos0 + m) * exp2f(-2.0f * (float)j / (float)D * log2_theta), &s, &c);
+    table[i] = make_float2(c, s);
 }
 
 // Rotate-half RoPE for D % 4 == 0: one thread owns two adjacent frequencies of one token and walks all heads, so
@@ -107,10 +120,11 @@ __global__ void rope_heads_kernel(__half* __restrict__ X, uint32_t H, uint32_t M
         for (int u = 0; u < 4; u++)
             if (h0 + u < H) {
                 const float a0 = __low2float(lo[u]), a1 = __high2float(lo[u]), b0 = __low2float(hi[u]), b1 = __high2float(hi[u]);
+                // (multiply-adds spelled out so that every kernel that rotates rounds alike)
                 *reinterpret_cast<__half2*>(x + u * head_stride) =
-                    __halves2half2(__float2half_rn(a0 * c0 - b0 * s0), __float2half_rn(a1 * c1 - b1 * s1));
+                    __halves2half2(__float2half_rn(__fmaf_rn(a0, c0, -__fmul_rn(b0, s0))), __float2half_rn(__fmaf_rn(a1, c1, -__fmul_rn(b1, s1))));
                 *reinterpret_cast<__half2*>(x + u * head_stride + half) =
-                    __halves2half2(__float2half_rn(b0 * c0 + a0 * s0), __float2half_rn(b1 * c1 + a1 * s1));
+                    __halves2half2(__float2half_rn(__fmaf_rn(b0, c0, __fmul_rn(a0, s0))), __float2half_rn(__fmaf_rn(b1, c1, __fmul_rn(a1, s1))));
             }
     }
 }
@@ -214,6 +228,99 @@ cudaError_t rope(void* X, uint32_t H, uint32_t M, uint32_t D, float theta, uint3
     }
     const size_t pairs = (size_t)H * M * (D / 2);
     rope_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>((__half*)X, M, D, log2f(theta), pos0, pairs);
+    return cudaGetLastError();
+}
+// Everything between the Q/K/V projections and attention in one pass: rotary embedding on Q and K (in place for Q),
+// K and V compressed to Q8_0 records.  One warp per token walks that token's rows of all heads: a row of D = 128 fp16 is
+// 8 bytes per lane, the rotation partner (i +- D/2) sits 16 lanes away, the 32 values of a Q8_0 record are those of 8
+// neighbouring lanes, and the token's (cos, sin) values are read from the table once and reused for every head.
+// Arithmetic is that of rope_heads_kernel and of attn::quantize_q8_0_kernel, bit for bit.
+__global__ void __launch_bounds__(128) kv_post_d128_kernel(__half* __restrict__ Q, const __half* __restrict__ Kin, const __half* __restrict__ Vin,
+                                                           uint8_t* __restrict__ Kq, uint8_t* __restrict__ Vq, __half* __restrict__ Kout,
+                                                           const float2* __restrict__ table, uint32_t Hq, uint32_t Hkv, uint32_t M, int rope, int q8) {
+    constexpr uint32_t D = 128, HALF = 64;
+    const uint32_t m = blockIdx.x * 4u + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
+    if (m >= M) return;
+    const bool upper = lane >= 16u;
+    float2 cs[4];
+    if (rope) {
+        const float4* t4 = reinterpret_cast<const float4*>(table + (size_t)m * HALF + (lane & 15u) * 4u);
+        const float4 a = __ldg(t4), b = __ldg(t4 + 1);
+        cs[0] = make_float2(a.x, a.y); cs[1] = make_float2(a.z, a.w); cs[2] = make_float2(b.x, b.y); cs[3] = make_float2(b.z, b.w);
+    }
+    auto rotate = [&](uint2 w) {
+        uint2 pw;
+        pw.x = __shfl_xor_sync(0xffffffffu, w.x, 16); pw.y = __shfl_xor_sync(0xffffffffu, w.y, 16);
+        const float2 x01 = __half22float2(*reinterpret_cast<const __half2*>(&w.x)), x23 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+        const float2 y01 = __half22float2(*reinterpret_cast<const __half2*>(&pw.x)), y23 = __half22float2(*reinterpret_cast<const __half2*>(&pw.y));
+        const float x[4] = {x01.x, x01.y, x23.x, x23.y}, y[4] = {y01.x, y01.y, y23.x, y23.y};
+        float r[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++)      // lower half: a*c - b*s with (a, b) = (x, y); upper half: b*c + a*s with (a, b) = (y, x)
+            r[e] = upper ? __fmaf_rn(x[e], cs[e].x, __fmul_rn(y[e], cs[e].y)) : __fmaf_rn(x[e], cs[e].x, -__fmul_rn(y[e], cs[e].y));
+        const __half2 h01 = __floats2half2_rn(r[0], r[1]), h23 = __floats2half2_rn(r[2], r[3]);
+        uint2 o;
+        o.x = *reinterpret_cast<const uint32_t*>(&h01); o.y = *reinterpret_cast<const uint32_t*>(&h23);
+        return o;
+    };
+    auto quantise = [&](uint2 w, uint8_t* rec_row) {      // rec_row: the four records of this (head, token) row
+        const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&w.x)), f23 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+        const float v[4] = {f01.x, f01.y, f23.x, f23.y};
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        const float d = __fdiv_rn(amax, 127.0f);
+        const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+        uint16_t* o = reinterpret_cast<uint16_t*>(rec_row + (lane >> 3) * 34u);
+        if ((lane & 7u) == 0u) o[0] = __half_as_ushort(__float2half_rn(d));
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            int q0 = (int)roundf(__fmul_rn(v[2 * e], id)), q1 = (int)roundf(__fmul_rn(v[2 * e + 1], id));
+            q0 = max(-128, min(127, q0)); q1 = max(-128, min(127, q1));
+            o[1 + (lane & 7u) * 2u + e] = (uint16_t)((uint32_t)(uint8_t)(int8_t)q0 | ((uint32_t)(uint8_t)(int8_t)q1 << 8));
+        }
+    };
+    if (rope) {
+        // heads in batches of four: the loads of a batch are issued before its first store
+        for (uint32_t h0 = 0; h0 < Hq; h0 += 4) {
+            uint2 w[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (h0 + u < Hq) w[u] = *reinterpret_cast<const uint2*>(Q + ((size_t)(h0 + u) * M + m) * D + lane * 4u);
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (h0 + u < Hq) *reinterpret_cast<uint2*>(Q + ((size_t)(h0 + u) * M + m) * D + lane * 4u) = rotate(w[u]);
+        }
+    }
+    for (uint32_t h = 0; h < Hkv; h++) {
+        const size_t row = ((size_t)h * M + m);
+        uint2 k = *reinterpret_cast<const uint2*>(Kin + row * D + lane * 4u);
+        const uint2 v = *reinterpret_cast<const uint2*>(Vin + row * D + lane * 4u);
+        if (rope) k = rotate(k);
+        if (q8) {
+            quantise(k, Kq + row * (D / 32u) * 34u);
+            quantise(v, Vq + row * (D / 32u) * 34u);
+        } else if (rope) {
+            *reinterpret_cast<uint2*>(Kout + row * D + lane * 4u) = k;
+        }
+    }
+}
+
+cudaError_t kv_post(void* Q, const void* K, const void* V, void* Kq, void* Vq, const void* rope_table, uint32_t Hq, uint32_t Hkv,
+                    uint32_t M, uint32_t D, bool rope, bool q8, cudaStream_t s) {
+    if (D != 128 || (rope && !rope_table) || (q8 && (!Kq || !Vq))) return cudaErrorInvalidValue;
+    if (((reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(K) | reinterpret_cast<uintptr_t>(V)) & 7u) ||
+        (reinterpret_cast<uintptr_t>(rope_table) & 15u))
+        return cudaErrorInvalidValue;
+    kv_post_d128_kernel<<<(M + 3) / 4, 128, 0, s>>>((__half*)Q, (const __half*)K, (const __half*)V, (uint8_t*)Kq, (uint8_t*)Vq, (__half*)K,
+                                                   (const float2*)rope_table, Hq, Hkv, M, rope ? 1 : 0, q8 ? 1 : 0);
+    return cudaGetLastError();
+}
+
+cudaError_t build_rope_table(void* table, uint32_t M, uint32_t D, float theta, uint32_t pos0, cudaStream_t s) {
+    const size_t n = (size_t)M * (D / 2);
+    rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>((float2*)table, M, D, log2f(theta), pos0);
     return cudaGetLastError();
 }
 cudaError_t add_residual_f32(const void* A, const float* B, void* Y, size_t n, cudaStream_t s) {

@@ -77,7 +77,7 @@ constexpr int ACC_STRIDE = 256; // tensor-memory columns per accumulator buffer
 
 constexpr int XCHG_BYTES = 2 * 128 * 32;   // epilogue exchange area: two buffers of 16 tokens x 128 features of fp16 (row-wise
                                            // epilogue), or of 8 floats per epilogue thread (SwiGLU)
-constexpr int XCHG_BYTES_F32 = 2 * XCHG_BYTES;   // row-wise epilogue of fp32 partial sums: 16 tokens x 128 features x 4 bytes, twice
+constexpr int XCHG_BYTES_F32 = XCHG_BYTES;       // fp32 staging turns over 8 tokens at a time: the same two 4 KB buffers
 constexpr int GATE_ROWS = W_TILE / 2;      // SwiGLU tile: 64 gate rows on TMEM lanes 0..63, their 64 up rows on lanes 64..127
 
 template <int FMT> struct Cfg {
@@ -126,6 +126,11 @@ struct Params {
     uint32_t tiles_per_owner;    // output tiles whose token rows belong to one rank (fused reduce-scatter only)
     uint32_t swiglu;             // 1: tiles are 64 gate rows (matrix 0) + their 64 up rows (matrix 1); output = silu(g) * u
     uint32_t row_epi;            // 1: outputs leave through the row-wise epilogue (16-byte stores of whole token rows)
+    // per matrix of a (grouped) head-major launch: POST_ROPE rotates each head's pairs (i, i + D/2) with the table's
+    // cosines and sines of the token's position; POST_Q8 writes block_q8_0 records [head][token][D/32] instead of fp16
+    uint32_t grp_post[3];
+    const float2* rope_table;    // [M][D/2] (cos, sin), row = token index of this launch
+    uint32_t kv_tokens, kv_pos0; // POST_Q8 records go to [head][kv_tokens][D/32], this launch's token t at index kv_pos0 + t
     const uint8_t* meta0;
     const uint8_t* meta1;
     const __half* row_scale0;
@@ -276,6 +281,34 @@ __device__ __forceinline__ void splitk_fixup(const Params& p, const Tile& t, uin
 // between, which every thread reaches after its reads of that buffer).
 //   KIND 0: fp16 to Y            KIND 1: fp16(acc + residual) to Y
 //   KIND 2: fp32 partial sums    KIND 3: fp16 partial sums          (both to `partial`, standard layout of width p.N)
+// Q8_0 record of the 32 values held by four neighbouring lanes (8 each, fp16 pairs in w): fp32 amax / 127 as the scale
+// (stored rounded to fp16), codes from the reciprocal of the unrounded scale, rounded half away from zero and clamped --
+// the arithmetic of attn::quantize_q8_0_kernel, i.e. of the reference's quantize_kv_to_q8_0 (unified_8b_kernels.metal:118-145).
+// `blk` is the record (34 bytes, 2-byte aligned), `part` this lane's quarter of it.  All 32 lanes call (shuffles).
+__device__ __forceinline__ void store_q8_quarter(const uint4& w, uint8_t* blk, uint32_t part, bool write) {
+    const __half2* h = reinterpret_cast<const __half2*>(&w);
+    float v[8], amax = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 4; e++) { const float2 f = __half22float2(h[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+#pragma unroll
+    for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(v[e]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    if (!write) return;
+    uint16_t* o = reinterpret_cast<uint16_t*>(blk);
+    if (part == 0u) o[0] = __half_as_ushort(__float2half_rn(d));
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        int q0 = (int)roundf(__fmul_rn(v[2 * e], id)), q1 = (int)roundf(__fmul_rn(v[2 * e + 1], id));
+        q0 = max(-128, min(127, q0)); q1 = max(-128, min(127, q1));
+        o[1 + part * 4u + e] = (uint16_t)((uint32_t)(uint8_t)(int8_t)q0 | ((uint32_t)(uint8_t)(int8_t)q1 << 8));
+    }
+}
+
+constexpr uint32_t POST_ROPE = 1u, POST_Q8 = 2u;
+
 template <int KIND>
 __device__ __forceinline__ void row_epilogue(const Params& p, uint8_t* stage, uint32_t& batch_ctr, uint32_t taddr, uint32_t et,
                                              uint32_t tok0, uint32_t valid, float rsc, bool row_scale, uint32_t n_tile0, uint32_t Ng,
@@ -284,8 +317,11 @@ __device__ __forceinline__ void row_epilogue(const Params& p, uint8_t* stage, ui
     constexpr int CH = F32 ? 4 : 8;                 // elements per 16-byte chunk of the staging buffer
     constexpr int CPR = W_TILE / CH;                // chunks per token row of the tile
     constexpr int ROWS = 128 / CPR;                 // token rows the 128 threads cover per pass
-    constexpr int PASSES = 16 / ROWS;
-    constexpr int BUF = 16 * W_TILE * (F32 ? 4 : 2);
+    constexpr int TOK = F32 ? 8 : 16;               // token rows turned over per barrier: one buffer is 4 KB either way, so the
+                                                    // exchange area stays at 8 KB and the operand rings keep their depth
+    constexpr int PASSES = TOK / ROWS;
+    constexpr int BUF = TOK * W_TILE * (F32 ? 4 : 2);
+    static_assert(2 * BUF <= XCHG_BYTES, "two staging buffers fit the exchange area");
     const uint32_t chunk = et % CPR, jrow = et / CPR;
     const uint32_t n = n_tile0 + chunk * CH;
     const bool n_ok = n < Ng;
@@ -294,12 +330,11 @@ __device__ __forceinline__ void row_epilogue(const Params& p, uint8_t* stage, ui
     else if (p.layout == 1) { col_base = (size_t)(n / p.D) * p.M * p.D + (n % p.D); tok_stride = p.D; }
     else { col_base = n; tok_stride = Ng; }
     col_base += (size_t)tok0 * tok_stride;
-    for (uint32_t c0 = 0; c0 < p.T; c0 += 16, batch_ctr++) {
-        uint8_t* buf = stage + (batch_ctr & 1u) * BUF;
-        uint2 res[PASSES];
+    for (uint32_t c0 = 0; c0 < p.T; c0 += 16) {
+        uint2 res[16 / ROWS];
         if (KIND == 1) {             // requested before the accumulator is read: the latency hides behind the turn-over
 #pragma unroll
-            for (int h = 0; h < PASSES; h++) {
+            for (int h = 0; h < 16 / ROWS; h++) {
                 const uint32_t tok = c0 + jrow + h * ROWS;
                 res[h] = (n_ok && tok < valid) ? __ldg(reinterpret_cast<const uint2*>(p.residual + col_base + (size_t)tok * tok_stride))
                                                : make_uint2(0u, 0u);
@@ -308,34 +343,103 @@ __device__ __forceinline__ void row_epilogue(const Params& p, uint8_t* stage, ui
         uint32_t v[16];
         ptx::tmem_ld_x16(taddr + c0, v);
         ptx::tmem_ld_wait();
-        if (F32) {
-            float* b = reinterpret_cast<float*>(buf) + et;
 #pragma unroll
-            for (int j = 0; j < 16; j++) b[j * W_TILE] = row_scale ? __uint_as_float(v[j]) * rsc : __uint_as_float(v[j]);
-        } else {
-            __half* b = reinterpret_cast<__half*>(buf) + et;
+        for (int part = 0; part < 16 / TOK; part++, batch_ctr++) {
+            uint8_t* buf = stage + (batch_ctr & 1u) * BUF;
+            if (F32) {
+                float* b = reinterpret_cast<float*>(buf) + et;
 #pragma unroll
-            for (int j = 0; j < 16; j++) b[j * W_TILE] = __float2half_rn(row_scale ? __uint_as_float(v[j]) * rsc : __uint_as_float(v[j]));
+                for (int j = 0; j < TOK; j++) {
+                    const float f = __uint_as_float(v[part * TOK + j]);
+                    b[j * W_TILE] = row_scale ? f * rsc : f;
+                }
+            } else {
+                __half* b = reinterpret_cast<__half*>(buf) + et;
+#pragma unroll
+                for (int j = 0; j < TOK; j++) {
+                    const float f = __uint_as_float(v[part * TOK + j]);
+                    b[j * W_TILE] = __float2half_rn(row_scale ? f * rsc : f);
+                }
+            }
+            ptx::bar_sync(2, 128);
+#pragma unroll
+            for (int h = 0; h < PASSES; h++) {
+                const uint32_t j = jrow + h * ROWS, tok = c0 + part * TOK + j;
+                if (!n_ok || tok >= valid) continue;
+                const uint4 w = reinterpret_cast<const uint4*>(buf)[j * CPR + chunk];
+                if (KIND == 2) {
+                    *reinterpret_cast<uint4*>(reinterpret_cast<float*>(partial) + col_base + (size_t)tok * tok_stride) = w;
+                } else if (KIND == 3) {
+                    *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(partial) + col_base + (size_t)tok * tok_stride) = w;
+                } else if (KIND == 1) {
+                    const uint2 rs = res[part * PASSES + h];
+                    const __half2 r01 = *reinterpret_cast<const __half2*>(&rs.x), r23 = *reinterpret_cast<const __half2*>(&rs.y);
+                    const __half2 h01 = __floats2half2_rn(__uint_as_float(w.x) + __low2float(r01), __uint_as_float(w.y) + __high2float(r01));
+                    const __half2 h23 = __floats2half2_rn(__uint_as_float(w.z) + __low2float(r23), __uint_as_float(w.w) + __high2float(r23));
+                    uint2 o;
+                    o.x = *reinterpret_cast<const uint32_t*>(&h01); o.y = *reinterpret_cast<const uint32_t*>(&h23);
+                    *reinterpret_cast<uint2*>(Yg + col_base + (size_t)tok * tok_stride) = o;
+                } else {
+                    *reinterpret_cast<uint4*>(Yg + col_base + (size_t)tok * tok_stride) = w;
+                }
+            }
         }
+    }
+}
+
+// KIND 0 with the K/V-cache post-operations of a head-major projection fused in: the staged fp16 row (exactly what the
+// plain epilogue would have written) is rotated (POST_ROPE) and / or compressed to Q8_0 (POST_Q8) by the row-moving
+// threads.  A thread's 8 features lie in one half of one head; their rotation partners are the chunk D/16 away in the
+// same staged row, and the 32 values of a Q8_0 record are those of four neighbouring lanes.
+__device__ __forceinline__ void row_epilogue_kv(const Params& p, uint8_t* stage, uint32_t& batch_ctr, uint32_t taddr, uint32_t et,
+                                                uint32_t tok0, uint32_t valid, uint32_t n_tile0, uint32_t Ng, __half* Yg, uint32_t post) {
+    constexpr int CPR = W_TILE / 8, ROWS = 128 / CPR, PASSES = 16 / ROWS, BUF = 16 * W_TILE * 2;
+    const uint32_t chunk = et % CPR, jrow = et / CPR;
+    const uint32_t n = n_tile0 + chunk * 8u;
+    const bool n_ok = n < Ng;
+    const uint32_t half_d = p.D / 2u, head = n / p.D, f = n % p.D;          // f: first of the 8 features inside its head
+    const bool upper = f >= half_d;
+    const uint32_t partner = chunk ^ (half_d / 8u);
+    const size_t col_base = ((size_t)head * p.M + tok0) * p.D + f;          // fp16 output [head][token][D]
+    for (uint32_t c0 = 0; c0 < p.T; c0 += 16, batch_ctr++) {
+        uint8_t* buf = stage + (batch_ctr & 1u) * BUF;
+        uint32_t v[16];
+        ptx::tmem_ld_x16(taddr + c0, v);
+        ptx::tmem_ld_wait();
+        __half* b = reinterpret_cast<__half*>(buf) + et;
+#pragma unroll
+        for (int j = 0; j < 16; j++) b[j * W_TILE] = __float2half_rn(__uint_as_float(v[j]));
         ptx::bar_sync(2, 128);
 #pragma unroll
         for (int h = 0; h < PASSES; h++) {
             const uint32_t j = jrow + h * ROWS, tok = c0 + j;
-            if (!n_ok || tok >= valid) continue;
-            const uint4 w = reinterpret_cast<const uint4*>(buf)[j * CPR + chunk];
-            if (KIND == 2) {
-                *reinterpret_cast<uint4*>(reinterpret_cast<float*>(partial) + col_base + (size_t)tok * tok_stride) = w;
-            } else if (KIND == 3) {
-                *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(partial) + col_base + (size_t)tok * tok_stride) = w;
-            } else if (KIND == 1) {
-                const __half2 r01 = *reinterpret_cast<const __half2*>(&res[h].x), r23 = *reinterpret_cast<const __half2*>(&res[h].y);
-                const __half2 h01 = __floats2half2_rn(__uint_as_float(w.x) + __low2float(r01), __uint_as_float(w.y) + __high2float(r01));
-                const __half2 h23 = __floats2half2_rn(__uint_as_float(w.z) + __low2float(r23), __uint_as_float(w.w) + __high2float(r23));
-                uint2 o;
-                o.x = *reinterpret_cast<const uint32_t*>(&h01); o.y = *reinterpret_cast<const uint32_t*>(&h23);
-                *reinterpret_cast<uint2*>(Yg + col_base + (size_t)tok * tok_stride) = o;
-            } else {
-                *reinterpret_cast<uint4*>(Yg + col_base + (size_t)tok * tok_stride) = w;
+            const bool ok = n_ok && tok < valid;
+            uint4 w = reinterpret_cast<const uint4*>(buf)[j * CPR + chunk];
+            if (post & POST_ROPE) {
+                const uint4 pw = reinterpret_cast<const uint4*>(buf)[j * CPR + partner];
+                const uint32_t trow = ok ? tok0 + tok : 0u;
+                const float4* tab = reinterpret_cast<const float4*>(p.rope_table + (size_t)trow * half_d + (f % half_d));
+                const __half2* hx = reinterpret_cast<const __half2*>(&w);
+                const __half2* hy = reinterpret_cast<const __half2*>(&pw);
+                uint4 o;
+                __half2* ho = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float4 cs = __ldg(tab + e);                       // (cos, sin) of two neighbouring frequencies
+                    const float2 x = __half22float2(hx[e]), y = __half22float2(hy[e]);
+                    // lower half: a*c - b*s with (a, b) = (x, y); upper half: b*c + a*s with (a, b) = (y, x)
+                    const float r0 = upper ? __fmaf_rn(x.x, cs.x, __fmul_rn(y.x, cs.y)) : __fmaf_rn(x.x, cs.x, -__fmul_rn(y.x, cs.y));
+                    const float r1 = upper ? __fmaf_rn(x.y, cs.z, __fmul_rn(y.y, cs.w)) : __fmaf_rn(x.y, cs.z, -__fmul_rn(y.y, cs.w));
+                    ho[e] = __floats2half2_rn(r0, r1);
+                }
+                w = o;
+            }
+            if (post & POST_Q8) {
+                // record (head, token, f / 32): 34 bytes each, [head][token][D/32]
+                uint8_t* blk = reinterpret_cast<uint8_t*>(Yg) + (((size_t)head * p.kv_tokens + p.kv_pos0 + (ok ? tok0 + tok : 0u)) * (p.D / 32u) + f / 32u) * 34u;
+                store_q8_quarter(w, blk, chunk & 3u, ok);
+            } else if (ok) {
+                *reinterpret_cast<uint4*>(Yg + col_base + (size_t)tok * p.D) = w;
             }
         }
     }
@@ -602,28 +706,31 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         const uint32_t q = warp - C::EPI_WARP0;               // == warp % 4: the TMEM lane quadrant
         const uint32_t et = threadIdx.x - C::EPI_WARP0 * 32;  // 0..127
         uint32_t it = 0, xb_i = 0;
-        // Fused reduce-scatter: tiles this warp has finished for the owner it is currently sending to.  When the owner
-        // changes (and at the end) every lane fences its peer stores at system scope once, the warp adds its count to
-        // the rank-wide counter of that owner, and the warp that completes it (tiles x 4 epilogue warps) raises this
-        // rank's arrival flag on the owner: the owner may reduce its rows while this rank still computes tiles for the
-        // others.  Counting per warp needs no barrier among the epilogue warps, so a warp that gave up on a wait cannot
-        // strand the others.
-        uint32_t sc_owner = 0xffffffffu, sc_count = 0;
+        // Fused reduce-scatter: every epilogue warp counts the tiles it has stored per owning rank (eight counters per warp
+        // in shared memory).  After its last tile the warp fences its peer stores at system scope once -- a system-scope
+        // fence under full store traffic costs several microseconds, so there is one per warp and launch, not one per
+        // owner -- and adds its counts to the rank-wide counters; the warp that completes an owner's count (tiles x 4
+        // epilogue warps) raises this rank's arrival flag on that owner.  Counting per warp needs no barrier among the
+        // epilogue warps, so a warp that gave up on a wait cannot strand the others.
+        uint32_t* sc_cnt = reinterpret_cast<uint32_t*>(bars) + 64 + q * 8;      // bytes 256..383 of the barrier block
+        if (p.scatter.world && lane < 8u) sc_cnt[lane] = 0u;
+        __syncwarp();
         bool sc_ok = true;
         auto scatter_flush = [&]() {
-            if (sc_count == 0u) return;
             __threadfence_system();
             __syncwarp();
-            if (lane == 0) {
-                const uint32_t old = atomicAdd(p.scatter.done_counter + 4 + sc_owner, sc_count);
-                if (old + sc_count == 4u * p.tiles_per_owner) {
-                    p.scatter.done_counter[4 + sc_owner] = 0u;
-                    __threadfence_system();
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.scatter.flags[sc_owner] + p.scatter.rank), "r"(p.scatter.epoch) : "memory");
+            if (lane < p.scatter.world) {
+                const uint32_t c = sc_cnt[lane];
+                if (c) {
+                    const uint32_t old = atomicAdd(p.scatter.done_counter + 4 + lane, c);
+                    if (old + c == 4u * p.tiles_per_owner) {
+                        p.scatter.done_counter[4 + lane] = 0u;
+                        __threadfence_system();
+                        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.scatter.flags[lane] + p.scatter.rank), "r"(p.scatter.epoch) : "memory");
+                    }
                 }
             }
             __syncwarp();
-            sc_count = 0u;
         };
         for (uint32_t idx = blockIdx.x; idx < total_tiles; idx += gridDim.x, it++) {
             const Tile t = decode_tile(idx, p);
@@ -643,12 +750,12 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             if (et == 0) QTRC(6, it, 0);
             ptx::tc_fence_after_sync();
             // grouped launch: the matrix this tile belongs to decides the output buffer and its width
-            uint32_t wt_l = t.wt, Ng = p.N;
+            uint32_t wt_l = t.wt, Ng = p.N, grp_post = p.grp_post[0];
             __half* Yg = p.Y;
             if (p.groups > 1u) {
                 uint32_t gi = 0;
                 if (wt_l >= p.grp_tiles[0]) { wt_l -= p.grp_tiles[0]; gi = 1; if (wt_l >= p.grp_tiles[1]) { wt_l -= p.grp_tiles[1]; gi = 2; } }
-                Ng = p.grp_N[gi]; Yg = p.grp_Y[gi];
+                Ng = p.grp_N[gi]; Yg = p.grp_Y[gi]; grp_post = p.grp_post[gi];
             }
             const uint32_t n = wt_l * W_TILE + q * 32 + lane;
             const bool n_ok = n < Ng;
@@ -672,8 +779,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 const ptrdiff_t off = ((ptrdiff_t)p.scatter.rank - (ptrdiff_t)owner) * (ptrdiff_t)p.scatter.rows * (ptrdiff_t)p.N;
                 partial_dst = p.scatter.fp16 ? reinterpret_cast<float*>(reinterpret_cast<__half*>(p.scatter.recv[owner]) + off)
                                              : p.scatter.recv[owner] + off;
-                if (owner != sc_owner) { scatter_flush(); sc_owner = owner; }
-                sc_count++;
+                if (lane == 0) sc_cnt[owner]++;
             }
             const int mode = p.k_splits > 1 ? 0 : (partial_dst ? 1 : ((RESID && p.residual) ? 2 : 3));
             // integer-valued codecs: the row's scale multiplies the fp32 accumulator (before SiLU, before split-K sums)
@@ -687,6 +793,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                     else row_epilogue<2>(p, stage, xb_i, taddr, et, tok0, valid, rsc0, Cd::ROW_SCALE, wt_l * W_TILE, Ng, Yg, partial_dst);
                 } else if (mode == 2) {
                     row_epilogue<1>(p, stage, xb_i, taddr, et, tok0, valid, rsc0, Cd::ROW_SCALE, wt_l * W_TILE, Ng, Yg, nullptr);
+                } else if (grp_post) {
+                    row_epilogue_kv(p, stage, xb_i, taddr, et, tok0, valid, wt_l * W_TILE, Ng, Yg, grp_post);
                 } else {
                     row_epilogue<0>(p, stage, xb_i, taddr, et, tok0, valid, rsc0, Cd::ROW_SCALE, wt_l * W_TILE, Ng, Yg, nullptr);
                 }
@@ -1126,6 +1234,19 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
         }
     }
     if (a.scatter.world && a.scatter.fp16 && !row_ok) return cudaErrorInvalidValue;     // fp16 partial sums exist on the row-wise epilogue only
+    // K/V-cache post-operations: head-major fp16 row epilogue only, whole heads per 128-row tile, Q8_0 records of 32
+    const bool any_post = (a.post[0] | a.post[1] | a.post[2]) != 0u;
+    if (any_post) {
+        if (!row_ok || a.layout != 1 || a.residual || a.partial_out || a.scatter.world || cdc::Codec<FMT>::ROW_SCALE ||
+            (a.D != 64u && a.D != 128u) || a.N % a.D != 0u)
+            return cudaErrorInvalidValue;
+        for (uint32_t e = 0; e < a.n_extra && e < 2u; e++) if (a.N_extra[e] % a.D != 0u) return cudaErrorInvalidValue;
+        if (((a.post[0] | a.post[1] | a.post[2]) & POST_ROPE) && (!a.rope_table || (reinterpret_cast<uintptr_t>(a.rope_table) & 15u))) return cudaErrorInvalidValue;
+    }
+    p.rope_table = reinterpret_cast<const float2*>(a.rope_table);
+    p.kv_tokens = a.kv_tokens ? a.kv_tokens : a.M; p.kv_pos0 = a.kv_pos0;
+    if (any_post && (uint64_t)p.kv_pos0 + a.M > p.kv_tokens) return cudaErrorInvalidValue;
+    for (int gi = 0; gi < 3; gi++) p.grp_post[gi] = (uint32_t)gi <= a.n_extra ? a.post[gi] : 0u;
     p.row_epi = row_ok ? 1u : 0u;
     const long xchg_bytes = a.W1 ? XCHG_BYTES : (row_ok ? ((partial_f32 || a.residual) ? XCHG_BYTES_F32 : XCHG_BYTES) : 0);
     p.raw_stages = raw_stages_for<FMT>(pl.T, xchg_bytes); p.b_stage_bytes = pl.T * 128u;

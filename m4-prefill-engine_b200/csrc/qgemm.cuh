@@ -25,6 +25,13 @@ struct GemmArgs {
     const void* W_extra[2];
     void* Y_extra[2];
     uint32_t N_extra[2];
+    // K/V-cache post-operations fused into the epilogue of a head-major launch (layout 1, D 64 or 128, no K split; else the
+    // launch is refused): post[i] for matrix i (0 = W0, 1.. = W_extra) is a bit set of 1 = rotary embedding with
+    // rope_table[token][D/2] = (cos, sin) of that token's position, 2 = write block_q8_0 records [head][token][D/32] to Y
+    // instead of fp16.  The results are bit-identical to the plain projection followed by lops::rope and attn::launch_quantize.
+    uint32_t post[3];
+    const void* rope_table;
+    uint32_t kv_tokens, kv_pos0;     // Q8_0 records go to [head][kv_tokens][D/32] at token index kv_pos0 + t (kv_tokens == 0: M, offset 0)
     // Tensor-parallel reduce-scatter fused into the epilogue (row-split projections): instead of one local fp32
     // [M][N] buffer, token rows [o * rows, (o + 1) * rows) go to rank o's receive buffer, slot `rank`, through
     // peer-mapped pointers.  Rank r works through the owners in the order r + 1, r + 2, ..., r (its own rows last);

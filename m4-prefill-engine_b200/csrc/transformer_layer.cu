@@ -23,6 +23,7 @@ struct TransformerLayerCoordinator::Impl {
     // intermediates (device)
     void *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *kq = nullptr, *vq = nullptr;
     void *attn = nullptr, *x_mid = nullptr, *act = nullptr;
+    void* rope_table = nullptr;      // (cos, sin) [M][D/2] of positions 0..M-1 for the fused rotation in the Q/K/V epilogue
     float* partial = nullptr;        // tensor-parallel partial sums [M][K]
     float* ws = nullptr;             // split-K scratch
     size_t ws_floats = 0;
@@ -37,6 +38,9 @@ struct TransformerLayerCoordinator::Impl {
     bool bound = false;
     cudaStream_t stream = nullptr;
     // per-launch timing of one forward (profile_forward): an event after every launch
+    bool fuse_kv = false;            // rotary embedding and Q8_0 K/V in the Q/K/V projection's epilogue (where that launch allows it)
+                                     // instead of one launch behind it; same bits, and measured slower: the work lands on the
+                                     // epilogue warps, which share issue slots with the unpack and MMA warps
     bool profiling = false;
     std::vector<cudaEvent_t> events;
     std::vector<std::string> labels;
@@ -57,7 +61,7 @@ TransformerLayerCoordinator::TransformerLayerCoordinator(int device, cudaStream_
 
 TransformerLayerCoordinator::~TransformerLayerCoordinator() {
     void* bufs[] = {impl_->xn, impl_->q, impl_->k, impl_->v, impl_->kq, impl_->vq, impl_->attn, impl_->x_mid, impl_->act,
-                    impl_->partial, impl_->ws, impl_->counters, impl_->own_px.done_counter};
+                    impl_->partial, impl_->ws, impl_->counters, impl_->own_px.done_counter, impl_->rope_table};
     for (void* b : bufs) if (b) cudaFree(b);
     for (cudaEvent_t e : impl_->events) cudaEventDestroy(e);
     delete impl_;
@@ -87,6 +91,10 @@ bool TransformerLayerCoordinator::initialize_pipelines(const void*) {
         ok = dev_alloc(&impl_->kq, qb) && dev_alloc(&impl_->vq, qb);
     }
     if (ok && c.tp_size > 1) ok = dev_alloc((void**)&impl_->partial, (size_t)c.M * c.K * 4);
+    if (ok && c.rope_theta > 0.0f) {
+        ok = dev_alloc(&impl_->rope_table, (size_t)c.M * (c.D / 2) * 8) &&
+             lops::build_rope_table(impl_->rope_table, c.M, c.D, c.rope_theta, 0, impl_->stream) == cudaSuccess;
+    }
     // split-K scratch: sized for the largest projection of this layer (tokens <= 256 per tile)
     if (ok) {
         size_t need = 0;
@@ -162,6 +170,7 @@ bool TransformerLayerCoordinator::attach_peer_exchange(peer::Exchange* shared) {
 }
 
 void TransformerLayerCoordinator::set_profiling(bool on) { impl_->profiling = on; }
+void TransformerLayerCoordinator::set_fused_kv_epilogue(bool on) { impl_->fuse_kv = on; }
 
 size_t TransformerLayerCoordinator::profile(const char** labels, float* us, size_t cap) const {
     const Impl& im = *impl_;
@@ -220,15 +229,28 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
     if (c.rms_eps > 0.0f) { check(lops::rmsnorm(X_in, im.norm1, im.xn, c.M, c.K, c.rms_eps, stream)); x_attn = im.xn; mark("rmsnorm 1"); }
     // Q, K and V read the same activations: one grouped launch (their weight tiles share the persistent grid, so
     // the two narrow projections do not each leave most SMs idle); separate launches where that is not available
-    bool qkv_done = false;
-    if (!status_) {
+    // Where the grouped launch runs without a K split, its epilogue also rotates Q and K (rotary embedding) and writes K
+    // and V as Q8_0 records, which removes four launches and a round trip of Q, K and V through memory.
+    bool qkv_done = false, kv_fused = false;
+    for (int attempt = im.fuse_kv ? 0 : 1; attempt < 2 && !qkv_done && !status_; attempt++) {
+        const bool fuse = attempt == 0 && (c.rope_theta > 0.0f || c.kv_q8_0);
+        if (attempt == 0 && !fuse) continue;
         qg::GemmArgs a; memset(&a, 0, sizeof(a));
         a.format = im.head_binding.format; a.X = x_attn; a.W0 = W_q; a.Y = im.q; a.M = c.M; a.N = hq * c.D; a.K = c.K;
         a.layout = im.head_binding.layout; a.H = hq; a.D = c.D;
         a.n_extra = 2; a.W_extra[0] = W_k; a.W_extra[1] = W_v; a.Y_extra[0] = im.k; a.Y_extra[1] = im.v;
         a.N_extra[0] = a.N_extra[1] = hkv * c.D;
-        if (qg::launch(a, ws, stream) == cudaSuccess) { qkv_done = true; launches_ += (uint32_t)qg::last_launch_count(); mark("q+k+v projections (grouped)"); }
-        else cudaGetLastError();
+        if (fuse) {
+            const uint32_t rope = c.rope_theta > 0.0f ? 1u : 0u, q8 = c.kv_q8_0 ? 2u : 0u;
+            a.post[0] = rope; a.post[1] = rope | q8; a.post[2] = q8;
+            a.rope_table = im.rope_table;
+            if (q8) { a.Y_extra[0] = im.kq; a.Y_extra[1] = im.vq; }
+        }
+        if (qg::launch(a, ws, stream) == cudaSuccess) {
+            qkv_done = true; kv_fused = fuse;
+            launches_ += (uint32_t)qg::last_launch_count();
+            mark(fuse ? "q+k+v projections (grouped) with rope and q8_0 kv in the epilogue" : "q+k+v projections (grouped)");
+        } else cudaGetLastError();
     }
     if (!qkv_done) {
         gemm(im.head_binding, x_attn, W_q, nullptr, im.q, hq * c.D, c.K, hq, nullptr, nullptr);
@@ -236,17 +258,28 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
         gemm(im.head_binding, x_attn, W_v, nullptr, im.v, hkv * c.D, c.K, hkv, nullptr, nullptr);
         mark("q, k, v projections (3 launches)");
     }
-    if (c.rope_theta > 0.0f) {
-        check(lops::rope(im.q, hq, c.M, c.D, c.rope_theta, 0, stream));
-        check(lops::rope(im.k, hkv, c.M, c.D, c.rope_theta, 0, stream));
-        mark("rope q, k");
-    }
     const void *kk = im.k, *vv = im.v;
-    if (c.kv_q8_0) {
-        check(attn::launch_quantize(im.k, im.kq, (size_t)hkv * c.M * c.D, stream));
-        check(attn::launch_quantize(im.v, im.vq, (size_t)hkv * c.M * c.D, stream));
-        kk = im.kq; vv = im.vq;
-        mark("quantize k, v to q8_0");
+    if (kv_fused) {
+        if (c.kv_q8_0) { kk = im.kq; vv = im.vq; }
+    } else if ((c.rope_theta > 0.0f || c.kv_q8_0) &&
+               lops::kv_post(im.q, im.k, im.v, im.kq, im.vq, im.rope_table, hq, hkv, c.M, c.D, c.rope_theta > 0.0f, c.kv_q8_0, stream) == cudaSuccess) {
+        // one pass over Q, K and V: rotary embedding and the Q8_0 records
+        launches_++;
+        if (c.kv_q8_0) { kk = im.kq; vv = im.vq; }
+        mark("rope q, k + quantize k, v (one launch)");
+    } else {
+        cudaGetLastError();
+        if (c.rope_theta > 0.0f) {
+            check(lops::rope(im.q, hq, c.M, c.D, c.rope_theta, 0, stream));
+            check(lops::rope(im.k, hkv, c.M, c.D, c.rope_theta, 0, stream));
+            mark("rope q, k");
+        }
+        if (c.kv_q8_0) {
+            check(attn::launch_quantize(im.k, im.kq, (size_t)hkv * c.M * c.D, stream));
+            check(attn::launch_quantize(im.v, im.vq, (size_t)hkv * c.M * c.D, stream));
+            kk = im.kq; vv = im.vq;
+            mark("quantize k, v to q8_0");
+        }
     }
     check(attn::launch_attention_simple(im.q, kk, vv, im.attn, hq, hkv, c.M, c.M, c.D, c.attn_scale, 0, 1, c.kv_q8_0 ? 0 : 1, stream));
     mark("attention");
@@ -473,6 +506,12 @@ int b200_layer_attach_peer_exchange(void* layer, void* exchange) {
     if (!g.initialized) return -1;
     if (!layer || !exchange) return -2;
     return ((LayerHandle*)layer)->layer->attach_peer_exchange((peer::Exchange*)exchange) ? 0 : -4;
+}
+
+int b200_layer_set_fused_kv_epilogue(void* layer, int on) {
+    if (!layer) return -2;
+    ((LayerHandle*)layer)->layer->set_fused_kv_epilogue(on != 0);
+    return 0;
 }
 
 int b200_layer_set_profiling(void* layer, int on) {

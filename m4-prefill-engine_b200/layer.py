@@ -78,6 +78,8 @@ def _bind_layer(lib) -> None:
     lib.b200_peer_exchange_destroy.restype = None
     lib.b200_layer_attach_peer_exchange.argtypes = [vp, vp]
     lib.b200_layer_set_profiling.argtypes = [vp, ctypes.c_int]
+    lib.b200_layer_set_fused_kv_epilogue.argtypes = [vp, ctypes.c_int]
+    lib.b200_layer_set_fused_kv_epilogue.restype = ctypes.c_int
     lib.b200_layer_profile.argtypes = [vp, ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_float), ctypes.c_size_t]
     for f in ("b200_peer_alloc", "b200_peer_open", "b200_peer_close", "b200_peer_free", "b200_layer_set_peer_exchange",
               "b200_peer_gemm_scatter", "b200_peer_reduce_broadcast", "b200_peer_wait_rows", "b200_layer_attach_peer_exchange",
@@ -139,6 +141,11 @@ class TransformerLayerCoordinator:
         if rc:
             raise RuntimeError(f"b200_layer_attach_peer_exchange failed with status code {rc} "
                                "(needs tp_size == world and M / world a multiple of 256)")
+
+    def set_fused_kv_epilogue(self, on: bool) -> None:
+        """Rotary embedding and Q8_0 K/V compression inside the Q/K/V projection's epilogue (default) or as separate
+        kernels behind it; the layer's output is the same bit for bit."""
+        self.lib.b200_layer_set_fused_kv_epilogue(self._h, int(on))
 
     def profile_forward(self, *tensors) -> list:
         """A forward with a CUDA event after every launch: [(what ran, microseconds), ...] in launch order.  Two forwards

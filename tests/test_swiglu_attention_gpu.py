@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import oracle as o
-from gpu_util import TOL, cfloat, check, check_swiglu, dev
+from gpu_util import TOL, cfloat, check, check_swiglu, dev, run_gemm
 
 pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).resolve().parent / "golden"
@@ -206,3 +206,74 @@ def test_attention_chunked_prefill_consistency(bridge):
     full = run_attn(bridge, Q, Kq, Vq, D ** -0.5, H, M)
     last = run_attn(bridge, np.ascontiguousarray(Q[:, M - 1:]), Kq, Vq, D ** -0.5, H, M, pos0=M - 1)
     assert np.abs(full[:, M - 1:].astype(np.float32) - last.astype(np.float32)).max() <= 1e-3
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(128, 8, 2), (64, 8, 8)])
+@pytest.mark.parametrize("fmt", [o.Q4_0, o.Q4_K])
+def test_fused_qkv_epilogue_is_bit_exact(bridge, fmt, D, Hq, Hkv):
+    """Rotary embedding and Q8_0 compression fused into the Q/K/V projection's epilogue, written straight into a Q8_0
+    cache at a token offset (chunked prefill): the cache bytes and Q equal, bit for bit, what the unfused path gives --
+    head-major projections, then b200_bridge_rope, then the Q8_0 quantiser, whose arithmetic is the reference's
+    quantize_kv_to_q8_0 (unified_8b_kernels.metal:118-145) and which is itself pinned bit-exact against the reference.
+    Then attention over past + present from that cache matches the oracle."""
+    import ctypes
+    L = bridge.lib
+    M1, M2, K = 512, 300, 512                  # two chunks; K = 512 is two packed chunks, which the planner never splits
+    theta, scale = 10000.0, D ** -0.5
+    g = o.RefLcg(77)
+    Wq, Wk, Wv = g.weights(fmt, K, Hq * D), g.weights(fmt, K, Hkv * D), g.weights(fmt, K, Hkv * D)
+    shrink = 0.05 if fmt == o.Q4_K else 1.0
+    Xall = (g.activations(M1 + M2, K).astype(np.float32) * shrink).astype(np.float16)
+    Mt = M1 + M2
+    nblk = Hkv * Mt * (D // 32)
+    Kc = torch.zeros(nblk * 34, dtype=torch.uint8, device="cuda")
+    Vc = torch.zeros(nblk * 34, dtype=torch.uint8, device="cuda")
+    Wd = [dev(w) for w in (Wq, Wk, Wv)]
+    Kref = np.zeros((Hkv, Mt, (D // 32) * 34), np.uint8)
+    Vref = np.zeros_like(Kref)
+    outs = []
+    for pos0, M in ((0, M1), (M1, M2)):
+        X = Xall[pos0:pos0 + M]
+        Xd = dev(X)
+        Qf = torch.full((Hq, M, D), float("nan"), dtype=torch.float16, device="cuda")
+        rc = L.b200_bridge_dispatch_qkv_fused(Xd.data_ptr(), Wd[0].data_ptr(), Wd[1].data_ptr(), Wd[2].data_ptr(), Qf.data_ptr(), Kc.data_ptr(),
+                                              Vc.data_ptr(), fmt, M, K, Hq, Hkv, D, cfloat(theta), pos0, 1, Mt)
+        assert rc == 0
+        # unfused: three head-major projections, rope on Q and K, quantiser on K and V
+        Qu = dev(run_gemm(bridge, fmt, X, Wq, Hq * D, layout=1, H=Hq, D=D))
+        Ku = dev(run_gemm(bridge, fmt, X, Wk, Hkv * D, layout=1, H=Hkv, D=D))
+        Vu = dev(run_gemm(bridge, fmt, X, Wv, Hkv * D, layout=1, H=Hkv, D=D))
+        assert L.b200_bridge_rope(Qu.data_ptr(), Hq, M, D, cfloat(theta), pos0) == 0
+        assert L.b200_bridge_rope(Ku.data_ptr(), Hkv, M, D, cfloat(theta), pos0) == 0
+        n = Hkv * M * D
+        Kq = torch.zeros(n // 32 * 34, dtype=torch.uint8, device="cuda")
+        Vq = torch.zeros_like(Kq)
+        assert L.b200_bridge_quantize_kv_q8_0(Ku.data_ptr(), n * 2, Kq.data_ptr(), Kq.numel(), n) == 0
+        assert L.b200_bridge_quantize_kv_q8_0(Vu.data_ptr(), n * 2, Vq.data_ptr(), Vq.numel(), n) == 0
+        bridge.synchronize()
+        assert bridge.device_error() == 0
+        assert torch.equal(Qf, Qu)
+        Kref[:, pos0:pos0 + M] = Kq.cpu().numpy().reshape(Hkv, M, -1)
+        Vref[:, pos0:pos0 + M] = Vq.cpu().numpy().reshape(Hkv, M, -1)
+        # the oracle's rope and quantiser on the same fp16 projections agree with the device's to the last bit of Q8_0
+        assert np.array_equal(o.quantize_q8_0(Vu.cpu().numpy()).reshape(Hkv, M, -1), Vref[:, pos0:pos0 + M])
+        outs.append(Qf)
+    assert np.array_equal(Kc.cpu().numpy().reshape(Hkv, Mt, -1), Kref)
+    assert np.array_equal(Vc.cpu().numpy().reshape(Hkv, Mt, -1), Vref)
+    # attention of the second chunk over the whole cache (past + present)
+    O = torch.zeros(Hq, M2, D, dtype=torch.float16, device="cuda")
+    assert L.b200_bridge_dispatch_attention_q8kv(outs[1].data_ptr(), Kc.data_ptr(), Vc.data_ptr(), O.data_ptr(), Hq, Hkv, M2, Mt, D,
+                                                 cfloat(scale), M1, 0, 0) == 0
+    bridge.synchronize()
+    Kd = o.dequantize_q8_0(Kc.cpu().numpy(), (Hkv, Mt, D))
+    Vd = o.dequantize_q8_0(Vc.cpu().numpy(), (Hkv, Mt, D))
+    gold = o.attention(outs[1].cpu().numpy(), Kd, Vd, scale, pos0=M1)
+    assert np.abs(O.cpu().numpy().astype(np.float32) - gold.astype(np.float32)).max() <= 2e-3 * max(1.0, float(np.abs(gold.astype(np.float32)).max()))
+    # few tokens and a long K: the planner splits K, which the fused epilogue does not do -- refused, the caller runs the
+    # unfused sequence
+    K2 = 2048
+    Wz = [torch.zeros(L.b200_bridge_weight_bytes(fmt, K2, n), dtype=torch.uint8, device="cuda") for n in (Hq * D, Hkv * D, Hkv * D)]
+    Xs = torch.zeros(33, K2, dtype=torch.float16, device="cuda")
+    Qs = torch.zeros(Hq, 33, D, dtype=torch.float16, device="cuda")
+    assert L.b200_bridge_dispatch_qkv_fused(Xs.data_ptr(), Wz[0].data_ptr(), Wz[1].data_ptr(), Wz[2].data_ptr(), Qs.data_ptr(), Kc.data_ptr(),
+                                            Vc.data_ptr(), fmt, 33, K2, Hq, Hkv, D, cfloat(theta), 0, 1, Mt) == -4
