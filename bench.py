@@ -516,6 +516,8 @@ def time_layer(br, pkg, world: int, rank: int, steps: int, warmup: int, collecti
         collective = "nccl"
         layer.set_allreduce(torch_allreduce_hook(br))
     stream = torch.cuda.ExternalStream(br.lib.b200_bridge_stream())
+    if px is not None:
+        Y = px.result_tensor(c["M"], c["K"])     # the output stays in the exchange's result buffer, as between the layers of a model
     args = (X, w["q"], w["k"], w["v"], w["o"], w["gate"], w["up"], w["down"], Y)
     layer.forward(*args)
     br.synchronize()

@@ -23,21 +23,30 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// true when flags[0 .. world) have all reached epoch; gives up after WAIT_LIMIT_CYCLES
+// True when flags[0 .. world) have all reached epoch; gives up after `limit` cycles.  Called by every lane of one warp:
+// lane s polls flag s, so the `world` round trips to the flag words overlap instead of following one another, and one
+// acquire fence at system scope after the last poll orders the data reads behind all of them.
 __device__ bool wait_flags(const uint32_t* flags, uint32_t world, uint32_t epoch, int* err, int code, long long limit) {
     // once any wait of this process has given up, later ones do not wait again (the host reads the error word and
     // stops using the exchange; without this a broken group would cost ten seconds per kernel)
     if (err && *reinterpret_cast<volatile int*>(err) != 0) return false;
+    const uint32_t lane = threadIdx.x & 31u;
     const long long t0 = clock64();
-    for (uint32_t s = 0; s < world; s++) {
-        while ((int32_t)(ld_acquire_sys(flags + s) - epoch) < 0) {
-            if (clock64() - t0 > limit) {
-                if (err) atomicCAS(err, 0, code);
-                return false;
-            }
-            __nanosleep(200);
+    bool mine = lane >= world;
+    for (;;) {
+        if (!mine) {
+            uint32_t v;
+            asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + lane) : "memory");
+            mine = (int32_t)(v - epoch) >= 0;
         }
+        if (__all_sync(0xffffffffu, mine)) break;
+        if (__any_sync(0xffffffffu, clock64() - t0 > limit)) {
+            if (lane == 0 && err) atomicCAS(err, 0, code);
+            return false;
+        }
+        __nanosleep(100);
     }
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
     return true;
 }
 
@@ -70,7 +79,10 @@ struct ReduceParams {
 template <bool H>
 __global__ void __launch_bounds__(256) reduce_broadcast_kernel(const ReduceParams p) {
     __shared__ uint32_t ok_s;
-    if (threadIdx.x == 0) ok_s = wait_flags(p.my_flags, p.world, p.epoch, p.err, 301, p.wait_limit) ? 1u : 0u;
+    if (threadIdx.x < 32) {
+        const bool ok = wait_flags(p.my_flags, p.world, p.epoch, p.err, 301, p.wait_limit);
+        if (threadIdx.x == 0) ok_s = ok ? 1u : 0u;
+    }
     __syncthreads();
     if (ok_s) {
         constexpr int U = 4;                                       // float4 groups in flight per thread and source
@@ -129,7 +141,10 @@ template <int V, bool H>
 __global__ void __launch_bounds__(256) reduce_norm_broadcast_kernel(const ReduceParams p) {
     __shared__ uint32_t ok_s;
     __shared__ float red[8];
-    if (threadIdx.x == 0) ok_s = wait_flags(p.my_flags, p.world, p.epoch, p.err, 301, p.wait_limit) ? 1u : 0u;
+    if (threadIdx.x < 32) {
+        const bool ok = wait_flags(p.my_flags, p.world, p.epoch, p.err, 301, p.wait_limit);
+        if (threadIdx.x == 0) ok_s = ok ? 1u : 0u;
+    }
     __syncthreads();
     if (ok_s) {
         const uint32_t K4 = p.K / 4;
@@ -203,7 +218,7 @@ __global__ void __launch_bounds__(256) reduce_norm_broadcast_kernel(const Reduce
 }
 
 __global__ void wait_rows_kernel(const uint32_t* my_flags, uint32_t world, uint32_t epoch, int* err, long long limit) {
-    if (threadIdx.x == 0) wait_flags(my_flags + 8, world, epoch, err, 302, limit);
+    wait_flags(my_flags + 8, world, epoch, err, 302, limit);      // one warp
 }
 
 }  // namespace

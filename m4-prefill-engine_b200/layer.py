@@ -271,6 +271,14 @@ class PeerExchange:
             return None
         return px
 
+    def result_tensor(self, M: int, K: int) -> torch.Tensor:
+        """This rank's copy of the exchange's second result buffer as an fp16 [M, K] tensor (no copy).  Passed to
+        ``forward`` as X_out it receives the layer's output directly from the owners' reductions; any other X_out costs
+        one device-to-device copy at the end of the layer.  Valid until ``close``."""
+        class _Raw:
+            __cuda_array_interface__ = {"shape": (M, K), "typestr": "<f2", "data": (self.own["out1"], False), "version": 3}
+        return torch.as_tensor(_Raw(), device="cuda")
+
     def close(self) -> None:
         if self.handle:
             self.bridge.lib.b200_peer_exchange_destroy(self.handle)

@@ -274,7 +274,7 @@ def bench_prefill(bridge: B200Bridge, world: int, rank: int, layers: int = 32, s
     cfg = EngineConfig(num_layers=layers, hidden_dim=4096, num_q_heads=32, num_kv_heads=8, head_dim=128, intermediate_dim=14336,
                        vocab_size=128256, rope_theta=500000.0, weight_format=0, max_context_length=2048, tp_size=world)
     M = 2048
-    if cfg.num_kv_heads % world or cfg.intermediate_dim % world or cfg.vocab_size % (world * 128):
+    if cfg.num_kv_heads % world or cfg.intermediate_dim % world or cfg.vocab_size % world:
         return {"skipped": f"shape does not shard over {world} ranks"}
     model = TransformerModel(cfg, M, bridge)
     model.init_synthetic_weights(seed=11, rank=rank)
