@@ -16,7 +16,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = CSRC / "_obj"
 LIB = HERE / "libb200_bridge.so"
-SOURCES = ["qgemm.cu", "qgemv.cu", "bridge.cu", "attention.cu", "layer_ops.cu", "transformer_layer.cu", "transformer_model.cu", "peer_reduce.cu", "no_alloc.cu", "quant_registry.cpp", "gguf_loader.cpp"]
+SOURCES = ["qgemm.cu", "qgemm_small.cu", "qgemv.cu", "bridge.cu", "attention.cu", "layer_ops.cu", "transformer_layer.cu", "transformer_model.cu", "peer_reduce.cu", "no_alloc.cu", "quant_registry.cpp", "gguf_loader.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v", "-I", str(HERE.parent / "include")]
 # development builds only: extra nvcc flags (e.g. -DATTN_TRACE, -DQG_TRACE=1) from the environment

@@ -338,6 +338,35 @@ def test_8b_projection_m2048(bridge, fmt):
     assert np.array_equal(Yp.view(np.uint16), Y[perm].view(np.uint16))
 
 
+@pytest.mark.parametrize("fmt", ALL_CODECS)
+def test_few_token_kernels_agree(bridge, fmt):
+    """The cluster kernel (weights unpacked into tensor memory, K split over a thread-block cluster, partial tiles summed in
+    distributed shared memory) against the persistent kernel (split-K through a scratch buffer) on the same inputs: both
+    within tolerance of the oracle, and of each other within the fp32 summation-order difference (one fp16 ulp)."""
+    K, N = 4096, 1000 if fmt != o.PRISM_Q2_0 else 1024
+    for M in (5, 33, 130, 256):
+        X, W = o.baseline_inputs(fmt, M, K, N, 60 + M)
+        gold = o.gemm_f64(fmt, X, W, N)
+        Ya = run_gemm(bridge, fmt, X, W, N, ex=True)
+        bridge.lib.b200_bridge_enable_small_kernel(0)
+        try:
+            Yb = run_gemm(bridge, fmt, X, W, N, ex=True)
+        finally:
+            bridge.lib.b200_bridge_enable_small_kernel(1)
+        check(Ya, gold, f"few-token cluster kernel fmt {fmt} M={M}", dev_gold=device_weight_gold(fmt, X, W, N))
+        check(Yb, gold, f"few-token persistent kernel fmt {fmt} M={M}")
+        assert np.abs(Ya.astype(np.float32) - Yb.astype(np.float32)).max() <= np.spacing(np.float16(np.abs(gold).max())).astype(np.float32)
+    # head-major output and a fused residual on the cluster kernel
+    M, D = 70, 64
+    X, W = o.baseline_inputs(fmt, M, K, 1024, 9)
+    Y = run_gemm(bridge, fmt, X, W, 1024, ex=True)
+    Yh = run_gemm(bridge, fmt, X, W, 1024, layout=1, H=1024 // D, D=D)
+    assert np.array_equal(Yh.view(np.uint16), Y.reshape(M, 1024 // D, D).transpose(1, 0, 2).copy().view(np.uint16))
+    R = o.RefLcg(4).activations(M, 1024)
+    Yr = run_gemm(bridge, fmt, X, W, 1024, residual=R)
+    check(Yr, o.gemm_f64(fmt, X, W, 1024) + R.astype(np.float64), f"few-token residual fmt {fmt}")
+
+
 def test_1b_reference_config_q4_0(bridge):
     # the CPU-reference configuration: M=33, K=N=2048, d ~ U(0.005, 0.02), X ~ N(0,1)
     X, W = o.baseline_inputs(o.Q4_0, 33, 2048, 2048, 42)

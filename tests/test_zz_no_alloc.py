@@ -25,7 +25,16 @@ def _call(br, fn, Xd, Wd, Yd, fmt, M, K, N):
     return rc
 
 
-def test_static_scratch_matches_regular_entry_point(bridge):
+@pytest.fixture(params=[1, 0], ids=["cluster-kernel", "split-k-scratch"])
+def few_token_path(request, bridge):
+    """Few-token shapes run on the cluster kernel by default (no scratch at all); with it switched off they take the
+    persistent kernel, whose split-K scratch is what this entry point keeps in the static array."""
+    bridge.lib.b200_bridge_enable_small_kernel(request.param)
+    yield request.param
+    bridge.lib.b200_bridge_enable_small_kernel(1)
+
+
+def test_static_scratch_matches_regular_entry_point(bridge, few_token_path):
     L = bridge.lib
     K = N = 4096
     first = None
@@ -47,7 +56,7 @@ def test_static_scratch_matches_regular_entry_point(bridge):
     assert np.array_equal(first.view(np.uint16), b.view(np.uint16))      # same inputs again: same bits
 
 
-def test_static_scratch_calls_leave_device_memory_alone(bridge):
+def test_static_scratch_calls_leave_device_memory_alone(bridge, few_token_path):
     """What the entry point is for: from the second call on (the first one may still make the driver load code), a
     call changes the amount of free device memory by nothing, whatever the split shape -- the regular entry point, by
     contrast, grows its scratch on demand.  cudaMemGetInfo is read straight from the runtime, with no torch
@@ -78,12 +87,12 @@ def test_static_scratch_calls_leave_device_memory_alone(bridge):
 
 def test_static_scratch_limits(bridge):
     L = bridge.lib
-    K = N = 4096
-    X = torch.zeros(256, K, dtype=torch.float16, device="cuda")
+    K, N = 4096, 2048
+    X = torch.zeros(512, K, dtype=torch.float16, device="cuda")
     W = torch.zeros(N * (K // 32) * 18, dtype=torch.uint8, device="cuda")
-    Y = torch.zeros(256, N, dtype=torch.float16, device="cuda")
-    # 256 tokens x 4096 outputs split four ways needs 4 Mi floats of scratch: over the 3 Mi limit
-    assert _call(bridge, L.b200_bridge_gemm_scratch_static, X, W, Y, 0, 256, K, N) == -7
+    Y = torch.zeros(512, N, dtype=torch.float16, device="cuda")
+    # 512 tokens x 2048 outputs are 32 tiles, split four ways: 4 Mi floats of scratch, over the 3 Mi limit
+    assert _call(bridge, L.b200_bridge_gemm_scratch_static, X, W, Y, 0, 512, K, N) == -7
     assert b"static array holds" in L.b200_bridge_last_error_string()
     # host memory would have to be staged, which needs an allocation: refused
     Xh = torch.zeros(33, K, dtype=torch.float16)
