@@ -142,8 +142,8 @@ int b200_bridge_clear_device_error(void);
 /* Testing hook: writes `value` into split-K tile counter `index` (what an aborted split-K launch leaves behind). */
 int b200_bridge_debug_set_tile_counter(uint32_t index, uint32_t value);
 void b200_bridge_force_generic(int on);
-/* Testing hook: 0 routes few-token projections (M <= 256 with fewer output tiles than SMs) to the persistent kernel and
- * its split-K scratch instead of the cluster kernel that is their default; != 0 restores the default. */
+/* Testing hook: 0 routes few-token projections (M <= 128 with fewer output tiles than SMs) to the persistent kernel
+ * instead of the cluster kernel that is their default; != 0 restores the default. */
 void b200_bridge_enable_small_kernel(int on);
 /* Up to three projections of the same activations in one launch (the Q, K and V projections of a layer): Y[i] =
  * X . W[i]^T with W[i] packed [N[i]][K/blk] in `format`, outputs in `layout` (LAYOUT_DIRECT_HEAD: [N[i]/D][M][D]).

@@ -1342,7 +1342,9 @@ bool fast_path_ok(const GemmArgs& a) {
 }
 
 size_t workspace_floats(const GemmArgs& a) {
-    if (gemv_path_ok(a) || small_path_ok(a) || !fast_path_ok(a)) return 0;
+    if (gemv_path_ok(a)) return 0;
+    if (small_path_ok(a)) return small_scratch_floats(a);
+    if (!fast_path_ok(a)) return 0;
     const Plan pl = make_plan(a);
     if (pl.k_splits <= 1) return 0;
     return (size_t)pl.k_splits * pl.n_tok_tiles * pl.n_w_tiles * pl.T * W_TILE;
@@ -1351,7 +1353,7 @@ size_t workspace_floats(const GemmArgs& a) {
 cudaError_t launch(const GemmArgs& a, const Workspace& ws, cudaStream_t stream) {
     g_last_launches = 1;
     if (gemv_path_ok(a)) return launch_gemv(a, stream);
-    if (small_path_ok(a)) return launch_small(a, ws.err, stream);
+    if (small_path_ok(a)) return launch_small(a, ws, stream);
     if (fast_path_ok(a)) return dispatch_fast(a, ws, stream);
     if (a.scatter.world || a.n_extra) return cudaErrorInvalidValue;   // fused reduce-scatter and grouped launches exist on the tensor-core path only
     Params p;

@@ -67,9 +67,10 @@ bool gemv_path_ok(const GemmArgs& a);
 cudaError_t launch_gemv(const GemmArgs& a, cudaStream_t stream);
 cudaError_t launch(const GemmArgs& a, const Workspace& ws, cudaStream_t stream);
 // Few-token path (qgemm_small.cu): weights unpacked straight into tensor memory, K split across a thread-block cluster whose
-// partial tiles meet in distributed shared memory.  Taken for M <= 256 where the persistent kernel would leave SMs idle.
+// CTAs share out the sum of the partial tiles.  Taken for M <= 128 where the persistent kernel would leave SMs idle.
 bool small_path_ok(const GemmArgs& a);
-cudaError_t launch_small(const GemmArgs& a, int* err, cudaStream_t stream);
+size_t small_scratch_floats(const GemmArgs& a);
+cudaError_t launch_small(const GemmArgs& a, const Workspace& ws, cudaStream_t stream);
 void set_small_kernel_enabled(bool on);      // testing hook: off routes those shapes to the persistent kernel again
 // Number of kernels the last launch() enqueued (1, or 2 with the generic tail) -- for launch accounting.
 int last_launch_count();

@@ -1,5 +1,5 @@
-// Few-token projection: Y[m][n] = sum_k X[m][k] * dequant(W)[n][k] for token counts where one launch has too few
-// output tiles to fill the GPU (the decode-like shapes M = 33 / 128 / 129 of the router sweep,
+// Few-token projection: Y[m][n] = sum_k X[m][k] * dequant(W)[n][k] for up to 128 tokens where one launch has too few
+// output tiles to fill the GPU (the decode-like shapes M = 33 / 127 / 128 of the router sweep,
 // bench_universal_router.mm:764-773, and every projection of a short prefill).  HBM-bound: the packed weights are
 // read once, so what matters is how fast an SM turns packed bytes into MMA operands.
 //
@@ -10,12 +10,14 @@
 //     shared memory.  That removes the 16 KB store + 16 KB operand read per 64-element step that bound the other kernel;
 //   * small CTAs (4 unpack warps = the 4 lane quadrants, a copy warp, an MMA warp; <= 100 KB of shared memory, 256
 //     tensor-memory columns) so that two CTAs share an SM and one's copies and unpacking overlap the other's;
-//   * one work item per CTA: K is split up to eight ways, the splits of a tile form a thread-block cluster, and the
-//     partial tiles meet in distributed shared memory (each CTA of the cluster sums one slice of the token columns in
-//     split order -- deterministic -- and writes fp16 Y): no scratch buffer in global memory, no counters.
+//   * one work item per CTA: K is split up to eight ways and the splits of a tile form a thread-block cluster.  Every CTA
+//     writes its partial tile to a scratch buffer (which stays in L2), one cluster barrier later each CTA of the cluster
+//     sums one slice of the token columns in split order -- deterministic -- and writes fp16 Y: no counters, no CTA that
+//     has to add everything alone.  (Passing the partial tiles through distributed shared memory instead measured
+//     slower: remote shared-memory stores ran at about 10 bytes per clock per SM.)
 //
-// Every mbarrier wait is bounded (ptx::mbar_wait).  The two cluster barriers are hardware barriers: every thread of
-// every CTA reaches them on every path, including after a wait has given up.
+// Every mbarrier wait is bounded (ptx::mbar_wait).  The cluster barrier is a hardware barrier: every thread of every
+// CTA reaches it on every path, including after a wait has given up.
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -38,8 +40,19 @@ constexpr int A_COLS = KSTEP / 2;    // fp16 pairs: 32 columns per stage
 constexpr int ACC_COL = A_STAGES * A_COLS;   // accumulator behind the A ring (columns 128 ..)
 constexpr int TMEM_COLS = 256;
 constexpr int RAW_STAGES = 2, B_STAGES = 4;
-constexpr int THREADS = 192;         // warps 0-3 unpack + epilogue, warp 4 copies, warp 5 issues MMAs
+constexpr int UNPACK_WARPS = 4;      // one per lane quadrant (a second group of four measured slower: 2080 against 550 cycles per sub-tile)
+constexpr int THREADS = (UNPACK_WARPS + 2) * 32;    // warps 0-3 unpack + epilogue, warp 4 copies, warp 5 issues MMAs
+constexpr int COPY_WARP = UNPACK_WARPS, MMA_WARP = UNPACK_WARPS + 1;
 constexpr int MAX_T = 128;
+
+// Development aid: with -DQS_TRACE the first CTA records clock64() stamps at its synchronisation points into a device
+// array that b200_debug_small_trace copies out.  Compiled out otherwise.
+#ifdef QS_TRACE
+__device__ unsigned long long g_qs_trace[8][64];
+#define QST(role, slot) do { if (blockIdx.x == QS_TRACE && (slot) < 64) g_qs_trace[role][slot] = clock64(); } while (0)
+#else
+#define QST(role, slot) do { } while (0)
+#endif
 
 struct Params {
     uint32_t M, N, K, T;
@@ -48,6 +61,7 @@ struct Params {
     const __half* residual;
     uint32_t layout, D;
     int* err;
+    float* scratch;              // [k_splits][tiles][T][128] partial tiles (k_splits > 1)
     const uint8_t* meta0;
     const __half* row_scale0;
 };
@@ -75,16 +89,6 @@ __device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// address of `local` (a shared-memory address of this CTA) in the shared memory of CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-
 template <int W, int HI>
 __device__ __forceinline__ void ld_words(const uint8_t* rowp, uint32_t* r) {
     if constexpr (W < HI) {
@@ -116,6 +120,7 @@ qgemm_small_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     static_assert(!Cd::RAW_SWIZZLE_128 && Cd::META_WORDS == 0, "planar layouts with side planes stay on the persistent kernel");
 
     extern __shared__ uint8_t smem_dyn[];
+    ptx::launch_dependents();     // the next kernel in the stream may set itself up while this grid runs
     const uint32_t pad = (1024u - (ptx::smem_u32(smem_dyn) & 1023u)) & 1023u;
     uint8_t* sB = smem_dyn + pad;                                   // [B_STAGES][T rows of 128 bytes], 128-byte swizzle
     const uint32_t b_stage_bytes = p.T * 128u;
@@ -130,8 +135,7 @@ qgemm_small_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     uint64_t* acc_full = b_empty + B_STAGES;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_full + 1);
     volatile uint32_t* abort_flag = tmem_holder + 1;
-    // after the main loop the activation and packed rings are idle: the cluster's partial tiles land there
-    float* recv = reinterpret_cast<float*>(sB);                     // [k_splits][T / k_splits token columns][128 features]
+
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t ks = blockIdx.x % p.k_splits;                    // == rank inside the cluster
@@ -140,34 +144,50 @@ qgemm_small_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     const uint32_t ksteps = p.kchunks * (uint32_t)SUBS;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < RAW_STAGES; i++) { ptx::mbar_init(&raw_full[i], 1); ptx::mbar_init(&raw_empty[i], 4); }
+        for (int i = 0; i < RAW_STAGES; i++) { ptx::mbar_init(&raw_full[i], 1); ptx::mbar_init(&raw_empty[i], UNPACK_WARPS); }
         for (int i = 0; i < A_STAGES; i++) { ptx::mbar_init(&a_full[i], 4); ptx::mbar_init(&a_empty[i], 1); }
         for (int i = 0; i < B_STAGES; i++) { ptx::mbar_init(&b_full[i], 1); ptx::mbar_init(&b_empty[i], 1); }
         ptx::mbar_init(acc_full, 1);
         *abort_flag = 0u;
         ptx::fence_barrier_init();
     }
-    if (warp == 5) { ptx::tmem_alloc(tmem_holder, TMEM_COLS); ptx::tmem_relinquish(); }
+    if (threadIdx.x == 0) QST(0, 0);
+    if (warp == MMA_WARP) { ptx::tmem_alloc(tmem_holder, TMEM_COLS); ptx::tmem_relinquish(); }
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if (threadIdx.x == 0) QST(0, 1);
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    // everything above touched only this CTA's shared and tensor memory; global memory is first touched below
+    ptx::grid_dependency_wait();
+    if (threadIdx.x == 0) QST(0, 2);
 
-    if (warp == 4) {
-        // ---------------- copies: packed weight chunks and activation tiles, interleaved in consumption order ----------------
+    if (warp == COPY_WARP) {
+        // ---------------- copies: packed weight chunks run ahead of the activation tiles ----------------
+        // (the packed bytes are what the launch waits for: every chunk that has a free stage is requested before the
+        // activation tiles of the chunk in front of it)
         if (lane == 0) { ptx::prefetch_tensormap(&tmW); ptx::prefetch_tensormap(&tmX); }
-        uint32_t rs = 0, rph = 0, bs = 0, bph = 0;
+        uint32_t rs = 0, rph = 0, bs = 0, bph = 0, raw_next = 0;
         bool ok = true;
-        for (uint32_t kc = 0; ok && kc < p.kchunks; kc++) {
-            ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&raw_empty[rs], rph ^ 1u, abort_flag, p.err, 111));
-            if (!ok) break;
+        auto issue_raw = [&](bool block) {       // request chunk raw_next if its stage is free (block: wait for it)
+            if (raw_next >= p.kchunks) return;
+            bool free_now = ptx::mbar_try_wait(&raw_empty[rs], rph ^ 1u);
+            if (!free_now && block) free_now = ptx::mbar_wait<32>(&raw_empty[rs], rph ^ 1u, abort_flag, p.err, 111);
+            free_now = __all_sync(0xffffffffu, free_now);
+            if (!free_now) { if (block) ok = false; return; }
             if (lane == 0) {
+                QST(1, raw_next);
                 ptx::mbar_arrive_expect_tx(&raw_full[rs], RAW_TILE_BYTES);
                 ptx::tma_load_2d(sRaw + rs * RAW_TILE_BYTES, &tmW, &raw_full[rs],
-                                 (int)((ks * p.kchunks + kc) * (ROW_BYTES / Cd::TMA_ELEM_BYTES)), (int)(wt * W_TILE));
+                                 (int)((ks * p.kchunks + raw_next) * (ROW_BYTES / Cd::TMA_ELEM_BYTES)), (int)(wt * W_TILE));
             }
             __syncwarp();
+            raw_next++;
             if (++rs == RAW_STAGES) { rs = 0; rph ^= 1u; }
+        };
+        for (int i = 0; i < RAW_STAGES; i++) issue_raw(false);
+        for (uint32_t kc = 0; ok && kc < p.kchunks; kc++) {
+            if (raw_next <= kc) issue_raw(true);              // the chunk these activation tiles belong to must be on its way
             for (uint32_t s = 0; ok && s < (uint32_t)SUBS; s++) {
                 ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&b_empty[bs], bph ^ 1u, abort_flag, p.err, 112));
                 if (!ok) break;
@@ -178,9 +198,10 @@ qgemm_small_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                 }
                 __syncwarp();
                 if (++bs == B_STAGES) { bs = 0; bph ^= 1u; }
+                issue_raw(false);                             // a packed stage may have been released meanwhile
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == MMA_WARP) {
         // ---------------- MMA issuer ----------------
         const uint32_t idesc = ptx::umma_idesc_f16(W_TILE, p.T);
         const uint64_t desc_hi = ptx::umma_desc_k_sw128(0u);
@@ -192,6 +213,7 @@ qgemm_small_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                                              ptx::mbar_wait(&b_full[bs], bph, abort_flag, p.err, 114));
             if (!ok) break;
             ptx::tc_fence_after_sync();
+            if (lane == 0) QST(2, st);
             if (ptx::elect_one()) {
                 const uint64_t bdesc = desc_hi | (uint64_t)(b_lo0 + bs * (b_stage_bytes >> 4));
                 const uint32_t acol = tmem_base + as * A_COLS;
@@ -209,18 +231,22 @@ qgemm_small_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         __syncwarp();
     } else {
         // ---------------- unpack: packed bytes -> registers -> tensor memory (A operand) ----------------
-        const uint32_t row = warp * 32u + lane;                     // weight row of the tile = tensor-memory lane
-        const uint32_t lane_base = (warp * 32u) << 16;
-        uint32_t rs = 0, rph = 0, as = 0, aph = 0;
+        const uint32_t quad = warp & 3u;                            // lane quadrant
+        const uint32_t row = quad * 32u + lane;                     // weight row of the tile = tensor-memory lane
+        const uint32_t lane_base = (quad * 32u) << 16;
+        uint32_t rs = 0, rph = 0;
         bool ok = true;
         for (uint32_t kc = 0; ok && kc < p.kchunks; kc++) {
             ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&raw_full[rs], rph, abort_flag, p.err, 115));
             if (!ok) break;
+            if (threadIdx.x == 0) QST(3, kc);
             uint32_t r[ROW_BYTES / 4];
             const uint8_t* rowp = sRaw + rs * RAW_TILE_BYTES + row * ROW_BYTES;
             ld_words<0, Cd::HDR_WORDS>(rowp, r);
             auto sub_tile = [&](auto S) {
                 constexpr int s = decltype(S)::value;
+                // step of this CTA, its stage of the A ring and the parity of that stage's use
+                const uint32_t step = kc * (uint32_t)SUBS + (uint32_t)s, as = step % A_STAGES, aph = (step / A_STAGES) & 1u;
                 uint32_t o[32];
                 ld_words<Cd::sub_lo(s), Cd::sub_hi(s)>(rowp, r);
                 Cd::dequant64(r, s, o, nullptr);
@@ -232,8 +258,8 @@ qgemm_small_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                     ptx::tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(&a_full[as]);
+                    if (threadIdx.x == 0) QST(4, step);
                 }
-                if (++as == A_STAGES) { as = 0; aph ^= 1u; }
             };
             for_each_sub(sub_tile, std::make_integer_sequence<int, SUBS>{});
             __syncwarp();
@@ -242,16 +268,16 @@ qgemm_small_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         }
     }
 
-    // ---------------- partial tiles meet in the cluster's shared memory ----------------
-    // (1) every CTA of the cluster has finished its main loop: its rings may be overwritten
+    // ---------------- partial tiles meet in the scratch buffer, the cluster shares out the sums ----------------
     if (warp < 4) {
-        // the accumulator is complete once every MMA has; a failed wait sets the abort flag, the barriers are still reached
+        // the accumulator is complete once every MMA has; a failed wait sets the abort flag, the barrier is still reached
         ptx::mbar_wait<64>(acc_full, 0u, abort_flag, p.err, 117);
     }
     __syncthreads();
+    if (threadIdx.x == 0) QST(0, 3);
     const bool bad = *abort_flag != 0u;
-    cluster_sync_all();
-    const uint32_t cols = p.T / p.k_splits;                         // token columns each CTA of the cluster finishes
+    const uint32_t n_tiles = p.n_w_tiles * p.n_tok_tiles;
+    const size_t tile_floats = (size_t)p.T * W_TILE;
     if (warp < 4 && !bad) {
         ptx::tc_fence_after_sync();
         const uint32_t f = warp * 32u + lane;                       // feature row of the tile
@@ -259,47 +285,68 @@ qgemm_small_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         float rsc = 1.0f;
         if (Cd::ROW_SCALE) rsc = n < p.N ? __half2float(p.row_scale0[n]) : 0.0f;
         const uint32_t taddr = tmem_base + ((warp * 32u) << 16) + ACC_COL;
-        const uint32_t my_slot = ptx::smem_u32(recv) + (ks * cols * W_TILE + f) * 4u;     // [ks][col][f] in the owner's buffer
-        for (uint32_t c0 = 0; c0 < p.T; c0 += 16) {
-            uint32_t v[16];
-            ptx::tmem_ld_x16(taddr + c0, v);
-            ptx::tmem_ld_wait();
+        if (p.k_splits > 1u) {
+            // [split][tile][token column][feature]: a warp's store covers 32 consecutive features of one column
+            float* dst = p.scratch + ((size_t)ks * n_tiles + tile) * tile_floats + f;
+            for (uint32_t c0 = 0; c0 < p.T; c0 += 16) {
+                uint32_t v[16];
+                ptx::tmem_ld_x16(taddr + c0, v);
+                ptx::tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                const uint32_t c = c0 + j, owner = c / cols, cl = c - owner * cols;
-                const float x = Cd::ROW_SCALE ? __uint_as_float(v[j]) * rsc : __uint_as_float(v[j]);
-                st_cluster_f32(map_to_rank(my_slot + cl * W_TILE * 4u, owner), x);
+                for (int j = 0; j < 16; j++)
+                    __stcg(dst + (size_t)(c0 + j) * W_TILE, Cd::ROW_SCALE ? __uint_as_float(v[j]) * rsc : __uint_as_float(v[j]));
+            }
+        } else {
+            // no split: this CTA's accumulator is the result
+            const uint32_t tok0 = tt * p.T;
+            for (uint32_t c0 = 0; c0 < p.T; c0 += 16) {
+                uint32_t v[16];
+                ptx::tmem_ld_x16(taddr + c0, v);
+                ptx::tmem_ld_wait();
+                if (n >= p.N) continue;
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const uint32_t tok = tok0 + c0 + j;
+                    if (tok >= p.M) break;
+                    float a = Cd::ROW_SCALE ? __uint_as_float(v[j]) * rsc : __uint_as_float(v[j]);
+                    const size_t o = p.layout == 1 ? ((size_t)(n / p.D) * p.M + tok) * p.D + (n % p.D) : (size_t)tok * p.N + n;
+                    if (p.residual) a += __half2float(p.residual[o]);
+                    p.Y[o] = __float2half_rn(a);
+                }
             }
         }
     }
-    // (2) every partial value has landed
+    if (threadIdx.x == 0) QST(0, 5);
+    // every partial tile of the cluster is written (release / acquire at cluster scope covers the global stores)
     cluster_sync_all();
-    if (!bad) {
+    if (threadIdx.x == 0) QST(0, 6);
+    if (!bad && p.k_splits > 1u) {
         // this CTA's token columns [ks * cols, (ks + 1) * cols): sum over the splits in split order, write fp16
+        const uint32_t cols = p.T / p.k_splits;
+        const float* base = p.scratch + (size_t)tile * tile_floats + (size_t)(ks * cols) * W_TILE;
+        const size_t split_stride = (size_t)n_tiles * tile_floats;
         const uint32_t tok0 = tt * p.T + ks * cols;
-        for (uint32_t i = threadIdx.x; i < cols * (W_TILE / 2); i += THREADS) {
-            const uint32_t cl = i / (W_TILE / 2), f = (i % (W_TILE / 2)) * 2u;
+        for (uint32_t i = threadIdx.x; i < cols * (W_TILE / 4); i += THREADS) {
+            const uint32_t cl = i / (W_TILE / 4), f = (i % (W_TILE / 4)) * 4u;
             const uint32_t tok = tok0 + cl, n = wt * W_TILE + f;
             if (tok >= p.M || n >= p.N) continue;
-            float a0 = 0.0f, a1 = 0.0f;
-            for (uint32_t s = 0; s < p.k_splits; s++) {
-                const float2 v = *reinterpret_cast<const float2*>(recv + (s * cols + cl) * W_TILE + f);
-                a0 += v.x; a1 += v.y;
+            float4 acc = __ldcg(reinterpret_cast<const float4*>(base + (size_t)cl * W_TILE + f));
+            for (uint32_t s = 1; s < p.k_splits; s++) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(base + s * split_stride + (size_t)cl * W_TILE + f));
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
             }
-            const bool pair = n + 1u < p.N;
-            if (p.layout == 1) {
-                const size_t o = ((size_t)(n / p.D) * p.M + tok) * p.D + (n % p.D);          // D is even: the pair stays in one head
-                if (pair) *reinterpret_cast<__half2*>(p.Y + o) = __floats2half2_rn(a0, a1);
-                else p.Y[o] = __float2half_rn(a0);
-            } else {
-                const size_t o = (size_t)tok * p.N + n;
-                if (p.residual) { a0 += __half2float(p.residual[o]); if (pair) a1 += __half2float(p.residual[o + 1]); }
-                if (pair && (p.N % 2u == 0u)) *reinterpret_cast<__half2*>(p.Y + o) = __floats2half2_rn(a0, a1);
-                else { p.Y[o] = __float2half_rn(a0); if (pair) p.Y[o + 1] = __float2half_rn(a1); }
+            float a[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                if (n + e >= p.N) break;
+                const size_t o = p.layout == 1 ? ((size_t)((n + e) / p.D) * p.M + tok) * p.D + ((n + e) % p.D) : (size_t)tok * p.N + n + e;
+                if (p.residual) a[e] += __half2float(p.residual[o]);
+                p.Y[o] = __float2half_rn(a[e]);
             }
         }
     }
     // ---------------- teardown ----------------
+    if (threadIdx.x == 0) QST(0, 7);
     ptx::tc_fence_before_sync();
     __syncthreads();
     if (bad) {      // let copies that are still in flight land before the CTA gives its shared memory back
@@ -307,9 +354,8 @@ qgemm_small_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         while (clock64() - t0 < 4000000LL) { }
         __syncthreads();
     }
-    if (warp == 5) { ptx::tc_fence_after_sync(); ptx::tmem_dealloc(tmem_base, TMEM_COLS); }
-    // no CTA of the cluster leaves while another may still read its shared memory (all reads precede this point)
-    cluster_sync_all();
+    if (warp == MMA_WARP) { ptx::tc_fence_after_sync(); ptx::tmem_dealloc(tmem_base, TMEM_COLS); }
+    if (threadIdx.x == 0) QST(0, 8);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -344,6 +390,7 @@ bool make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, uint64_t 
 
 struct Plan { uint32_t T, n_tok_tiles, n_w_tiles, k_splits, kchunks; size_t smem; };
 
+// alignment slack + activation ring + packed ring + barrier block
 template <int FMT> size_t smem_bytes(uint32_t T) {
     return 1024 + (size_t)B_STAGES * T * 128 + (size_t)RAW_STAGES * cdc::Codec<FMT>::ROW_BYTES * W_TILE + 256;
 }
@@ -370,16 +417,25 @@ template <int FMT> bool make_plan(const GemmArgs& a, Plan& pl) {
         pl.k_splits = s;
     }
     pl.kchunks = chunks / pl.k_splits;
+    // at least 80 KB, so that no more than two CTAs share an SM: each holds 256 of the SM's 512 tensor-memory columns, and a
+    // third CTA would sit in tcgen05.alloc until one of the others leaves
     pl.smem = smem_bytes<FMT>(pl.T);
-    // the cluster's receive buffer ([T][128] floats) lies over the activation and packed rings
-    const size_t rings = (size_t)B_STAGES * pl.T * 128 + (size_t)RAW_STAGES * Cd::ROW_BYTES * W_TILE;
-    return (size_t)pl.T * W_TILE * 4 <= rings && tiles * pl.k_splits <= 65535u * 8u;
+    if (pl.smem < 80 * 1024) pl.smem = 80 * 1024;
+    return tiles * pl.k_splits <= 65535u * 8u;
 }
 
-template <int FMT> cudaError_t launch_fmt(const GemmArgs& a, int* err, cudaStream_t stream) {
+template <int FMT> size_t scratch_floats_fmt(const GemmArgs& a) {
+    Plan pl;
+    if (!make_plan<FMT>(a, pl) || pl.k_splits <= 1) return 0;
+    return (size_t)pl.k_splits * pl.n_tok_tiles * pl.n_w_tiles * pl.T * W_TILE;
+}
+
+template <int FMT> cudaError_t launch_fmt(const GemmArgs& a, const Workspace& ws, cudaStream_t stream) {
     using Cd = cdc::Codec<FMT>;
     Plan pl;
     if (!make_plan<FMT>(a, pl)) return cudaErrorInvalidValue;
+    if (pl.k_splits > 1 && (!ws.partial || ws.partial_floats < (size_t)pl.k_splits * pl.n_tok_tiles * pl.n_w_tiles * pl.T * W_TILE))
+        return cudaErrorInvalidValue;
     const uint64_t w_row_bytes = (uint64_t)(a.K / Cd::CHUNK) * Cd::ROW_BYTES;
     CUtensorMap tmX, tmW;
     if (!make_map(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a.X, a.K, a.M, (uint64_t)a.K * 2, KSTEP, pl.T, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -392,7 +448,7 @@ template <int FMT> cudaError_t launch_fmt(const GemmArgs& a, int* err, cudaStrea
     p.M = a.M; p.N = a.N; p.K = a.K; p.T = pl.T;
     p.n_tok_tiles = pl.n_tok_tiles; p.n_w_tiles = pl.n_w_tiles; p.k_splits = pl.k_splits; p.kchunks = pl.kchunks;
     p.Y = (__half*)a.Y; p.residual = (const __half*)a.residual; p.layout = (uint32_t)a.layout; p.D = a.D ? a.D : 2;
-    p.err = err;
+    p.err = ws.err; p.scratch = ws.partial;
     p.meta0 = (const uint8_t*)a.W0 + (size_t)a.N * w_row_bytes;
     p.row_scale0 = (const __half*)p.meta0;
     static uint64_t attr_mask = 0;
@@ -413,10 +469,12 @@ template <int FMT> cudaError_t launch_fmt(const GemmArgs& a, int* err, cudaStrea
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = pl.smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = pl.k_splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;      // prologue may overlap the previous kernel's tail
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 2;
     return cudaLaunchKernelEx(&cfg, qgemm_small_kernel<FMT>, tmX, tmW, p);
 }
 
@@ -426,6 +484,12 @@ bool g_enabled = true;
 }  // namespace small
 
 void set_small_kernel_enabled(bool on) { small::g_enabled = on; }
+
+#ifdef QS_TRACE
+extern "C" int b200_debug_small_trace(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, small::g_qs_trace, sizeof(small::g_qs_trace)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 bool small_path_ok(const GemmArgs& a) {
     if (!small::g_enabled || a.force_generic) return false;
@@ -447,21 +511,31 @@ bool small_path_ok(const GemmArgs& a) {
     int dev = 0, n_sm = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-    return a.M <= 256u && big_tiles < (uint32_t)n_sm;
+    // (one token tile of up to 128 tokens: with two, every weight tile would be unpacked twice)
+    return a.M <= (uint32_t)small::MAX_T && big_tiles < (uint32_t)n_sm;
 }
 
-cudaError_t launch_small(const GemmArgs& a, int* err, cudaStream_t stream) {
-    switch (a.format) {
-        case QUANT_Q4_0: return small::launch_fmt<QUANT_Q4_0>(a, err, stream);
-        case QUANT_MLX_4BIT: return small::launch_fmt<QUANT_MLX_4BIT>(a, err, stream);
-        case QUANT_Q4_K: return small::launch_fmt<QUANT_Q4_K>(a, err, stream);
-        case QUANT_TERNARY_1_58: return small::launch_fmt<QUANT_TERNARY_1_58>(a, err, stream);
-        case QUANT_VAR_RATE_AFFINE: return small::launch_fmt<QUANT_VAR_RATE_AFFINE>(a, err, stream);
-        case QUANT_EXL3: return small::launch_fmt<QUANT_EXL3>(a, err, stream);
-        case QUANT_TERNARY_ROW: return small::launch_fmt<QUANT_TERNARY_ROW>(a, err, stream);
-        case QUANT_PRISM_Q2_0: return small::launch_fmt<QUANT_PRISM_Q2_0>(a, err, stream);
-        default: return cudaErrorInvalidValue;
+#define QG_SMALL_DISPATCH(EXPR)                                                            \
+    switch (a.format) {                                                                    \
+        case QUANT_Q4_0: { constexpr int F = QUANT_Q4_0; return EXPR; }                    \
+        case QUANT_MLX_4BIT: { constexpr int F = QUANT_MLX_4BIT; return EXPR; }            \
+        case QUANT_Q4_K: { constexpr int F = QUANT_Q4_K; return EXPR; }                    \
+        case QUANT_TERNARY_1_58: { constexpr int F = QUANT_TERNARY_1_58; return EXPR; }    \
+        case QUANT_VAR_RATE_AFFINE: { constexpr int F = QUANT_VAR_RATE_AFFINE; return EXPR; } \
+        case QUANT_EXL3: { constexpr int F = QUANT_EXL3; return EXPR; }                    \
+        case QUANT_TERNARY_ROW: { constexpr int F = QUANT_TERNARY_ROW; return EXPR; }      \
+        case QUANT_PRISM_Q2_0: { constexpr int F = QUANT_PRISM_Q2_0; return EXPR; }        \
+        default: break;                                                                    \
     }
+
+cudaError_t launch_small(const GemmArgs& a, const Workspace& ws, cudaStream_t stream) {
+    QG_SMALL_DISPATCH(small::launch_fmt<F>(a, ws, stream))
+    return cudaErrorInvalidValue;
+}
+
+size_t small_scratch_floats(const GemmArgs& a) {
+    QG_SMALL_DISPATCH(small::scratch_floats_fmt<F>(a))
+    return 0;
 }
 
 }  // namespace qg

@@ -47,15 +47,17 @@ def strict_bound(gold64: np.ndarray) -> np.ndarray:
     return np.maximum(TOL, ulp)
 
 
-def tolerance(gold64: np.ndarray) -> np.ndarray:
+def tolerance(gold64: np.ndarray, rms_factor: float = 1.0) -> np.ndarray:
     """Pass line for fp16 outputs against the double-precision gold:
         |diff| <= max(1/128, ulp_fp16(gold), 2^-9 * rms(gold)).
     1/128 is the reference's tolerance on its own test distribution (output rms about 1); one fp16 ulp
     covers outputs above 8 where the fp16 grid itself is coarser than 1/128; the rms term scales the
     bound with the output magnitude for the heavier benchmark distributions (fp16 weights carry a relative
-    rounding error of 2^-11 each, which a K = 4096 contraction turns into about 2^-11 * rms(y) of noise)."""
+    rounding error of 2^-11 each, which a K = 4096 contraction turns into about 2^-11 * rms(y) of noise).  rms_factor
+    widens that term for codecs whose fp16 weight is built from several rounded terms (the variable-rate affine codec
+    rounds its sub-scale, its sub-bias and their multiply-add: three roundings per weight instead of one)."""
     rms = float(np.sqrt(np.mean(gold64 ** 2)))
-    return np.maximum(strict_bound(gold64), 2.0 ** -9 * rms)
+    return np.maximum(strict_bound(gold64), rms_factor * 2.0 ** -9 * rms)
 
 
 def parity_stats(Y, gold64, what="") -> dict:
@@ -100,7 +102,7 @@ def device_weight_gold(fmt, X, W, N):
     return Y
 
 
-def check(Y, gold64, what="", dev_gold=None):
+def check(Y, gold64, what="", dev_gold=None, rms_factor=1.0):
     """Pass line: every output within tolerance() of the oracle's double-precision gold.  With `dev_gold` (see
     device_weight_gold) the strict criterion max(1/128, 1 ulp) must hold against it with no exception, which shows
     that anything the rms term of the pass line covers is fp16 weight rounding, not a defect of the kernel.  The
@@ -112,7 +114,7 @@ def check(Y, gold64, what="", dev_gold=None):
         sd = parity_stats(Y, dev_gold, what)
         st["vs_device_weights"] = {"max_abs": sd["max_abs"], "over_strict": sd["over_strict"], "max_over_factor": sd["max_over_factor"]}
     PARITY_REPORT.append(st)
-    tol = tolerance(gold64)
+    tol = tolerance(gold64, rms_factor)
     bad = diff > tol
     assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} outputs over tolerance, max-abs {diff.max():.5f}"
     if dev_gold is not None:
