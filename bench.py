@@ -55,7 +55,7 @@ M, K, N = 2048, 4096, 4096
 FLOPS_PER_STEP = 2.0 * M * N * K
 BLOCKS = 5
 FORMATS = {"q4_0": 0, "mlx_4bit": 1, "q4_k": 2, "ternary_1_58": 3, "var_rate_affine": 4, "exl3": 5, "prism_q2_0": 7,
-           "mlx_4bit_g64": 100, "ternary_row": 101}
+           "mlx_4bit_g64": 100, "ternary_row": 101, "mlx_4bit_planar": 102}
 FMT_NAME = {v: k for k, v in FORMATS.items()}
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, only for the (format, M) pairs that have a committed
 # ncu summary (K = N = 4096); every other row reports traffic null
@@ -246,6 +246,10 @@ def synth_w(fmt: int, k: int, n: int, rng) -> np.ndarray:
         sc = rng.uniform(0.005, 0.02, n * k // 64)
         W = np.concatenate([rng.integers(0, 256, n * k // 2, dtype=np.uint8), f16(sc).reshape(-1),
                             f16(-8.0 * sc + rng.uniform(-0.01, 0.01, sc.size)).reshape(-1)])
+    elif fmt == 102:     # the reference's planar MLX group 32: 16 nibble bytes per block, then fp16 scales, then fp16 biases
+        sc = rng.uniform(0.005, 0.02, n * k // 32)       # (n * k / 32 blocks; the planes are 16-byte multiples whenever k % 256 == 0)
+        W = np.concatenate([rng.integers(0, 256, n * k // 2, dtype=np.uint8), f16(sc).reshape(-1),
+                            f16(-8.0 * sc + rng.uniform(-0.01, 0.01, sc.size)).reshape(-1)])
     elif fmt == 101:     # planar ternary: [n][k/16] u32 of 2-bit codes, then one fp16 absmean scale per row
         codes = rng.choice(np.array([0, 1, 2], dtype=np.uint32), size=(n * k // 16, 16), p=[0.25, 0.5, 0.25])
         words = (codes << (2 * np.arange(16, dtype=np.uint32))).sum(axis=1, dtype=np.uint32)
@@ -412,7 +416,7 @@ def run_sweep(br, steps: int) -> list:
     for f in ("q4_0", "mlx_4bit_g64"):
         for m in (33, 128, 129, 2048):
             cases.append((f, m, 4096, 4096, False, f"{f} projection M={m} K=N=4096"))
-    for f in ("mlx_4bit", "q4_k", "ternary_1_58", "var_rate_affine", "exl3", "ternary_row", "prism_q2_0"):
+    for f in ("mlx_4bit", "mlx_4bit_planar", "q4_k", "ternary_1_58", "var_rate_affine", "exl3", "ternary_row", "prism_q2_0"):
         cases.append((f, 2048, 4096, 4096, False, f"{f} projection M=2048 K=N=4096"))
     cases.append(("q4_k", 2048, 4096, 14336, True, "q4_k fused gate/up SwiGLU M=2048 K=4096 F=14336"))
     cases.append(("q4_k", 2048, 14336, 4096, False, "q4_k down projection M=2048 K=14336 N=4096"))

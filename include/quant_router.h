@@ -32,6 +32,9 @@ enum QuantFormat : int {
     // extensions (no counterpart in the reference)
     QUANT_MLX_4BIT_G64    = 100, // planar: u32 qs[N][K/8] | half scales[N][K/64] | half biases[N][K/64]
     QUANT_TERNARY_ROW     = 101, // planar: u32 qs[N][K/16] | half row_scale[N]
+    QUANT_MLX_4BIT_PLANAR = 102, // planar, group 32 (unified_multi_scale_kernels.metal:17-31, packer bench_all_scales.mm:62-95):
+                                 // u8 qs[N*K/32][16] | half scales[N*K/32] | half biases[N*K/32], each plane 16-byte aligned;
+                                 // byte j of a block: low nibble = element j, high nibble = element j + 16
     QUANT_CUSTOM          = 99
 };
 
@@ -98,6 +101,10 @@ inline size_t compute_quant_weight_bytes(QuantFormat fmt, size_t total_elements)
 inline size_t compute_quant_matrix_bytes(QuantFormat fmt, size_t K, size_t N) {
     if (fmt == QUANT_MLX_4BIT_G64) return N * (K / 8) * 4 + 2 * N * (K / 64) * 2;
     if (fmt == QUANT_TERNARY_ROW)  return N * (K / 16) * 4 + N * 2;
+    if (fmt == QUANT_MLX_4BIT_PLANAR) {          // the reference's mlx_4bit_buffer_size(): planes padded to 16 bytes
+        const size_t blocks = N * (K / 32), scales_off = (blocks * 16 + 15) & ~(size_t)15;
+        return ((scales_off + blocks * 2 + 15) & ~(size_t)15) + blocks * 2;
+    }
     QuantFormatInfo info = get_quant_info(fmt);
     if (info.block_bytes == 0) return 0;
     return N * (K / info.block_size) * (size_t)info.block_bytes;

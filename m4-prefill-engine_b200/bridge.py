@@ -30,6 +30,7 @@ class QuantFormat(IntEnum):
     # extension layouts of this library
     QUANT_MLX_4BIT_G64 = 100
     QUANT_TERNARY_ROW = 101
+    QUANT_MLX_4BIT_PLANAR = 102
 
 
 def library_path() -> Path:

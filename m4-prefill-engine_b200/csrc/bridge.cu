@@ -119,7 +119,8 @@ int validate_gemm(const void* X, size_t Xb, const void* W, size_t Wb, const void
     if (!X || !W || !Y) return -2;
     if (((uintptr_t)X % 2 != 0) || ((uintptr_t)Y % 2 != 0)) return -2;
     const bool base_fmt = format >= 0 && format < 6;
-    const bool ext_fmt = extended && (format == QUANT_PRISM_Q2_0 || format == QUANT_MLX_4BIT_G64 || format == QUANT_TERNARY_ROW);
+    const bool ext_fmt = extended && (format == QUANT_PRISM_Q2_0 || format == QUANT_MLX_4BIT_G64 || format == QUANT_TERNARY_ROW ||
+                                     format == QUANT_MLX_4BIT_PLANAR);
     if (!base_fmt && !ext_fmt) return -3;
     if (M == 0 || K == 0 || N == 0) return -4;
     if ((K % 32) != 0) return -4;
@@ -252,7 +253,8 @@ size_t m4_bridge_get_expected_weight_bytes(int format, uint32_t K, uint32_t N) {
 }
 
 size_t b200_bridge_weight_bytes(int format, uint32_t K, uint32_t N) {
-    if (!((format >= 0 && format < 6) || format == QUANT_PRISM_Q2_0 || format == QUANT_MLX_4BIT_G64 || format == QUANT_TERNARY_ROW))
+    if (!((format >= 0 && format < 6) || format == QUANT_PRISM_Q2_0 || format == QUANT_MLX_4BIT_G64 || format == QUANT_TERNARY_ROW ||
+          format == QUANT_MLX_4BIT_PLANAR))
         return 0;
     return compute_quant_matrix_bytes((QuantFormat)format, K, N);
 }

@@ -375,6 +375,34 @@ template <> struct Codec<QUANT_MLX_4BIT_G64> : CodecDefaults {
     }
 };
 
+// ---- MLX 4-bit, group 32, planar (unified_multi_scale_kernels.metal:17-79; layout id 102) ----------------
+// The reference's layer benchmarks keep MLX weights as three planes: 16 nibble bytes per block of 32 (byte j: low
+// nibble = element j, high nibble = element j + 16, as in the 20-byte block), then one fp16 scale per block, then
+// one fp16 bias per block.  Packed row: 128 bytes per 256 elements; meta[0..3] hold the chunk's eight scales,
+// meta[4..7] its eight biases.  w = q*s + b, one fused fp16 multiply-add.
+template <> struct Codec<QUANT_MLX_4BIT_PLANAR> : CodecDefaults {
+    static constexpr int ROW_BYTES = 128;
+    static constexpr int GROUPS = 3;
+    CDC_HD static constexpr int sub_lo(int s) { return 8 * s; }
+    CDC_HD static constexpr int sub_hi(int s) { return 8 * s + 8; }
+    static constexpr int META_WORDS = 8;
+    static constexpr bool RAW_SWIZZLE_128 = true;
+    CDC_HD static void dequant64(const uint32_t* r, int s, uint32_t* out, const uint32_t* meta) {
+#pragma unroll
+        for (int bi = 0; bi < 2; bi++) {
+            const int b = 2 * s + bi;
+            const uint32_t d2 = bcast16(meta, 2 * b), b2 = bcast16(meta + 4, 2 * b);
+#pragma unroll
+            for (int p = 0; p < 8; p++) {
+                uint32_t lo, hi;
+                nib_pairs(spread_pair(r, 16 * b + 2 * p), lo, hi);
+                out[16 * bi + p] = h2fma(h2sub(lo, H2_1024), d2, b2);
+                out[16 * bi + 8 + p] = h2fma(h2sub(hi, H2_64), d2, b2);
+            }
+        }
+    }
+};
+
 // ---- ternary with one scale per output row, planar (extension layout 101) -------------------------------
 // Packed row: u32 words of 16 two-bit codes, code t of word i is k = 16i + t; 64 bytes per 256 elements.  The
 // weights go to the tensor core as the exact integers code - 1; the row's fp16 scale multiplies the fp32

@@ -630,26 +630,37 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         bool ok = true;
         for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
             const Tile t = decode_tile(idx, p);
-            uint32_t meta_next[4] = {0u, 0u, 0u, 0u};
-            auto load_meta = [&](uint32_t kc, uint32_t (&m)[4]) {
+            // META_WORDS / 2 words of scales and as many of biases per chunk: one group per 64 elements (4 words)
+            // or per 32 elements (8 words); the bias plane follows the scale plane
+            constexpr int MW = Cd::META_WORDS > 0 ? Cd::META_WORDS : 4;
+            uint32_t meta_next[MW] = {};
+            auto load_meta = [&](uint32_t kc, uint32_t (&m)[MW]) {
                 const uint32_t n = t.wt * (p.swiglu ? GATE_ROWS : W_TILE) + mrow_in_tile;
                 if (n < p.N) {
-                    const uint32_t g64 = p.K / 64;
-                    const uint8_t* mp = (mat == 0 ? p.meta0 : p.meta1) + ((size_t)n * g64 + (size_t)(t.ks * p.kchunks + kc) * 4) * 2;
-                    const uint2 sc = __ldg(reinterpret_cast<const uint2*>(mp));
-                    const uint2 bi = __ldg(reinterpret_cast<const uint2*>(mp + (size_t)p.N * g64 * 2));
-                    m[0] = sc.x; m[1] = sc.y; m[2] = bi.x; m[3] = bi.y;
+                    const uint32_t groups = (p.K / 256) * MW;
+                    const uint8_t* mp = (mat == 0 ? p.meta0 : p.meta1) + ((size_t)n * groups + (size_t)(t.ks * p.kchunks + kc) * MW) * 2;
+                    const uint8_t* bp = mp + (size_t)p.N * groups * 2;
+                    if (MW == 4) {
+                        const uint2 sc = __ldg(reinterpret_cast<const uint2*>(mp));
+                        const uint2 bi = __ldg(reinterpret_cast<const uint2*>(bp));
+                        m[0] = sc.x; m[1] = sc.y; m[2] = bi.x; m[3] = bi.y;
+                    } else {
+                        const uint4 sc = __ldg(reinterpret_cast<const uint4*>(mp));
+                        const uint4 bi = __ldg(reinterpret_cast<const uint4*>(bp));
+                        m[0] = sc.x; m[1] = sc.y; m[2] = sc.z; m[3] = sc.w;
+                        m[MW - 4] = bi.x; m[MW - 3] = bi.y; m[MW - 2] = bi.z; m[MW - 1] = bi.w;
+                    }
                 }
             };
             (void)load_meta; (void)meta_next;
             for (uint32_t kc = 0; ok && kc < p.kchunks; kc++) {
                 // scales and biases kept outside the packed rows come straight from global memory, one chunk
                 // ahead of their use so the latency hides behind the unpacking of the current chunk
-                uint32_t meta[4] = {0u, 0u, 0u, 0u};
-                if (Cd::META_WORDS == 4) {
+                uint32_t meta[MW] = {};
+                if (Cd::META_WORDS != 0) {
                     if (kc == 0) load_meta(0u, meta_next);
 #pragma unroll
-                    for (int i = 0; i < 4; i++) meta[i] = meta_next[i];
+                    for (int i = 0; i < MW; i++) meta[i] = meta_next[i];
                     if (kc + 1 < p.kchunks) load_meta(kc + 1, meta_next);
                 }
                 ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&raw_full[rs], rph, abort_flag, p.err, 106));
@@ -1050,6 +1061,14 @@ __device__ float generic_weight(int fmt, const uint8_t* W, uint32_t n, uint32_t 
             uint32_t q = (qs[k / 8] >> (4 * (k % 8))) & 15u;
             return (float)q * __half2float(sc[k / 64]) + __half2float(bi[k / 64]);
         }
+        case QUANT_MLX_4BIT_PLANAR: {
+            const size_t blocks = (size_t)N * (K / 32), blk = (size_t)n * (K / 32) + k / 32;
+            const size_t scales_off = (blocks * 16 + 15) & ~(size_t)15, biases_off = (scales_off + blocks * 2 + 15) & ~(size_t)15;
+            const uint8_t byte = W[blk * 16 + (k % 16)];
+            const uint32_t q = ((k % 32) < 16) ? (byte & 15u) : (byte >> 4);
+            return (float)q * __half2float(reinterpret_cast<const __half*>(W + scales_off)[blk]) +
+                   __half2float(reinterpret_cast<const __half*>(W + biases_off)[blk]);
+        }
         case QUANT_TERNARY_ROW: {
             const uint32_t* qs = reinterpret_cast<const uint32_t*>(W) + (size_t)n * (K / 16);
             const __half* rs = reinterpret_cast<const __half*>(W + (size_t)N * (K / 16) * 4);
@@ -1123,6 +1142,7 @@ int row_bytes_256(int fmt) {
         case QUANT_VAR_RATE_AFFINE: return 160;
         case QUANT_EXL3: return 144;
         case QUANT_MLX_4BIT_G64: return 128;     // nibble plane only; scales and biases sit in planes behind it
+        case QUANT_MLX_4BIT_PLANAR: return 128;  // nibble plane only; one scale and one bias per 32 elements in planes behind it
         case QUANT_TERNARY_ROW: return 64;       // 2-bit plane only; one fp16 scale per row behind it
         default: return 0;
     }
@@ -1307,6 +1327,7 @@ cudaError_t dispatch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t s
         case QUANT_VAR_RATE_AFFINE: return launch_fast<QUANT_VAR_RATE_AFFINE>(a, ws, s);
         case QUANT_EXL3: return launch_fast<QUANT_EXL3>(a, ws, s);
         case QUANT_MLX_4BIT_G64: return launch_fast<QUANT_MLX_4BIT_G64>(a, ws, s);
+        case QUANT_MLX_4BIT_PLANAR: return launch_fast<QUANT_MLX_4BIT_PLANAR>(a, ws, s);
         case QUANT_TERNARY_ROW: return launch_fast<QUANT_TERNARY_ROW>(a, ws, s);
         case QUANT_PRISM_Q2_0: return launch_fast<QUANT_PRISM_Q2_0>(a, ws, s);
         default: return cudaErrorInvalidValue;
@@ -1325,6 +1346,7 @@ cudaError_t prepare_device() {
     if (e == cudaSuccess) e = set_kernel_attributes<QUANT_VAR_RATE_AFFINE>();
     if (e == cudaSuccess) e = set_kernel_attributes<QUANT_EXL3>();
     if (e == cudaSuccess) e = set_kernel_attributes<QUANT_MLX_4BIT_G64>();
+    if (e == cudaSuccess) e = set_kernel_attributes<QUANT_MLX_4BIT_PLANAR>();
     if (e == cudaSuccess) e = set_kernel_attributes<QUANT_TERNARY_ROW>();
     if (e == cudaSuccess) e = set_kernel_attributes<QUANT_PRISM_Q2_0>();
     return e;

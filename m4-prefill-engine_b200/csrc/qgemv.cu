@@ -61,13 +61,22 @@ __global__ void __launch_bounds__(GV_THREADS) qgemv_kernel(const GvParams p) {
                     const uint4 v = __ldg(src + i);
                     r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
                 }
-                uint32_t meta[4] = {0u, 0u, 0u, 0u};
-                if (Cd::META_WORDS == 4) {
-                    const uint32_t g64 = p.K / 64;
-                    const uint8_t* mp = p.meta + ((size_t)n * g64 + (size_t)c * 4) * 2;
-                    const uint2 sc = __ldg(reinterpret_cast<const uint2*>(mp));
-                    const uint2 bi = __ldg(reinterpret_cast<const uint2*>(mp + (size_t)p.N * g64 * 2));
-                    meta[0] = sc.x; meta[1] = sc.y; meta[2] = bi.x; meta[3] = bi.y;
+                constexpr int MW = Cd::META_WORDS > 0 ? Cd::META_WORDS : 4;
+                uint32_t meta[MW] = {};
+                if (Cd::META_WORDS != 0) {           // one scale and one bias per 64 (4 words) or 32 (8 words) elements, two planes
+                    const uint32_t groups = (p.K / 256) * MW;
+                    const uint8_t* mp = p.meta + ((size_t)n * groups + (size_t)c * MW) * 2;
+                    const uint8_t* bp = mp + (size_t)p.N * groups * 2;
+                    if (MW == 4) {
+                        const uint2 sc = __ldg(reinterpret_cast<const uint2*>(mp));
+                        const uint2 bi = __ldg(reinterpret_cast<const uint2*>(bp));
+                        meta[0] = sc.x; meta[1] = sc.y; meta[2] = bi.x; meta[3] = bi.y;
+                    } else {
+                        const uint4 sc = __ldg(reinterpret_cast<const uint4*>(mp));
+                        const uint4 bi = __ldg(reinterpret_cast<const uint4*>(bp));
+                        meta[0] = sc.x; meta[1] = sc.y; meta[2] = sc.z; meta[3] = sc.w;
+                        meta[MW - 4] = bi.x; meta[MW - 3] = bi.y; meta[MW - 2] = bi.z; meta[MW - 1] = bi.w;
+                    }
                 }
                 const float* xc = sx + (size_t)c * XSTRIDE;
 #pragma unroll
@@ -149,7 +158,7 @@ bool gemv_path_ok(const GemmArgs& a) {
     if ((size_t)a.M * (a.K / 256) * XSTRIDE * sizeof(float) > 200 * 1024) return false;
     switch (a.format) {
         case QUANT_Q4_0: case QUANT_MLX_4BIT: case QUANT_Q4_K: case QUANT_TERNARY_1_58: case QUANT_VAR_RATE_AFFINE: case QUANT_EXL3:
-        case QUANT_MLX_4BIT_G64: case QUANT_TERNARY_ROW: return true;
+        case QUANT_MLX_4BIT_G64: case QUANT_TERNARY_ROW: case QUANT_MLX_4BIT_PLANAR: return true;
         default: return false;
     }
 }
@@ -163,6 +172,7 @@ cudaError_t launch_gemv(const GemmArgs& a, cudaStream_t s) {
         case QUANT_VAR_RATE_AFFINE: return launch_gemv_fmt<QUANT_VAR_RATE_AFFINE>(a, s);
         case QUANT_EXL3: return launch_gemv_fmt<QUANT_EXL3>(a, s);
         case QUANT_MLX_4BIT_G64: return launch_gemv_fmt<QUANT_MLX_4BIT_G64>(a, s);
+        case QUANT_MLX_4BIT_PLANAR: return launch_gemv_fmt<QUANT_MLX_4BIT_PLANAR>(a, s);
         case QUANT_TERNARY_ROW: return launch_gemv_fmt<QUANT_TERNARY_ROW>(a, s);
         default: return cudaErrorInvalidValue;
     }

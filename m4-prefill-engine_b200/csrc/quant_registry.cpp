@@ -1,6 +1,9 @@
 // QuantRegistry implementation: the eight built-in descriptors of the reference
-// (src/router/quant_registry.mm:60-172, same names, sizes and kernel-name strings) plus the two
-// planar extension layouts, and kernel-name resolution for the CUDA launchers.
+// (src/router/quant_registry.mm:60-172, same names, sizes and kernel-name strings) and kernel-name
+// resolution for the CUDA launchers.  Two planar MLX layouts are registered as well, so that the layer coordinator
+// can bind them: the group-32 planes of the reference's layer benchmarks under the kernel names of its unified
+// pipelines (unified_multi_scale_kernels.metal: gemm_mma_mlx_4bit_64x64, qkv_head_gemm_mma_mlx_4bit_64x64), and
+// the group-64 extension layout.  Their struct_size is the bytes one block occupies over all three planes.
 #include "../../include/quant_registry.h"
 
 #include <cstring>
@@ -75,7 +78,7 @@ void QuantRegistry::register_builtin_codecs() {
         {QUANT_VAR_RATE_AFFINE, "VAR_RATE_AFFINE", "256-element mixed 3/4/5-bit affine super-blocks", 256, sizeof(block_var_rate_affine), 5.00, "var_rate_affine", true},
         {QUANT_EXL3, "EXL3", "256-element codebook super-blocks with residual correction", 256, sizeof(block_exl3), 4.50, "exl3", true},
         {QUANT_Q8_0, "Q8_0", "32-element symmetric 8-bit blocks (KV cache)", 32, sizeof(block_q8_0), 8.50, "q8_0", false},
-        {QUANT_PRISM_Q2_0, "PRISM_Q2_0", "128-element 2-bit ternary blocks, fp16 scale", 128, sizeof(block_prism_q2_0), 2.125, "prism_q2_0", false},
+        {QUANT_PRISM_Q2_0, "PRISM_Q2_0", "128-element 2-bit ternary blocks, fp16 scale", 128, sizeof(block_prism_q2_0), 2.125, "prism_q2_0", true},
     };
     for (const Row& r : rows) {
         QuantCodecDescriptor d;
@@ -87,6 +90,18 @@ void QuantRegistry::register_builtin_codecs() {
         d.tensor_core_codec = r.tc;
         register_codec(d);
     }
+    QuantCodecDescriptor p;
+    p.format = QUANT_MLX_4BIT_PLANAR; p.name = "MLX_4BIT_PLANAR";
+    p.description = "32-element affine 4-bit blocks in three planes: nibbles, fp16 scales, fp16 biases";
+    p.block_size = 32; p.struct_size = 20; p.bits_per_weight = 5.0;
+    p.gemm_kernel_name = "gemm_mma_mlx_4bit_64x64"; p.head_gemm_kernel_name = "qkv_head_gemm_mma_mlx_4bit_64x64";
+    p.quantize_fn = nullptr; p.dequantize_fn = nullptr; p.tensor_core_codec = true;
+    register_codec(p);
+    p.format = QUANT_MLX_4BIT_G64; p.name = "MLX_4BIT_G64";
+    p.description = "64-element affine 4-bit groups, sequential nibbles, in three planes";
+    p.block_size = 64; p.struct_size = 36; p.bits_per_weight = 4.5;
+    p.gemm_kernel_name = "quant_router_gemm_mlx_4bit_g64_64x64"; p.head_gemm_kernel_name = "quant_router_head_gemm_mlx_4bit_g64_64x64";
+    register_codec(p);
 }
 
 }  // namespace b200_llm

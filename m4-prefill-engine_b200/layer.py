@@ -323,8 +323,8 @@ def shard_rows(W: np.ndarray, fmt, K: int, N: int, rank: int, tp: int) -> np.nda
 
 def shard_rows_any(W: np.ndarray, fmt, K: int, N: int, rank: int, tp: int) -> np.ndarray:
     """Column split of Y = X.W^T for every layout the projection accepts, the planar extension layouts included
-    (format 100: nibble plane, scale plane, bias plane; format 101: 2-bit plane, one scale per row): each plane is an
-    [N][x] matrix and keeps rows [rank*N/tp, (rank+1)*N/tp).  This is how the N-sharded ternary projection of the
+    (formats 100 and 102: nibble plane, scale plane, bias plane; format 101: 2-bit plane, one scale per row): each plane
+    is an [N][x] matrix and keeps rows [rank*N/tp, (rank+1)*N/tp); the planes of format 102 start on 16-byte boundaries.  This is how the N-sharded ternary projection of the
     benchmark (K=4096, N=14336 over 1/2/4/8 GPUs) is cut; no collective follows it."""
     fmt = int(fmt)
     n_loc = N // tp
@@ -332,13 +332,20 @@ def shard_rows_any(W: np.ndarray, fmt, K: int, N: int, rank: int, tp: int) -> np
         planes = [N * K // 2, N * (K // 64) * 2, N * (K // 64) * 2]
     elif fmt == 101:
         planes = [N * K // 4, N * 2]
+    elif fmt == 102:
+        planes = [N * K // 2, N * (K // 32) * 2, N * (K // 32) * 2]
     elif fmt == 7:
         planes = [N * (K // 128) * 34]
     else:
         return shard_rows(W, fmt, K, N, rank, tp)
+    pad = 16 if fmt == 102 else 1
     out, at = [], 0
     for nbytes in planes:
-        out.append(np.ascontiguousarray(W[at:at + nbytes].reshape(N, -1)[rank * n_loc:(rank + 1) * n_loc]).reshape(-1))
+        at = (at + pad - 1) // pad * pad
+        part = np.ascontiguousarray(W[at:at + nbytes].reshape(N, -1)[rank * n_loc:(rank + 1) * n_loc]).reshape(-1)
+        have = sum(len(x) for x in out)
+        out.append(np.zeros((have + pad - 1) // pad * pad - have, np.uint8))
+        out.append(part)
         at += nbytes
     return np.concatenate(out)
 

@@ -21,12 +21,12 @@ HERE = Path(__file__).resolve().parent
 
 # format ids (include/quant_router.h)
 Q4_0, MLX_4BIT, Q4_K, TERNARY_1_58, VAR_RATE_AFFINE, EXL3, Q8_0, PRISM_Q2_0 = range(8)
-MLX_4BIT_G64, TERNARY_ROW = 100, 101
+MLX_4BIT_G64, TERNARY_ROW, MLX_4BIT_PLANAR = 100, 101, 102
 BLOCK = {Q4_0: (32, 18), MLX_4BIT: (32, 20), Q4_K: (256, 144), TERNARY_1_58: (32, 12),
          VAR_RATE_AFFINE: (256, 160), EXL3: (256, 144), Q8_0: (32, 34), PRISM_Q2_0: (128, 34)}
 FORMAT_NAMES = {Q4_0: "q4_0", MLX_4BIT: "mlx_4bit", Q4_K: "q4_k", TERNARY_1_58: "ternary_1_58",
                 VAR_RATE_AFFINE: "var_rate_affine", EXL3: "exl3", PRISM_Q2_0: "prism_q2_0",
-                MLX_4BIT_G64: "mlx_4bit_g64", TERNARY_ROW: "ternary_row"}
+                MLX_4BIT_G64: "mlx_4bit_g64", TERNARY_ROW: "ternary_row", MLX_4BIT_PLANAR: "mlx_4bit_planar"}
 
 
 def weight_bytes(fmt: int, K: int, N: int) -> int:
@@ -34,6 +34,10 @@ def weight_bytes(fmt: int, K: int, N: int) -> int:
         return N * (K // 8) * 4 + 2 * N * (K // 64) * 2
     if fmt == TERNARY_ROW:
         return N * (K // 16) * 4 + N * 2
+    if fmt == MLX_4BIT_PLANAR:
+        blocks = N * (K // 32)
+        scales_off = (blocks * 16 + 15) & ~15
+        return ((scales_off + blocks * 2 + 15) & ~15) + blocks * 2
     be, bb = BLOCK[fmt]
     return N * (K // be) * bb
 
@@ -254,6 +258,20 @@ def baseline_inputs(fmt: int, M: int, K: int, N: int, seed: int = 0):
     return X, baseline_weights(fmt, K, N, rng)
 
 
+def mlx_aos_to_planar(W: np.ndarray, K: int, N: int) -> np.ndarray:
+    """20-byte MLX blocks {d, bias, qs[16]} -> the three planes of the reference's layer benchmarks
+    (bench_all_scales.mm:62-95): qs | scales | biases, each plane starting on a 16-byte boundary."""
+    nb = N * (K // 32)
+    blk = np.ascontiguousarray(W).reshape(nb, 20)
+    out = np.zeros(weight_bytes(MLX_4BIT_PLANAR, K, N), np.uint8)
+    scales_off = (nb * 16 + 15) & ~15
+    biases_off = (scales_off + nb * 2 + 15) & ~15
+    out[:nb * 16] = blk[:, 4:].reshape(-1)
+    out[scales_off:scales_off + nb * 2] = blk[:, 0:2].reshape(-1)
+    out[biases_off:biases_off + nb * 2] = blk[:, 2:4].reshape(-1)
+    return out
+
+
 def baseline_weights(fmt: int, K: int, N: int, rng) -> np.ndarray:
     if isinstance(rng, (int, np.integer)):
         rng = np.random.default_rng(int(rng))
@@ -272,6 +290,8 @@ def baseline_weights(fmt: int, K: int, N: int, rng) -> np.ndarray:
         W[:, 2:4] = b.astype(np.float16).view(np.uint8).reshape(nb, 2)
         W[:, 4:] = rng.integers(0, 256, (nb, 16), dtype=np.uint8)
         return W.reshape(-1)
+    if fmt == MLX_4BIT_PLANAR:
+        return mlx_aos_to_planar(baseline_weights(MLX_4BIT, K, N, rng), K, N)
     if fmt == MLX_4BIT_G64:
         qs = rng.integers(0, 2**32, (N, K // 8), dtype=np.uint32)
         s = rng.uniform(0.005, 0.02, (N, K // 64))

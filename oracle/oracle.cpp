@@ -215,6 +215,22 @@ void expand_mlx_g64(const uint8_t* base, uint32_t n, uint32_t N, uint32_t K, dou
         kidx[k] = k;
     }
 }
+//   MLX planar g32 (the layout of the reference's layer benchmarks, unified_multi_scale_kernels.metal:17-31 and
+//   bench_all_scales.mm:62-95; values as the AoS gold cpu_gold_reference.h:55-95): u8 qs[blocks][16] | f16 scale[blocks]
+//   | f16 bias[blocks], planes padded to 16 bytes, block = n*(K/32) + k/32, byte j: low nibble = element j, high j+16.
+void expand_mlx_planar(const uint8_t* base, uint32_t n, uint32_t N, uint32_t K, double* w, uint32_t* kidx) {
+    const size_t blocks = (size_t)N * (K / 32);
+    const size_t scales_off = (blocks * 16 + 15) & ~(size_t)15, biases_off = (scales_off + blocks * 2 + 15) & ~(size_t)15;
+    const f16* scales = (const f16*)(base + scales_off);
+    const f16* biases = (const f16*)(base + biases_off);
+    for (uint32_t k = 0; k < K; k++) {
+        const size_t blk = (size_t)n * (K / 32) + k / 32;
+        const uint8_t byte = base[blk * 16 + (k % 16)];
+        const int q = (k % 32) < 16 ? (byte & 15) : (byte >> 4);
+        w[k] = (double)q * (double)scales[blk] + (double)biases[blk];
+        kidx[k] = k;
+    }
+}
 void expand_ternary_row(const uint8_t* base, uint32_t n, uint32_t N, uint32_t K, double* w, uint32_t* kidx) {
     const uint32_t* qs = (const uint32_t*)base + (size_t)n * (K / 16);
     const f16* rs = (const f16*)(base + (size_t)N * (K / 16) * 4);
@@ -228,6 +244,7 @@ void expand_ternary_row(const uint8_t* base, uint32_t n, uint32_t N, uint32_t K,
 bool expand_row(int format, const uint8_t* W, uint32_t n, uint32_t N, uint32_t K, double* w, uint32_t* kidx) {
     if (format == QUANT_MLX_4BIT_G64) { expand_mlx_g64(W, n, N, K, w, kidx); return true; }
     if (format == QUANT_TERNARY_ROW)  { expand_ternary_row(W, n, N, K, w, kidx); return true; }
+    if (format == QUANT_MLX_4BIT_PLANAR) { expand_mlx_planar(W, n, N, K, w, kidx); return true; }
     QuantFormatInfo info = get_quant_info((QuantFormat)format);
     const uint8_t* row = W + (size_t)n * (K / info.block_size) * info.block_bytes;
     switch (format) {
@@ -245,6 +262,7 @@ bool expand_row(int format, const uint8_t* W, uint32_t n, uint32_t N, uint32_t K
 inline bool format_ok(int format, uint32_t K) {
     if (format == QUANT_MLX_4BIT_G64) return K % 64 == 0;
     if (format == QUANT_TERNARY_ROW) return K % 16 == 0;
+    if (format == QUANT_MLX_4BIT_PLANAR) return K % 32 == 0;
     if (format < 0 || format > 7 || format == QUANT_Q8_0) return false;
     return K % get_quant_info((QuantFormat)format).block_size == 0;
 }

@@ -15,10 +15,12 @@ static void run(const uint8_t* W, uint16_t* out, uint32_t N, uint32_t K) {
         for (uint32_t kc = 0; kc < K / CH; kc++) {
             uint32_t r[RB / 4];
             std::memcpy(r, W + n * row_bytes + (size_t)kc * RB, RB);
-            uint32_t meta[4] = {0, 0, 0, 0};
-            if (cdc::Codec<FMT>::META_WORDS == 4) {             // 4 scales then 4 biases of this chunk
-                std::memcpy(meta, plane2 + ((size_t)n * (K / 64) + kc * 4) * 2, 8);
-                std::memcpy(meta + 2, plane2 + (size_t)N * (K / 64) * 2 + ((size_t)n * (K / 64) + kc * 4) * 2, 8);
+            constexpr int MW = cdc::Codec<FMT>::META_WORDS > 0 ? cdc::Codec<FMT>::META_WORDS : 4;
+            uint32_t meta[MW] = {};
+            if (cdc::Codec<FMT>::META_WORDS != 0) {             // MW scales then MW biases of this chunk (one per 256 / MW elements)
+                const size_t groups = (size_t)(K / 256) * MW, at = ((size_t)n * groups + (size_t)kc * MW) * 2;
+                std::memcpy(meta, plane2 + at, MW * 2);
+                std::memcpy(meta + MW / 2, plane2 + (size_t)N * groups * 2 + at, MW * 2);
             }
             for (int s = 0; s < CH / 64; s++) {
                 uint32_t o[32];
@@ -38,6 +40,7 @@ extern "C" int codec_host_dequant(int fmt, const uint8_t* W, uint16_t* out, uint
         case QUANT_EXL3: run<QUANT_EXL3>(W, out, N, K); return 0;
         case QUANT_PRISM_Q2_0: run<QUANT_PRISM_Q2_0>(W, out, N, K); return 0;
         case QUANT_MLX_4BIT_G64: run<QUANT_MLX_4BIT_G64>(W, out, N, K); return 0;
+        case QUANT_MLX_4BIT_PLANAR: run<QUANT_MLX_4BIT_PLANAR>(W, out, N, K); return 0;
         case QUANT_TERNARY_ROW: run<QUANT_TERNARY_ROW>(W, out, N, K); return 0;   // integers code-1: the row scale is applied later
         default: return -3;
     }

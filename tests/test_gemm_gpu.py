@@ -103,10 +103,10 @@ def test_every_format_on_the_fallback_kernel(bridge):
         assert np.abs(Y.astype(np.float64) - o.gemm_f64(fmt, X, W, N)).max() <= TOL
 
 
-@pytest.mark.parametrize("fmt", [o.MLX_4BIT_G64, o.TERNARY_ROW])
+@pytest.mark.parametrize("fmt", [o.MLX_4BIT_G64, o.TERNARY_ROW, o.MLX_4BIT_PLANAR])
 @pytest.mark.parametrize("shape", [(33, 512, 96), (1, 4096, 200), (129, 4096, 1000), (300, 1024, 130), (40, 192, 70)])
 def test_extension_layouts(bridge, fmt, shape):
-    """Planar layouts 100 / 101: tensor-core path (K % 256 == 0; the K = 4096 cases split K and cut ragged
+    """Planar layouts 100 / 101 / 102: tensor-core path (K % 256 == 0; the K = 4096 cases split K and cut ragged
     row and token tiles) and the CUDA-core path (K = 192), which must agree with each other as well."""
     M, K, N = shape
     X, W = o.baseline_inputs(fmt, M, K, N, 3)
@@ -121,7 +121,7 @@ def test_extension_layouts(bridge, fmt, shape):
     check(Yg, gold, f"fmt {fmt} {shape} generic")
 
 
-@pytest.mark.parametrize("fmt", [o.MLX_4BIT_G64, o.TERNARY_ROW])
+@pytest.mark.parametrize("fmt", [o.MLX_4BIT_G64, o.TERNARY_ROW, o.MLX_4BIT_PLANAR])
 def test_extension_layouts_swiglu(bridge, fmt):
     from gpu_util import check_swiglu
     from test_swiglu_attention_gpu import run_swiglu
@@ -242,7 +242,7 @@ def test_host_buffers_pipeline_in_order(bridge):
 
 
 @pytest.mark.parametrize("fmt", [o.Q4_0, o.MLX_4BIT, o.Q4_K, o.TERNARY_1_58, o.VAR_RATE_AFFINE, o.EXL3, o.MLX_4BIT_G64,
-                                 o.TERNARY_ROW])
+                                 o.TERNARY_ROW, o.MLX_4BIT_PLANAR])
 @pytest.mark.parametrize("M", [1, 2, 3, 4])
 def test_few_token_path(bridge, fmt, M):
     """A single token runs on the CUDA-core streaming kernel (one lane per 256-element chunk of a weight row): 16
@@ -282,7 +282,8 @@ def test_residual_epilogue(bridge):
 
 
 # ---- benchmark shapes (K = N = 4096; the value distributions the benchmark contract names) ----
-ALL_CODECS = [o.Q4_0, o.MLX_4BIT, o.Q4_K, o.TERNARY_1_58, o.VAR_RATE_AFFINE, o.EXL3, o.PRISM_Q2_0, o.MLX_4BIT_G64, o.TERNARY_ROW]
+ALL_CODECS = [o.Q4_0, o.MLX_4BIT, o.Q4_K, o.TERNARY_1_58, o.VAR_RATE_AFFINE, o.EXL3, o.PRISM_Q2_0, o.MLX_4BIT_G64, o.TERNARY_ROW,
+              o.MLX_4BIT_PLANAR]
 
 
 @pytest.mark.parametrize("shape", [(33, 1024, 256), (127, 2048, 130), (129, 1024, 65), (512, 3072, 300), (2, 4096, 200)])
@@ -344,8 +345,8 @@ def test_8b_projection_m2048(bridge, fmt):
 
 @pytest.mark.parametrize("fmt", ALL_CODECS)
 def test_few_token_kernels_agree(bridge, fmt):
-    """The cluster kernel (weights unpacked into tensor memory, K split over a thread-block cluster, partial tiles summed in
-    distributed shared memory) against the persistent kernel (split-K through a scratch buffer) on the same inputs: both
+    """The cluster kernel (weights unpacked into tensor memory, K split over a thread-block cluster, partial tiles summed by
+    the cluster's CTAs out of the L2-resident scratch) against the persistent kernel (split-K through a scratch buffer) on the same inputs: both
     within tolerance of the oracle, and of each other within the fp32 summation-order difference (one fp16 ulp)."""
     K, N = 4096, 1000 if fmt != o.PRISM_Q2_0 else 1024
     for M in (5, 33, 100, 128):

@@ -146,9 +146,9 @@ def test_unpackers_baseline_distribution(codec_lib):
 
 
 def test_planar_unpackers_match_oracle(codec_lib):
-    """The two planar extension layouts: nibble / 2-bit plane through the tensor-core codec, metadata planes beside it."""
+    """The planar layouts (the reference's group-32 MLX planes and the two extension layouts): nibble / 2-bit plane through the tensor-core codec, metadata planes beside it."""
     K, N = 1024, 40
-    for fmt in (o.MLX_4BIT_G64, o.TERNARY_ROW):
+    for fmt in (o.MLX_4BIT_G64, o.TERNARY_ROW, o.MLX_4BIT_PLANAR):
         _, W = o.baseline_inputs(fmt, 1, K, N, 5)
         out = np.empty((N, K), np.uint16)
         assert codec_lib.codec_host_dequant(fmt, o._ptr(W), o._ptr(out), N, K) == 0

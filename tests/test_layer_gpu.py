@@ -101,6 +101,30 @@ def test_layer_reference_semantics(bridge, pkg, fmt, M):
     assert diff.max() <= max(TOL, 2.0 ** -7 * rms), f"max-abs {diff.max()} rms {rms}"
 
 
+@pytest.mark.parametrize("M", [129, 600])
+def test_layer_mlx_planar_weights(bridge, pkg, M):
+    """The layer on the planar group-32 MLX layout of the reference's layer benchmarks (bench_all_scales.mm:62-95,
+    kernels gemm_mma_mlx_4bit_64x64 / qkv_head_gemm_mma_mlx_4bit_64x64 / swiglu_mma_mlx_4bit_dual_simd): the same
+    weights as 20-byte blocks and as three planes give the oracle's layer within tolerance, and each other closely
+    (the two codecs produce the same fp16 weights; the K-split plans of the launches may differ)."""
+    K, H, D, F = 512, 8, 64, 768
+    w, g = layer_weights(o.MLX_4BIT, K, H, H, D, F)
+    shapes = {"q": (H * D, K), "k": (H * D, K), "v": (H * D, K), "o": (K, H * D), "gate": (F, K), "up": (F, K), "down": (K, F)}
+    wp = {n: o.mlx_aos_to_planar(w[n], k, r) for n, (r, k) in shapes.items()}
+    X = g.activations(M, K)
+    kw = dict(M=M, K=K, H=H, D=D, N_mlp=F, attn_scale=D ** -0.5)
+    Ya, _ = run_layer(pkg, dict(kw, weight_format=o.MLX_4BIT), X, w)
+    Yp, _ = run_layer(pkg, dict(kw, weight_format=o.MLX_4BIT_PLANAR), X, wp)
+    gold = o.layer(o.MLX_4BIT_PLANAR, X, wp["q"], wp["k"], wp["v"], wp["o"], wp["gate"], wp["up"], wp["down"], H, H, D, F, D ** -0.5)
+    assert np.array_equal(gold, o.layer(o.MLX_4BIT, X, w["q"], w["k"], w["v"], w["o"], w["gate"], w["up"], w["down"], H, H, D, F, D ** -0.5))
+    rms = float(np.sqrt(np.mean(gold.astype(np.float64) ** 2)))
+    for Y, what in ((Ya, "blocks"), (Yp, "planes")):
+        diff = np.abs(Y.astype(np.float64) - gold.astype(np.float64))
+        PARITY_REPORT.append(parity_stats(Y, gold.astype(np.float64), f"layer mlx {what} M={M}"))
+        assert diff.max() <= max(TOL, 2.0 ** -7 * rms), f"{what}: max-abs {diff.max()} rms {rms}"
+    assert np.abs(Ya.astype(np.float64) - Yp.astype(np.float64)).max() <= max(TOL, 2.0 ** -7 * rms) / 2
+
+
 @pytest.mark.parametrize("host_io", [False, True])
 def test_layer_llama_style(bridge, pkg, host_io):
     """RMSNorm + grouped-query attention + rotary embedding + Q8_0 KV, the benchmark's layer (small shape)."""

@@ -138,6 +138,21 @@ def test_mlx_g64_matches_aos_when_groups_repeat():
             assert dq[n, k] == q * sc[n, k // 64] + bi[n, k // 64]
 
 
+def test_mlx_planar_matches_aos():
+    """The planar group-32 layout of the reference's layer benchmarks holds the same weights as its 20-byte blocks
+    (bench_all_scales.mm:62-95 against quant_router.h:41-45): same values, same sizes as mlx_4bit_buffer_size()."""
+    rng = np.random.default_rng(8)
+    for K, N in ((64, 5), (96, 3), (256, 4)):            # 96 x 3: nine blocks, both side planes need padding
+        Wa = o.baseline_weights(o.MLX_4BIT, K, N, rng)
+        Wp = o.mlx_aos_to_planar(Wa, K, N)
+        nb = N * K // 32
+        scales_off = (nb * 16 + 15) & ~15
+        assert Wp.size == ((scales_off + nb * 2 + 15) & ~15) + nb * 2 == o.weight_bytes(o.MLX_4BIT_PLANAR, K, N)
+        assert np.array_equal(o.dequant_matrix(o.MLX_4BIT_PLANAR, Wp, N, K), o.dequant_matrix(o.MLX_4BIT, Wa, N, K))
+        X = rng.standard_normal((3, K)).astype(np.float16)
+        assert np.array_equal(o.gemm(o.MLX_4BIT_PLANAR, X, Wp, N), o.gemm(o.MLX_4BIT, X, Wa, N))
+
+
 def test_ternary_row_matches_blocks_with_equal_scales():
     rng = np.random.default_rng(4)
     K, N = 64, 6
