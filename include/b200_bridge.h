@@ -143,7 +143,8 @@ int b200_bridge_clear_device_error(void);
 int b200_bridge_debug_set_tile_counter(uint32_t index, uint32_t value);
 void b200_bridge_force_generic(int on);
 /* Testing hook: 0 routes few-token projections (M <= 128 with fewer output tiles than SMs) to the persistent kernel
- * instead of the cluster kernel that is their default; != 0 restores the default. */
+ * instead of the cluster kernel that is their default; 1 restores the default; 2 sends every shape the cluster kernel can
+ * compute to it, whatever the token count (one CTA per 128 x 128 output tile, two CTAs per SM). */
 void b200_bridge_enable_small_kernel(int on);
 /* Up to three projections of the same activations in one launch (the Q, K and V projections of a layer): Y[i] =
  * X . W[i]^T with W[i] packed [N[i]][K/blk] in `format`, outputs in `layout` (LAYOUT_DIRECT_HEAD: [N[i]/D][M][D]).
@@ -163,8 +164,9 @@ int b200_bridge_dispatch_gemm_grouped(const void* X, const void* const* W, void*
 int b200_bridge_dispatch_qkv_fused(const void* X, const void* Wq, const void* Wk, const void* Wv, void* Q, void* Kc, void* Vc, int format,
                                    uint32_t M, uint32_t K, uint32_t Hq, uint32_t Hkv, uint32_t D, float rope_theta, uint32_t pos0,
                                    int kv_q8_0, uint32_t kv_tokens);
-/* Testing hook: != 0 routes head-dim-128 Q8_0 attention to the warp-level MMA kernels instead of the
- * tensor-memory kernel, so the two can be compared on the same inputs. */
+/* Testing hook: 1 routes head-dim-128 Q8_0 attention to the warp-level MMA kernels instead of the tensor-memory kernel,
+ * 2 keeps the tensor-memory kernel but stores V transposed in shared memory (its earlier form), so the variants can be
+ * compared on the same inputs; 0 restores the default. */
 void b200_bridge_force_legacy_attention(int on);
 
 #ifdef __cplusplus

@@ -29,7 +29,8 @@
 
 namespace attn {
 
-int g_force_legacy = 0;      // testing hook: route head-dim-128 Q8_0 attention to the warp-level MMA kernels
+int g_force_legacy = 0;      // testing hook: 1 routes head-dim-128 Q8_0 attention to the warp-level MMA kernels,
+                             // 2 keeps the tensor-memory kernel but with V transposed in shared memory (K-major B operand)
 
 constexpr int BQ = 64, BK = 64, THREADS = 128;
 
@@ -62,6 +63,7 @@ struct Params {
     uint32_t Hq, Hkv, M, Mkv, pos0;
     float scale_log2e;
     int out_tokens_major, kv_fp16;
+    int v_mode = 0;    // tensor-memory kernel: 0 V as an MN-major B operand (unpacked like K), 1 V transposed in shared memory
 };
 
 // D: head dim (64 or 128).  Shared layout: Q, K, V fp16 tiles with a 16-byte row pad (ldmatrix
@@ -741,7 +743,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const Params p, 
                               (which ? phV : phK) + r * TC_ROW_RAW + h * 68u;
         const __half2 off = __half2half2(__float2half(1152.0f));
         uint8_t* vt[8];
-        if (which) {
+        const bool transposed = which && p.v_mode != 0;
+        if (transposed) {
             const uint32_t cr = (r & 63u) >> 3;
             uint8_t* vb = sVt + (r >> 6) * TC_ATOM + h * 8u * 1024u + (r & 7u) * 2u;     // dims 64 h ..: 8 row groups further
 #pragma unroll
@@ -783,9 +786,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const Params p, 
 #pragma unroll
                 for (int f = 0; f < 16; f++) w[f] = 0u;    // absent keys: zero (P is zero there, 0 * garbage is not)
             }
-            if (which == 0) {
+            if (!transposed) {
                 // row r, 16-byte chunks 4 b .. 4 b + 3 of atom h: (rowbase | xr << 4) ^ (c << 4) = rowbase + ((c ^ xr) << 4)
-                uint8_t* rowb = sK + h * TC_ATOM + (r >> 3) * 1024u + (r & 7u) * 128u + ((r & 7u) << 4);
+                uint8_t* rowb = (which ? sVt : sK) + h * TC_ATOM + (r >> 3) * 1024u + (r & 7u) * 128u + ((r & 7u) << 4);
 #pragma unroll
                 for (int e = 0; e < 4; e++)
                     *reinterpret_cast<uint4*>(rowb + (((b * 4 + e) << 4) ^ ((r & 7u) << 4)) - ((r & 7u) << 4)) =
@@ -821,6 +824,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const Params p, 
     const uint64_t desc_hi = ptx::umma_desc_k_sw128(0u);
     auto desc = [&](const uint8_t* tile, int atom, int kk) {
         return desc_hi | (uint64_t)((((ptx::smem_u32(tile) + atom * TC_ATOM) & 0x3FFFFu) >> 4) + 2 * kk);
+    };
+    // V as the B operand of O += P.V in its natural [key][d] form: MN-major (d contiguous), 128-byte swizzle.  The 64
+    // d of an atom row are the contiguous run, the second atom (d 64..127) lies TC_ATOM bytes further (leading byte
+    // offset), groups of eight keys are 1024 bytes apart (stride byte offset); 16 keys further = 2048 bytes.
+    const uint32_t idesc_pv = p.v_mode == 0 ? (idesc | (1u << 16)) : idesc;
+    const uint64_t vdesc_hi = ((uint64_t)(TC_ATOM >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+    auto desc_v = [&](int atom, int kk) {
+        if (p.v_mode != 0) return desc(sVt, atom, kk);
+        return vdesc_hi | (uint64_t)(((ptx::smem_u32(sVt) + (uint32_t)(atom * 4 + kk) * 2048u) & 0x3FFFFu) >> 4);
     };
 
     // Two threads per query row: thread t and t + 128 (warps w and w + 4 address the same tensor-memory lanes)
@@ -947,14 +959,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const Params p, 
                 for (int a = 0; a < 2; a++)
 #pragma unroll
                     for (int kk = 0; kk < 4; kk++)
-                        ptx::umma_f16_ss(tO, desc(sP, a, kk), desc(sVt, a, kk), idesc, (kt | (uint32_t)(a | kk)) != 0u);
+                        ptx::umma_f16_ss(tO, desc(sP, a, kk), desc_v(a, kk), idesc_pv, (kt | (uint32_t)(a | kk)) != 0u);
                 ptx::umma_commit(bar_o);
             }
             __syncwarp();
         }
         if (kt + 1 < n_ktiles) {
+            // Bulk copies complete on an mbarrier that every thread waits on itself, and raw stage kt & 1 was last read
+            // (V of tile kt) before the barrier above: no further CTA barrier, so the workers start on the next K tile
+            // while warp 8 is still held issuing the PV MMAs.  The cp.async path needs every thread's copies to be visible.
             wait_raw(kt + 1);
-            __syncthreads();                               // ... visible to every thread; raw stage kt & 1 is free
+            if (!bulk_ok(kt + 1)) __syncthreads();
             ATR(0);
             if (kt + 2 < n_ktiles) issue(kt + 2);
             ATR(6);
@@ -1019,11 +1034,13 @@ cudaError_t launch_attention(const Params& p, uint32_t D, cudaStream_t stream) {
     // grouped-head kernel when the group size divides its 128-row tile into whole warps
     const uint32_t G = p.Hq / p.Hkv;
     // tensor-memory kernel: head dim 128, Q8_0 cache, every row of a lone pointer 16-byte aligned for the Q loads
-    if (D == 128 && !p.kv_fp16 && !g_force_legacy && ((uintptr_t)p.Q & 15u) == 0 && ((uintptr_t)p.O & 15u) == 0) {
-        if (G == 1) return launch_tc<1>(p, stream);
-        if (G == 2) return launch_tc<2>(p, stream);
-        if (G == 4) return launch_tc<4>(p, stream);
-        if (G == 8) return launch_tc<8>(p, stream);
+    if (D == 128 && !p.kv_fp16 && g_force_legacy != 1 && ((uintptr_t)p.Q & 15u) == 0 && ((uintptr_t)p.O & 15u) == 0) {
+        Params q = p;
+        q.v_mode = g_force_legacy == 2 ? 1 : 0;
+        if (G == 1) return launch_tc<1>(q, stream);
+        if (G == 2) return launch_tc<2>(q, stream);
+        if (G == 4) return launch_tc<4>(q, stream);
+        if (G == 8) return launch_tc<8>(q, stream);
     }
     if (D == 128) {
         if (G == 1) return launch_gqa<128, 1>(p, stream);

@@ -490,6 +490,6 @@ const char* b200_bridge_last_error_string(void) { return g.last_error.c_str(); }
 uint64_t b200_bridge_kernel_launches(void) { return g.launches; }
 void* b200_bridge_stream(void) { return (void*)g.stream; }
 void b200_bridge_force_generic(int on) { g.force_generic = on; }
-void b200_bridge_enable_small_kernel(int on) { qg::set_small_kernel_enabled(on != 0); }
+void b200_bridge_enable_small_kernel(int on) { qg::set_small_kernel_enabled(on); }
 
 }  // extern "C"

@@ -71,7 +71,8 @@ cudaError_t launch(const GemmArgs& a, const Workspace& ws, cudaStream_t stream);
 bool small_path_ok(const GemmArgs& a);
 size_t small_scratch_floats(const GemmArgs& a);
 cudaError_t launch_small(const GemmArgs& a, const Workspace& ws, cudaStream_t stream);
-void set_small_kernel_enabled(bool on);      // testing hook: off routes those shapes to the persistent kernel again
+void set_small_kernel_enabled(int mode);     // testing hook: 0 routes those shapes to the persistent kernel again, 1 default,
+                                             // 2 takes every shape the kernel can compute (any number of token tiles)
 // Number of kernels the last launch() enqueued (1, or 2 with the generic tail) -- for launch accounting.
 int last_launch_count();
 

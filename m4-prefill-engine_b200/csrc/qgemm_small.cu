@@ -478,12 +478,12 @@ template <int FMT> cudaError_t launch_fmt(const GemmArgs& a, const Workspace& ws
     return cudaLaunchKernelEx(&cfg, qgemm_small_kernel<FMT>, tmX, tmW, p);
 }
 
-bool g_enabled = true;
+int g_mode = 1;
 
 }  // namespace
 }  // namespace small
 
-void set_small_kernel_enabled(bool on) { small::g_enabled = on; }
+void set_small_kernel_enabled(int mode) { small::g_mode = mode; }
 
 #ifdef QS_TRACE
 extern "C" int b200_debug_small_trace(unsigned long long* out) {
@@ -492,7 +492,7 @@ extern "C" int b200_debug_small_trace(unsigned long long* out) {
 #endif
 
 bool small_path_ok(const GemmArgs& a) {
-    if (!small::g_enabled || a.force_generic) return false;
+    if (small::g_mode == 0 || a.force_generic) return false;
     if (a.W1 || a.partial_out || a.scatter.world || a.n_extra || a.post[0] || a.post[1] || a.post[2]) return false;
     if (a.M == 0 || a.N == 0 || a.K == 0) return false;
     if (((uintptr_t)a.X & 15u) || ((uintptr_t)a.W0 & 15u) || ((uintptr_t)a.Y & 3u)) return false;
@@ -512,6 +512,7 @@ bool small_path_ok(const GemmArgs& a) {
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     // (one token tile of up to 128 tokens: with two, every weight tile would be unpacked twice)
+    if (small::g_mode == 2) return true;
     return a.M <= (uint32_t)small::MAX_T && big_tiles < (uint32_t)n_sm;
 }
 
