@@ -164,10 +164,12 @@ int b200_bridge_dispatch_gemm_grouped(const void* X, const void* const* W, void*
 int b200_bridge_dispatch_qkv_fused(const void* X, const void* Wq, const void* Wk, const void* Wv, void* Q, void* Kc, void* Vc, int format,
                                    uint32_t M, uint32_t K, uint32_t Hq, uint32_t Hkv, uint32_t D, float rope_theta, uint32_t pos0,
                                    int kv_q8_0, uint32_t kv_tokens);
-/* Testing hook: 1 routes head-dim-128 Q8_0 attention to the warp-level MMA kernels instead of the tensor-memory kernel,
- * 2 keeps the tensor-memory kernel but stores V transposed in shared memory (its earlier form), so the variants can be
- * compared on the same inputs; 0 restores the default. */
+/* Testing hook, so that the attention kernels can be compared on the same inputs: 1 routes head-dim-128 attention to the
+ * warp-level MMA kernels; 2 and 3 to the tensor-memory kernel that unpacks the Q8_0 tiles itself (2: V transposed in shared
+ * memory, 3: V in its natural form); 0 restores the default (Q8_0 cache dequantised once per call, tiles through TMA). */
 void b200_bridge_force_legacy_attention(int on);
+/* Kernels the last attention dispatch enqueued (2 when a Q8_0 cache was dequantised first). */
+int b200_bridge_attention_launches(void);
 
 #ifdef __cplusplus
 }

@@ -29,8 +29,9 @@
 
 namespace attn {
 
-int g_force_legacy = 0;      // testing hook: 1 routes head-dim-128 Q8_0 attention to the warp-level MMA kernels,
-                             // 2 keeps the tensor-memory kernel but with V transposed in shared memory (K-major B operand)
+int g_force_legacy = 0;      // testing hook: 1 routes head-dim-128 attention to the warp-level MMA kernels; 2 and 3 to the
+                             // tensor-memory kernel that unpacks Q8_0 tiles itself, with V transposed in shared memory
+                             // (K-major B operand) or in its natural form (MN-major)
 
 constexpr int BQ = 64, BK = 64, THREADS = 128;
 
@@ -1024,6 +1025,340 @@ template <int G> cudaError_t launch_tc(const Params& p, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-memory variant fed by TMA (head dim 128): K and V arrive as fp16 [Hkv][Mkv][128] -- an fp16 cache as it is, a
+// Q8_0 cache dequantised once per call by dequant_q8_0_rows_kernel below (value = fp16(q * d), the rounding of the
+// reference's dequantize_q8_0), instead of once per 128-position query block inside the attention kernel, where
+// unpacking took half of every key tile's time.  TMA writes the tiles straight into the 128-byte-swizzled operand
+// layout; V is used in its natural [key][d] form as an MN-major B operand.
+//
+//   shared memory   Q, P (32 KB each), two stages each of K and V (4 x 32 KB)
+//   tensor memory   S in two buffers (columns 0..127, 128..255), O (256..383)
+//   warp 8          one thread issues every TMA load and every MMA:
+//                     S(kt+1) = Q.K(kt+1)^T is issued while the workers are busy with the softmax of tile kt,
+//                     O += P(kt).V(kt) right after the CTA barrier that ends that softmax
+//   warps 0-7       softmax of tile kt as in the kernel above (two threads per query row): S(kt) from tensor memory,
+//                   running maximum, then -- once PV(kt-1) has completed -- P to shared memory and the rescaling of O
+//   One CTA barrier per key tile.  Every mbarrier wait is bounded.
+//
+//   Buffer reuse      S buffer b: written by S(kt), kt & 1 == b, issued after the barrier of tile kt-1, by which the
+//                     workers have read S(kt-2) out of it.  K stage: S(kt) has completed before the workers leave the
+//                     barrier of tile kt (they waited for it), K(kt+2) is requested after that barrier.  V stage and P:
+//                     freed by the completion of PV(kt), which the workers (before writing P(kt+1)) and the issuing
+//                     thread (before requesting V(kt+2)) wait for during tile kt+1.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t T2_SMEM = 1024 + 6 * (size_t)TC_TILE + 128 + 2 * 2 * 128 * 4;
+
+template <int G>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+attn_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const Params p, int* err) {
+    constexpr int BP = TC_ROWS / G;                      // query positions per CTA
+    extern __shared__ uint8_t smem_raw_[];
+    uint8_t* base = smem_raw_ + ((1024u - (ptx::smem_u32(smem_raw_) & 1023u)) & 1023u);
+    uint8_t* sQ = base;
+    uint8_t* sP = sQ + TC_TILE;
+    uint8_t* sK = sP + TC_TILE;                          // [2 stages]
+    uint8_t* sV = sK + 2 * TC_TILE;                      // [2 stages]
+    uint64_t* bar_s = reinterpret_cast<uint64_t*>(sV + 2 * TC_TILE);   // [2] S(kt) complete in buffer kt & 1
+    uint64_t* bar_o = bar_s + 2;                         // PV(kt) complete
+    uint64_t* k_full = bar_o + 1;                        // [2] K(kt) landed in stage kt & 1
+    uint64_t* v_full = k_full + 2;                       // [2]
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(v_full + 2);
+    volatile uint32_t* abort_flag = tmem_holder + 1;
+    float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bar_s) + 128);   // [2 parities][2 halves][128 rows]
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t pb = gridDim.x - 1 - blockIdx.x;      // latest position blocks (longest) first
+    const uint32_t hk = blockIdx.y;
+    const uint32_t p0 = pb * BP;
+    const uint32_t last_pos = min(p.pos0 + min(p0 + BP, p.M) - 1, p.Mkv - 1);
+    const uint32_t n_ktiles = last_pos / TC_BK + 1;
+    const bool worker = warp < 8u;
+
+    auto load_tile = [&](const CUtensorMap* map, uint8_t* stage_base, uint64_t* bar, uint32_t kt) {   // one thread
+        uint8_t* dst = stage_base + (kt & 1u) * TC_TILE;
+        ptx::mbar_arrive_expect_tx(&bar[kt & 1u], TC_TILE);
+        ptx::tma_load_3d(dst, map, &bar[kt & 1u], 0, (int)(kt * TC_BK), (int)hk);             // d 0..63
+        ptx::tma_load_3d(dst + TC_ATOM, map, &bar[kt & 1u], 64, (int)(kt * TC_BK), (int)hk);  // d 64..127
+    };
+    if (tid == TC_WORKERS) {
+        for (int i = 0; i < 2; i++) { ptx::mbar_init(&bar_s[i], 1); ptx::mbar_init(&k_full[i], 1); ptx::mbar_init(&v_full[i], 1); }
+        ptx::mbar_init(bar_o, 1);
+        *abort_flag = 0u;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&tmK); ptx::prefetch_tensormap(&tmV);
+        load_tile(&tmK, sK, k_full, 0); load_tile(&tmV, sV, v_full, 0);
+        if (n_ktiles > 1) { load_tile(&tmK, sK, k_full, 1); load_tile(&tmV, sV, v_full, 1); }
+    }
+    __syncwarp();
+    if (warp == 8) { ptx::tmem_alloc(tmem_holder, 512); ptx::tmem_relinquish(); }
+
+    // ---- stage Q: row r = head (r / BP), position p0 + r % BP ----
+    for (uint32_t i = tid; i < TC_ROWS * (TC_D / 8); i += TC_THREADS) {
+        const uint32_t r = i / (TC_D / 8), c = i % (TC_D / 8);
+        const uint32_t h = hk * G + r / BP, pos = p0 + r % BP;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (pos < p.M) v = *reinterpret_cast<const uint4*>(p.Q + ((size_t)h * p.M + pos) * TC_D + c * 8);
+        *reinterpret_cast<uint4*>(sQ + tc_off(r, c * 8)) = v;
+    }
+    ptx::fence_proxy_async_smem();
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_holder;
+    const uint32_t tO = tmem + 256u;
+    const uint32_t idesc = ptx::umma_idesc_f16(128, 128);
+    const uint32_t idesc_pv = idesc | (1u << 16);         // B (= V) MN-major
+    const uint64_t desc_hi = ptx::umma_desc_k_sw128(0u);
+    auto desc = [&](const uint8_t* tile, int atom, int kk) {
+        return desc_hi | (uint64_t)((((ptx::smem_u32(tile) + atom * TC_ATOM) & 0x3FFFFu) >> 4) + 2 * kk);
+    };
+    // V [key][d]: the 64 d of an atom row are the contiguous run, the second atom lies TC_ATOM bytes further (leading
+    // byte offset), groups of eight keys are 1024 bytes apart (stride byte offset); 16 keys further = 2048 bytes
+    const uint64_t vdesc_hi = ((uint64_t)(TC_ATOM >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+    auto desc_v = [&](const uint8_t* tile, int step) {   // step: 16 keys
+        return vdesc_hi | (uint64_t)(((ptx::smem_u32(tile) + (uint32_t)step * 2048u) & 0x3FFFFu) >> 4);
+    };
+    auto issue_s = [&](uint32_t kt) {                     // one thread
+        const uint8_t* kt_tile = sK + (kt & 1u) * TC_TILE;
+#pragma unroll
+        for (int a = 0; a < 2; a++)
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++)
+                ptx::umma_f16_ss(tmem + (kt & 1u) * 128u, desc(sQ, a, kk), desc(kt_tile, a, kk), idesc, (uint32_t)(a | kk) != 0u);
+        ptx::umma_commit(&bar_s[kt & 1u]);
+    };
+
+    const uint32_t row = tid & 127u, half_id = tid >> 7, c_base = half_id * 64u;
+    const uint32_t head = hk * G + row / BP, pos = p0 + row % BP;
+    const uint32_t row_pos = p.pos0 + pos;
+    float m_run = -1e30f, l_run = 0.0f;
+    const uint32_t lane_addr = ((warp & 3u) * 32u) << 16;
+
+    if (warp == 8) {
+        const bool ok = __all_sync(0xffffffffu, ptx::mbar_wait(&k_full[0], 0u, abort_flag, err, 211));
+        ptx::tc_fence_after_sync();
+        if (ok && ptx::elect_one()) issue_s(0);
+        __syncwarp();
+    }
+    for (uint32_t kt = 0; kt < n_ktiles; kt++) {
+        const uint32_t st = kt & 1u, use = (kt >> 1) & 1u;     // stage / S buffer and the parity of this use of it
+        if (warp == 8) {
+            bool ok = true;
+            if (kt + 1 < n_ktiles) {
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait(&k_full[st ^ 1u], ((kt + 1) >> 1) & 1u, abort_flag, err, 211));
+                ptx::tc_fence_after_sync();
+                if (ok && ptx::elect_one()) issue_s(kt + 1);
+                __syncwarp();
+            }
+            if (ok && kt > 0 && kt + 1 < n_ktiles) {
+                // V stage (kt + 1) & 1 was read by PV(kt - 1)
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(bar_o, (kt - 1) & 1u, abort_flag, err, 212));
+                if (ok && lane == 0) load_tile(&tmV, sV, v_full, kt + 1);
+                __syncwarp();
+            }
+        } else {
+            bool ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&bar_s[st], use, abort_flag, err, 213));
+            // (a failed wait has set the abort flag; the code below still runs so that the pair barrier and the
+            // warp-collective tensor-memory accesses stay matched, its results are discarded after the CTA barrier)
+            ptx::tc_fence_after_sync();
+            const uint32_t k0 = kt * TC_BK;
+            const bool full = (k0 + TC_BK - 1 <= p.pos0 + p0) && (k0 + TC_BK <= p.Mkv);
+            float sc[64];
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+                uint32_t v[16];
+                ptx::tmem_ld_x16(tmem + st * 128u + lane_addr + c_base + c0, v);
+#pragma unroll
+                for (int j = 0; j < 16; j++) sc[c0 + j] = __uint_as_float(v[j]);
+            }
+            ptx::tmem_ld_wait();
+            float mx = -1e30f;
+            if (full) {
+#pragma unroll
+                for (int j = 0; j < 64; j++) mx = fmaxf(mx, sc[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 64; j++) {
+                    const uint32_t key = k0 + c_base + j;
+                    if (key > row_pos || key >= p.Mkv) sc[j] = -INFINITY;
+                    mx = fmaxf(mx, sc[j]);
+                }
+            }
+            mx = mx * p.scale_log2e;                        // the scale is positive: max and scaling commute
+            float* xm = xch + st * 256u;
+            xm[half_id * 128u + row] = mx;
+            ptx::bar_sync(1 + (int)(warp & 3u), 64);        // this warp and its partner
+            mx = fmaxf(fmaxf(mx, xm[(half_id ^ 1u) * 128u + row]), m_run);
+            const float corr = ex2(m_run - mx);
+            m_run = mx;
+            uint32_t pk[32];
+            float rs = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 64; j += 2) {
+                // masked scores are -inf: fma gives -inf, ex2 gives 0
+                const float e0 = ex2(fmaf(sc[j], p.scale_log2e, -mx));
+                const float e1 = ex2(fmaf(sc[j + 1], p.scale_log2e, -mx));
+                rs += e0 + e1;
+                pk[j >> 1] = pack_h2(e0, e1);
+            }
+            l_run = l_run * corr + rs;
+            // P and O belong to PV(kt-1) until it has completed
+            if (kt > 0) ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(bar_o, (kt - 1) & 1u, abort_flag, err, 214)) && ok;
+            ptx::tc_fence_after_sync();
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 8)
+                *reinterpret_cast<uint4*>(sP + tc_off(row, c_base + c0)) = make_uint4(pk[c0 / 2], pk[c0 / 2 + 1], pk[c0 / 2 + 2], pk[c0 / 2 + 3]);
+            // O *= corr on this thread's 64 columns, skipped while no row of this warp raised its maximum
+            if (kt > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll
+                for (int c0 = 0; c0 < 64; c0 += 16) {
+                    uint32_t v[16];
+                    ptx::tmem_ld_x16(tO + lane_addr + c_base + c0, v);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
+                    ptx::tmem_st_x16(tO + lane_addr + c_base + c0, v);
+                }
+                ptx::tmem_st_wait();
+            }
+            ptx::fence_proxy_async_smem();
+            ptx::tc_fence_before_sync();
+        }
+        __syncthreads();
+        if (*abort_flag) break;
+        if (warp == 8) {
+            const bool ok = __all_sync(0xffffffffu, ptx::mbar_wait(&v_full[st], use, abort_flag, err, 215));
+            ptx::tc_fence_after_sync();
+            if (ok && ptx::elect_one()) {
+                const uint8_t* v_tile = sV + st * TC_TILE;
+#pragma unroll
+                for (int a = 0; a < 2; a++)
+#pragma unroll
+                    for (int kk = 0; kk < 4; kk++)
+                        ptx::umma_f16_ss(tO, desc(sP, a, kk), desc_v(v_tile, a * 4 + kk), idesc_pv, (kt | (uint32_t)(a | kk)) != 0u);
+                ptx::umma_commit(bar_o);
+                // K stage kt & 1: S(kt) completed before the workers entered the barrier above
+                if (kt + 2 < n_ktiles) load_tile(&tmK, sK, k_full, kt + 2);
+            }
+            __syncwarp();
+        }
+    }
+    // the last PV
+    if (!*abort_flag) ptx::mbar_wait<32>(bar_o, (n_ktiles - 1u) & 1u, abort_flag, err, 216);
+    __syncthreads();
+
+    if (worker) xch[half_id * 128u + row] = l_run;         // (the loop's last use of this buffer is behind a CTA barrier)
+    __syncthreads();
+    const bool bad = *abort_flag != 0u;
+    if (worker && !bad) {
+        // (the tensor-memory loads are warp-collective: every lane takes part, only the stores depend on the row)
+        ptx::tc_fence_after_sync();
+        const bool row_ok = pos < p.M;
+        const float l_tot = l_run + xch[(half_id ^ 1u) * 128u + row];
+        const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
+        __half* dst = (p.out_tokens_major ? p.O + ((size_t)pos * p.Hq + head) * TC_D : p.O + ((size_t)head * p.M + pos) * TC_D) + c_base;
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 16) {
+            uint32_t v[16];
+            ptx::tmem_ld_x16(tO + lane_addr + c_base + c0, v);
+            ptx::tmem_ld_wait();
+            uint32_t pk[8];
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) pk[j >> 1] = pack_h2(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv);
+            if (row_ok) {
+                *reinterpret_cast<uint4*>(dst + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4*>(dst + c0 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            }
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (bad) {      // let loads that are still in flight land before the CTA gives its shared memory back
+        const long long t0 = clock64();
+        while (clock64() - t0 < 4000000LL) { }
+        __syncthreads();
+    }
+    if (warp == 8) { ptx::tc_fence_after_sync(); ptx::tmem_dealloc(tmem, 512); }
+}
+
+// Q8_0 rows of head dim 128 (four 34-byte blocks, 2-byte aligned) -> fp16, one warp per key: lane l takes codes
+// 4 (l % 8) .. + 3 of block l / 8 and writes 8 bytes, a warp one 256-byte row.  value = fp16(q * d), one rounding.
+__global__ void __launch_bounds__(256) dequant_q8_0_rows_kernel(const uint8_t* __restrict__ K, const uint8_t* __restrict__ V,
+                                                               __half* __restrict__ out, size_t rows) {
+    const size_t w = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t lane = threadIdx.x & 31u;
+    if (w >= 2 * rows) return;
+    const uint8_t* blk = (w < rows ? K + w * TC_ROW_RAW : V + (w - rows) * TC_ROW_RAW) + (lane >> 3) * 34u;
+    const __half d = *reinterpret_cast<const __half*>(blk);
+    const uint16_t* cp = reinterpret_cast<const uint16_t*>(blk + 2u + 4u * (lane & 7u));
+    const uint32_t c = (uint32_t)cp[0] | ((uint32_t)cp[1] << 16);
+    __half v[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) v[i] = __hmul(__int2half_rn((int)(int8_t)(c >> (8 * i))), d);
+    uint2 o;
+    o.x = (uint32_t)__half_as_ushort(v[0]) | ((uint32_t)__half_as_ushort(v[1]) << 16);
+    o.y = (uint32_t)__half_as_ushort(v[2]) | ((uint32_t)__half_as_ushort(v[3]) << 16);
+    *reinterpret_cast<uint2*>(out + w * TC_D + lane * 4u) = o;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return (EncodeTiledFn)f;
+    }();
+    return fn;
+}
+// fp16 [Hkv][Mkv][128] as a 3-D map, boxes of 128 keys x 64 d with the 128-byte swizzle; keys past Mkv read as zero
+static bool make_kv_map(CUtensorMap* m, const void* ptr, uint32_t Hkv, uint32_t Mkv) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {TC_D, Mkv, Hkv};
+    cuuint64_t strides[2] = {TC_D * 2, (cuuint64_t)Mkv * TC_D * 2};
+    cuuint32_t box[3] = {64, TC_BK, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int g_last_launches = 1;     // kernels the last launch_attention call enqueued
+
+template <int G> cudaError_t launch_tma(const Params& p, cudaStream_t stream) {
+    constexpr int BP = TC_ROWS / G;
+    const __half *Kf = reinterpret_cast<const __half*>(p.K), *Vf = reinterpret_cast<const __half*>(p.V);
+    g_last_launches = 1;
+    if (!p.kv_fp16) {
+        // the Q8_0 cache is dequantised once per call into a scratch block that grows with the longest context seen
+        const size_t rows = (size_t)p.Hkv * p.Mkv;
+        if (!bridge::g.kv_fp16.ensure(2 * rows * TC_D * sizeof(__half))) return cudaErrorMemoryAllocation;
+        __half* scratch = static_cast<__half*>(bridge::g.kv_fp16.p);
+        const size_t threads = 2 * rows * 32;
+        dequant_q8_0_rows_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(p.K, p.V, scratch, rows);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        Kf = scratch; Vf = scratch + rows * TC_D;
+        g_last_launches = 2;
+    }
+    CUtensorMap tmK, tmV;
+    if (!make_kv_map(&tmK, Kf, p.Hkv, p.Mkv) || !make_kv_map(&tmV, Vf, p.Hkv, p.Mkv)) return cudaErrorInvalidValue;
+    dim3 grid((p.M + BP - 1) / BP, p.Hkv);
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T2_SMEM);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    attn_tma_kernel<G><<<grid, TC_THREADS, T2_SMEM, stream>>>(tmK, tmV, p, bridge::g.err_word);
+    return cudaGetLastError();
+}
+
 template <int D> size_t smem_bytes() {
     constexpr int LD = D + 8;
     constexpr int RAW_TILE_PAD = (((BK * (D / 32) * 34) + 15) & ~15) + 16;
@@ -1033,8 +1368,18 @@ template <int D> size_t smem_bytes() {
 cudaError_t launch_attention(const Params& p, uint32_t D, cudaStream_t stream) {
     // grouped-head kernel when the group size divides its 128-row tile into whole warps
     const uint32_t G = p.Hq / p.Hkv;
-    // tensor-memory kernel: head dim 128, Q8_0 cache, every row of a lone pointer 16-byte aligned for the Q loads
-    if (D == 128 && !p.kv_fp16 && g_force_legacy != 1 && ((uintptr_t)p.Q & 15u) == 0 && ((uintptr_t)p.O & 15u) == 0) {
+    g_last_launches = 1;
+    // tensor-memory kernels: head dim 128, every row of a lone pointer 16-byte aligned for the Q loads.  Default: K and V
+    // as fp16 through TMA (a Q8_0 cache is dequantised once per call first; an fp16 cache needs 16-byte alignment).
+    const bool tc_ok = D == 128 && ((uintptr_t)p.Q & 15u) == 0 && ((uintptr_t)p.O & 15u) == 0;
+    if (tc_ok && g_force_legacy == 0 && (!p.kv_fp16 || (((uintptr_t)p.K | (uintptr_t)p.V) & 15u) == 0) && encode_fn() != nullptr) {
+        if (G == 1) return launch_tma<1>(p, stream);
+        if (G == 2) return launch_tma<2>(p, stream);
+        if (G == 4) return launch_tma<4>(p, stream);
+        if (G == 8) return launch_tma<8>(p, stream);
+    }
+    // the kernel that unpacks the Q8_0 tiles itself (hooks 2 and 3)
+    if (tc_ok && !p.kv_fp16 && g_force_legacy != 1) {
         Params q = p;
         q.v_mode = g_force_legacy == 2 ? 1 : 0;
         if (G == 1) return launch_tc<1>(q, stream);
@@ -1079,6 +1424,8 @@ cudaError_t launch_dequantize(const void* src, void* dst, size_t n_elements, cud
     dequantize_q8_0_kernel<<<(unsigned)((nb + 127) / 128), 128, 0, stream>>>((const uint8_t*)src, (__half*)dst, nb);
     return cudaGetLastError();
 }
+
+int last_attention_launches() { return g_last_launches; }
 
 cudaError_t launch_attention_simple(const void* Q, const void* K, const void* V, void* O, uint32_t Hq, uint32_t Hkv,
                                     uint32_t M, uint32_t Mkv, uint32_t D, float scale, uint32_t pos0, int out_tokens_major,
@@ -1137,6 +1484,7 @@ int b200_bridge_dequantize_q8_0(void* src, size_t src_bytes, void* dst, size_t d
 }
 
 void b200_bridge_force_legacy_attention(int on) { attn::g_force_legacy = on; }
+int b200_bridge_attention_launches(void) { return attn::g_last_launches; }
 #ifdef ATTN_TRACE
 void b200_bridge_debug_attn_trace(unsigned long long* out) { cudaMemcpyFromSymbol(out, attn::g_attn_trace, 64); }
 #endif
@@ -1169,7 +1517,7 @@ int b200_bridge_dispatch_attention_q8kv(void* Q, void* K, void* V, void* O, uint
     p.scale_log2e = scale * 1.4426950408889634f;
     p.out_tokens_major = out_tokens_major; p.kv_fp16 = kv_fp16;
     if (attn::launch_attention(p, D, g.stream) != cudaSuccess) { set_error("attention launch failed"); return -6; }
-    g.launches++;
+    g.launches += (uint64_t)attn::g_last_launches;
     if (host_dst && copy_back(host_dst, p.O, q_bytes) != 0) return -5;
     return 0;
 }

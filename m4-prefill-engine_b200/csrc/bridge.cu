@@ -451,6 +451,7 @@ void m4_bridge_shutdown(void) {
     g.stage_aux0.release(); g.stage_aux1.release(); g.stage_aux2.release();
     g.ws_partial.release();
     g.rope_table.release(); g.rope_M = g.rope_D = 0;
+    g.kv_fp16.release();
     for (auto& kv : g.registered) cudaFree(kv.second.dev);
     g.registered.clear();
     cudaFree(g.counters); g.counters = nullptr; g.err_word = nullptr;

@@ -46,6 +46,7 @@ struct State {
     uint64_t dispatch_seq = 0;           // counts device -> host copies enqueued; synchronize clears marks up to its snapshot
     DevBuf stage_x, stage_w0, stage_w1, stage_y, stage_res, stage_aux0, stage_aux1, stage_aux2;
     DevBuf ws_partial;          // split-K partial tiles
+    DevBuf kv_fp16;             // K and V of the last Q8_0 attention call, dequantised once per call (attention.cu)
     DevBuf rope_table;          // (cos, sin) table of the last fused Q/K/V dispatch, and the request it was built for
     uint32_t rope_M = 0, rope_D = 0, rope_pos0 = 0;
     float rope_theta = 0.0f;

@@ -30,6 +30,7 @@ struct Params;
 cudaError_t launch_quantize(const void* src, void* dst, size_t n_elements, cudaStream_t stream);
 cudaError_t launch_dequantize(const void* src, void* dst, size_t n_elements, cudaStream_t stream);
 // thin wrapper so other translation units need not see attn::Params
+int last_attention_launches();     // kernels the last launch_attention_simple call enqueued (2 when a Q8_0 cache was dequantised first)
 cudaError_t launch_attention_simple(const void* Q, const void* K, const void* V, void* O, uint32_t Hq, uint32_t Hkv,
                                     uint32_t M, uint32_t Mkv, uint32_t D, float scale, uint32_t pos0, int out_tokens_major,
                                     int kv_fp16, cudaStream_t stream);

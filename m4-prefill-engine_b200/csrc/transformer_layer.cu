@@ -282,6 +282,7 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
         }
     }
     check(attn::launch_attention_simple(im.q, kk, vv, im.attn, hq, hkv, c.M, c.M, c.D, c.attn_scale, 0, 1, c.kv_q8_0 ? 0 : 1, stream));
+    launches_ += (uint32_t)(attn::last_attention_launches() - 1);
     mark("attention");
     // 2. O projection + first residual
     const void* x_mid = im.x_mid;

@@ -161,14 +161,18 @@ def test_attention_tensor_memory_kernel_long(bridge):
         bridge.lib.b200_bridge_force_legacy_attention(0)
     assert np.abs(b.astype(np.float64) - gold.astype(np.float64)).max() <= TOL
     assert np.abs(a.astype(np.float32) - b.astype(np.float32)).max() <= 2e-3
-    # the tensor-memory kernel with V transposed in shared memory (K-major operand) against its default, V in its natural
-    # [key][d] form as an MN-major operand: the same products in the same order
-    bridge.lib.b200_bridge_force_legacy_attention(2)
-    try:
-        c = run_attn(bridge, Q, Kq, Vq, D ** -0.5, Hkv, Mkv, pos0, True)
-    finally:
-        bridge.lib.b200_bridge_force_legacy_attention(0)
-    assert np.array_equal(a.view(np.uint16), c.view(np.uint16))
+    # the kernel that unpacks the Q8_0 tiles itself, with V transposed in shared memory (K-major operand, hook 2) and in
+    # its natural [key][d] form (MN-major operand, hook 3), against the default (cache dequantised once, tiles through
+    # TMA): the same products in the same order
+    outs = {}
+    for hook in (2, 3):
+        bridge.lib.b200_bridge_force_legacy_attention(hook)
+        try:
+            outs[hook] = run_attn(bridge, Q, Kq, Vq, D ** -0.5, Hkv, Mkv, pos0, True)
+        finally:
+            bridge.lib.b200_bridge_force_legacy_attention(0)
+    assert np.array_equal(outs[2].view(np.uint16), outs[3].view(np.uint16))
+    assert np.array_equal(a.view(np.uint16), outs[3].view(np.uint16))
     assert bridge.device_error() == 0
 
 
