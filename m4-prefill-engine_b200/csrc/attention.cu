@@ -1043,8 +1043,8 @@ template <int G> cudaError_t launch_tc(const Params& p, cudaStream_t stream) {
 //   One CTA barrier per key tile.  Every mbarrier wait is bounded.
 //
 //   Buffer reuse      S buffer b: written by S(kt), kt & 1 == b, issued after the barrier of tile kt-1, by which the
-//                     workers have read S(kt-2) out of it.  K stage: S(kt) has completed before the workers leave the
-//                     barrier of tile kt (they waited for it), K(kt+2) is requested after that barrier.  V stage and P:
+//                     workers have read S(kt-2) out of it.  K stage: the issuing thread waits for S(kt) itself during
+//                     tile kt and requests K(kt+2) then, a whole tile before it is needed.  V stage and P:
 //                     freed by the completion of PV(kt), which the workers (before writing P(kt+1)) and the issuing
 //                     thread (before requesting V(kt+2)) wait for during tile kt+1.
 // ---------------------------------------------------------------------------------------------
@@ -1052,9 +1052,11 @@ constexpr size_t T2_SMEM = 1024 + 6 * (size_t)TC_TILE + 128 + 2 * 2 * 128 * 4;
 
 template <int G>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-attn_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const Params p, int* err) {
+attn_tma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                const Params p, int* err) {
     constexpr int BP = TC_ROWS / G;                      // query positions per CTA
     extern __shared__ uint8_t smem_raw_[];
+    ATR_DECL;
     uint8_t* base = smem_raw_ + ((1024u - (ptx::smem_u32(smem_raw_) & 1023u)) & 1023u);
     uint8_t* sQ = base;
     uint8_t* sP = sQ + TC_TILE;
@@ -1064,7 +1066,8 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     uint64_t* bar_o = bar_s + 2;                         // PV(kt) complete
     uint64_t* k_full = bar_o + 1;                        // [2] K(kt) landed in stage kt & 1
     uint64_t* v_full = k_full + 2;                       // [2]
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(v_full + 2);
+    uint64_t* q_full = v_full + 2;                       // the query tile landed
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(q_full + 1);
     volatile uint32_t* abort_flag = tmem_holder + 1;
     float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bar_s) + 128);   // [2 parities][2 halves][128 rows]
 
@@ -1084,25 +1087,20 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     };
     if (tid == TC_WORKERS) {
         for (int i = 0; i < 2; i++) { ptx::mbar_init(&bar_s[i], 1); ptx::mbar_init(&k_full[i], 1); ptx::mbar_init(&v_full[i], 1); }
-        ptx::mbar_init(bar_o, 1);
+        ptx::mbar_init(bar_o, 1); ptx::mbar_init(q_full, 1);
         *abort_flag = 0u;
         ptx::fence_barrier_init();
-        ptx::prefetch_tensormap(&tmK); ptx::prefetch_tensormap(&tmV);
+        // Q: row r = head hk * G + r / BP, position p0 + r % BP: a box of BP positions x G heads per 64 d, which lands as the
+        // 128 rows of an atom in exactly that order; positions past M read as zero
+        ptx::mbar_arrive_expect_tx(q_full, TC_TILE);
+        ptx::tma_load_3d(sQ, &tmQ, q_full, 0, (int)p0, (int)(hk * G));
+        ptx::tma_load_3d(sQ + TC_ATOM, &tmQ, q_full, 64, (int)p0, (int)(hk * G));
         load_tile(&tmK, sK, k_full, 0); load_tile(&tmV, sV, v_full, 0);
         if (n_ktiles > 1) { load_tile(&tmK, sK, k_full, 1); load_tile(&tmV, sV, v_full, 1); }
     }
     __syncwarp();
     if (warp == 8) { ptx::tmem_alloc(tmem_holder, 512); ptx::tmem_relinquish(); }
 
-    // ---- stage Q: row r = head (r / BP), position p0 + r % BP ----
-    for (uint32_t i = tid; i < TC_ROWS * (TC_D / 8); i += TC_THREADS) {
-        const uint32_t r = i / (TC_D / 8), c = i % (TC_D / 8);
-        const uint32_t h = hk * G + r / BP, pos = p0 + r % BP;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (pos < p.M) v = *reinterpret_cast<const uint4*>(p.Q + ((size_t)h * p.M + pos) * TC_D + c * 8);
-        *reinterpret_cast<uint4*>(sQ + tc_off(r, c * 8)) = v;
-    }
-    ptx::fence_proxy_async_smem();
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
@@ -1137,11 +1135,13 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     const uint32_t lane_addr = ((warp & 3u) * 32u) << 16;
 
     if (warp == 8) {
-        const bool ok = __all_sync(0xffffffffu, ptx::mbar_wait(&k_full[0], 0u, abort_flag, err, 211));
+        const bool ok = __all_sync(0xffffffffu, ptx::mbar_wait(q_full, 0u, abort_flag, err, 210) &&
+                                                    ptx::mbar_wait(&k_full[0], 0u, abort_flag, err, 211));
         ptx::tc_fence_after_sync();
         if (ok && ptx::elect_one()) issue_s(0);
         __syncwarp();
     }
+    ATR(7);                                                // prologue
     for (uint32_t kt = 0; kt < n_ktiles; kt++) {
         const uint32_t st = kt & 1u, use = (kt >> 1) & 1u;     // stage / S buffer and the parity of this use of it
         if (warp == 8) {
@@ -1150,6 +1150,12 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
                 ok = __all_sync(0xffffffffu, ptx::mbar_wait(&k_full[st ^ 1u], ((kt + 1) >> 1) & 1u, abort_flag, err, 211));
                 ptx::tc_fence_after_sync();
                 if (ok && ptx::elect_one()) issue_s(kt + 1);
+                __syncwarp();
+            }
+            if (ok && kt + 2 < n_ktiles) {
+                // K stage kt & 1 is free once S(kt) has completed: request K(kt+2) now, a whole tile before S(kt+2) is issued
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&bar_s[st], use, abort_flag, err, 217));
+                if (ok && lane == 0) load_tile(&tmK, sK, k_full, kt + 2);
                 __syncwarp();
             }
             if (ok && kt > 0 && kt + 1 < n_ktiles) {
@@ -1163,6 +1169,7 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
             // (a failed wait has set the abort flag; the code below still runs so that the pair barrier and the
             // warp-collective tensor-memory accesses stay matched, its results are discarded after the CTA barrier)
             ptx::tc_fence_after_sync();
+            ATR(0);
             const uint32_t k0 = kt * TC_BK;
             const bool full = (k0 + TC_BK - 1 <= p.pos0 + p0) && (k0 + TC_BK <= p.Mkv);
             float sc[64];
@@ -1193,6 +1200,7 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
             mx = fmaxf(fmaxf(mx, xm[(half_id ^ 1u) * 128u + row]), m_run);
             const float corr = ex2(m_run - mx);
             m_run = mx;
+            ATR(1);
             uint32_t pk[32];
             float rs = 0.0f;
 #pragma unroll
@@ -1204,12 +1212,15 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
                 pk[j >> 1] = pack_h2(e0, e1);
             }
             l_run = l_run * corr + rs;
+            ATR(2);
             // P and O belong to PV(kt-1) until it has completed
             if (kt > 0) ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(bar_o, (kt - 1) & 1u, abort_flag, err, 214)) && ok;
             ptx::tc_fence_after_sync();
+            ATR(3);
 #pragma unroll
             for (int c0 = 0; c0 < 64; c0 += 8)
                 *reinterpret_cast<uint4*>(sP + tc_off(row, c_base + c0)) = make_uint4(pk[c0 / 2], pk[c0 / 2 + 1], pk[c0 / 2 + 2], pk[c0 / 2 + 3]);
+            ATR(4);
             // O *= corr on this thread's 64 columns, skipped while no row of this warp raised its maximum
             if (kt > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll
@@ -1225,8 +1236,10 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
             }
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_before_sync();
+            ATR(5);
         }
         __syncthreads();
+        ATR(6);
         if (*abort_flag) break;
         if (warp == 8) {
             const bool ok = __all_sync(0xffffffffu, ptx::mbar_wait(&v_full[st], use, abort_flag, err, 215));
@@ -1239,8 +1252,6 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
                     for (int kk = 0; kk < 4; kk++)
                         ptx::umma_f16_ss(tO, desc(sP, a, kk), desc_v(v_tile, a * 4 + kk), idesc_pv, (kt | (uint32_t)(a | kk)) != 0u);
                 ptx::umma_commit(bar_o);
-                // K stage kt & 1: S(kt) completed before the workers entered the barrier above
-                if (kt + 2 < n_ktiles) load_tile(&tmK, sK, k_full, kt + 2);
             }
             __syncwarp();
         }
@@ -1248,6 +1259,7 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     // the last PV
     if (!*abort_flag) ptx::mbar_wait<32>(bar_o, (n_ktiles - 1u) & 1u, abort_flag, err, 216);
     __syncthreads();
+    ATR_FLUSH();
 
     if (worker) xch[half_id * 128u + row] = l_run;         // (the loop's last use of this buffer is behind a CTA barrier)
     __syncthreads();
@@ -1316,13 +1328,14 @@ static EncodeTiledFn encode_fn() {
     }();
     return fn;
 }
-// fp16 [Hkv][Mkv][128] as a 3-D map, boxes of 128 keys x 64 d with the 128-byte swizzle; keys past Mkv read as zero
-static bool make_kv_map(CUtensorMap* m, const void* ptr, uint32_t Hkv, uint32_t Mkv) {
+// fp16 [heads][rows][128] as a 3-D map, boxes of box_heads x box_rows x 64 d with the 128-byte swizzle (box_heads * box_rows
+// == 128: one atom); rows past the end read as zero
+static bool make_kv_map(CUtensorMap* m, const void* ptr, uint32_t heads, uint32_t rows, uint32_t box_rows, uint32_t box_heads) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
-    cuuint64_t dims[3] = {TC_D, Mkv, Hkv};
-    cuuint64_t strides[2] = {TC_D * 2, (cuuint64_t)Mkv * TC_D * 2};
-    cuuint32_t box[3] = {64, TC_BK, 1};
+    cuuint64_t dims[3] = {TC_D, rows, heads};
+    cuuint64_t strides[2] = {TC_D * 2, (cuuint64_t)rows * TC_D * 2};
+    cuuint32_t box[3] = {64, box_rows, box_heads};
     cuuint32_t estr[3] = {1, 1, 1};
     return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -1346,8 +1359,10 @@ template <int G> cudaError_t launch_tma(const Params& p, cudaStream_t stream) {
         Kf = scratch; Vf = scratch + rows * TC_D;
         g_last_launches = 2;
     }
-    CUtensorMap tmK, tmV;
-    if (!make_kv_map(&tmK, Kf, p.Hkv, p.Mkv) || !make_kv_map(&tmV, Vf, p.Hkv, p.Mkv)) return cudaErrorInvalidValue;
+    CUtensorMap tmQ, tmK, tmV;
+    if (!make_kv_map(&tmK, Kf, p.Hkv, p.Mkv, TC_BK, 1) || !make_kv_map(&tmV, Vf, p.Hkv, p.Mkv, TC_BK, 1) ||
+        !make_kv_map(&tmQ, p.Q, p.Hq, p.M, BP, G))
+        return cudaErrorInvalidValue;
     dim3 grid((p.M + BP - 1) / BP, p.Hkv);
     static bool attr_set = false;
     if (!attr_set) {
@@ -1355,7 +1370,7 @@ template <int G> cudaError_t launch_tma(const Params& p, cudaStream_t stream) {
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    attn_tma_kernel<G><<<grid, TC_THREADS, T2_SMEM, stream>>>(tmK, tmV, p, bridge::g.err_word);
+    attn_tma_kernel<G><<<grid, TC_THREADS, T2_SMEM, stream>>>(tmQ, tmK, tmV, p, bridge::g.err_word);
     return cudaGetLastError();
 }
 

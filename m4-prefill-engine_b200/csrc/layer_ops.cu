@@ -237,7 +237,8 @@ cudaError_t rope(void* X, uint32_t H, uint32_t M, uint32_t D, float theta, uint3
 // Arithmetic is that of rope_heads_kernel and of attn::quantize_q8_0_kernel, bit for bit.
 __global__ void __launch_bounds__(128) kv_post_d128_kernel(__half* __restrict__ Q, const __half* __restrict__ Kin, const __half* __restrict__ Vin,
                                                            uint8_t* __restrict__ Kq, uint8_t* __restrict__ Vq, __half* __restrict__ Kout,
-                                                           const float2* __restrict__ table, uint32_t Hq, uint32_t Hkv, uint32_t M, int rope, int q8) {
+                                                           __half* __restrict__ Vout, const float2* __restrict__ table, uint32_t Hq, uint32_t Hkv,
+                                                           uint32_t M, int rope, int q8, int dq) {
     constexpr uint32_t D = 128, HALF = 64;
     const uint32_t m = blockIdx.x * 4u + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
     if (m >= M) return;
@@ -263,7 +264,9 @@ __global__ void __launch_bounds__(128) kv_post_d128_kernel(__half* __restrict__ 
         o.x = *reinterpret_cast<const uint32_t*>(&h01); o.y = *reinterpret_cast<const uint32_t*>(&h23);
         return o;
     };
-    auto quantise = [&](uint2 w, uint8_t* rec_row) {      // rec_row: the four records of this (head, token) row
+    // rec_row: the four records of this (head, token) row; dq_row (optional): the row's values as the cache will give them
+    // back, fp16(q * fp16(d)) -- what attention over the Q8_0 cache multiplies with
+    auto quantise = [&](uint2 w, uint8_t* rec_row, __half* dq_row) {
         const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&w.x)), f23 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
         const float v[4] = {f01.x, f01.y, f23.x, f23.y};
         float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
@@ -273,13 +276,17 @@ __global__ void __launch_bounds__(128) kv_post_d128_kernel(__half* __restrict__ 
         const float d = __fdiv_rn(amax, 127.0f);
         const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
         uint16_t* o = reinterpret_cast<uint16_t*>(rec_row + (lane >> 3) * 34u);
-        if ((lane & 7u) == 0u) o[0] = __half_as_ushort(__float2half_rn(d));
+        const __half dh = __float2half_rn(d);
+        if ((lane & 7u) == 0u) o[0] = __half_as_ushort(dh);
+        uint32_t back[2];
 #pragma unroll
         for (int e = 0; e < 2; e++) {
             int q0 = (int)roundf(__fmul_rn(v[2 * e], id)), q1 = (int)roundf(__fmul_rn(v[2 * e + 1], id));
             q0 = max(-128, min(127, q0)); q1 = max(-128, min(127, q1));
             o[1 + (lane & 7u) * 2u + e] = (uint16_t)((uint32_t)(uint8_t)(int8_t)q0 | ((uint32_t)(uint8_t)(int8_t)q1 << 8));
+            back[e] = (uint32_t)__half_as_ushort(__hmul(__int2half_rn(q0), dh)) | ((uint32_t)__half_as_ushort(__hmul(__int2half_rn(q1), dh)) << 16);
         }
+        if (dq_row) *reinterpret_cast<uint2*>(dq_row + lane * 4u) = make_uint2(back[0], back[1]);
     };
     if (rope) {
         // heads in batches of four: the loads of a batch are issued before its first store
@@ -299,22 +306,23 @@ __global__ void __launch_bounds__(128) kv_post_d128_kernel(__half* __restrict__ 
         const uint2 v = *reinterpret_cast<const uint2*>(Vin + row * D + lane * 4u);
         if (rope) k = rotate(k);
         if (q8) {
-            quantise(k, Kq + row * (D / 32u) * 34u);
-            quantise(v, Vq + row * (D / 32u) * 34u);
+            quantise(k, Kq + row * (D / 32u) * 34u, dq ? Kout + row * D : nullptr);
+            quantise(v, Vq + row * (D / 32u) * 34u, dq ? Vout + row * D : nullptr);
         } else if (rope) {
             *reinterpret_cast<uint2*>(Kout + row * D + lane * 4u) = k;
         }
     }
 }
 
-cudaError_t kv_post(void* Q, const void* K, const void* V, void* Kq, void* Vq, const void* rope_table, uint32_t Hq, uint32_t Hkv,
-                    uint32_t M, uint32_t D, bool rope, bool q8, cudaStream_t s) {
+cudaError_t kv_post(void* Q, void* K, void* V, void* Kq, void* Vq, const void* rope_table, uint32_t Hq, uint32_t Hkv,
+                    uint32_t M, uint32_t D, bool rope, bool q8, bool dequant_in_place, cudaStream_t s) {
     if (D != 128 || (rope && !rope_table) || (q8 && (!Kq || !Vq))) return cudaErrorInvalidValue;
     if (((reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(K) | reinterpret_cast<uintptr_t>(V)) & 7u) ||
         (reinterpret_cast<uintptr_t>(rope_table) & 15u))
         return cudaErrorInvalidValue;
     kv_post_d128_kernel<<<(M + 3) / 4, 128, 0, s>>>((__half*)Q, (const __half*)K, (const __half*)V, (uint8_t*)Kq, (uint8_t*)Vq, (__half*)K,
-                                                   (const float2*)rope_table, Hq, Hkv, M, rope ? 1 : 0, q8 ? 1 : 0);
+                                                   (__half*)V, (const float2*)rope_table, Hq, Hkv, M, rope ? 1 : 0, q8 ? 1 : 0,
+                                                   (q8 && dequant_in_place) ? 1 : 0);
     return cudaGetLastError();
 }
 

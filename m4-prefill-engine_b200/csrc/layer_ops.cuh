@@ -16,9 +16,11 @@ cudaError_t rope(void* X, uint32_t H, uint32_t M, uint32_t D, float theta, uint3
 cudaError_t build_rope_table(void* table, uint32_t M, uint32_t D, float theta, uint32_t pos0, cudaStream_t s);
 // One launch for everything between the Q/K/V projections and attention (head size 128): rotary embedding on Q [Hq][M][D] and
 // K [Hkv][M][D] in place (rope), K and V compressed to Q8_0 records [Hkv][M][D/32] (q8).  Bit-identical to rope() on Q and K
-// followed by attn::launch_quantize on K and V.  cudaErrorInvalidValue for other head sizes or misaligned buffers.
-cudaError_t kv_post(void* Q, const void* K, const void* V, void* Kq, void* Vq, const void* rope_table, uint32_t Hq, uint32_t Hkv,
-                    uint32_t M, uint32_t D, bool rope, bool q8, cudaStream_t s);
+// followed by attn::launch_quantize on K and V.  With dequant_in_place (and q8) K and V are overwritten by what the records
+// give back, fp16(q * d): the operands of attention over this Q8_0 cache, ready for it as fp16 tiles.
+// cudaErrorInvalidValue for other head sizes or misaligned buffers.
+cudaError_t kv_post(void* Q, void* K, void* V, void* Kq, void* Vq, const void* rope_table, uint32_t Hq, uint32_t Hkv,
+                    uint32_t M, uint32_t D, bool rope, bool q8, bool dequant_in_place, cudaStream_t s);
 // Y = fp16(float(A) + B) elementwise, A fp16, B fp32 (residual add after an fp32 all-reduce).
 cudaError_t add_residual_f32(const void* A_f16, const float* B_f32, void* Y_f16, size_t n, cudaStream_t s);
 // Y = fp16(A + B), all fp16; n % 8 == 0 and 16-byte aligned pointers (else cudaErrorInvalidValue)

@@ -259,13 +259,15 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
         mark("q, k, v projections (3 launches)");
     }
     const void *kk = im.k, *vv = im.v;
+    bool kv_as_fp16 = !c.kv_q8_0;
     if (kv_fused) {
         if (c.kv_q8_0) { kk = im.kq; vv = im.vq; }
     } else if ((c.rope_theta > 0.0f || c.kv_q8_0) &&
-               lops::kv_post(im.q, im.k, im.v, im.kq, im.vq, im.rope_table, hq, hkv, c.M, c.D, c.rope_theta > 0.0f, c.kv_q8_0, stream) == cudaSuccess) {
-        // one pass over Q, K and V: rotary embedding and the Q8_0 records
+               lops::kv_post(im.q, im.k, im.v, im.kq, im.vq, im.rope_table, hq, hkv, c.M, c.D, c.rope_theta > 0.0f, c.kv_q8_0, true, stream) == cudaSuccess) {
+        // one pass over Q, K and V: rotary embedding, the Q8_0 records, and K and V overwritten by the values the records
+        // give back, so that attention over this cache gets its operands as fp16 tiles without unpacking them again
         launches_++;
-        if (c.kv_q8_0) { kk = im.kq; vv = im.vq; }
+        kv_as_fp16 = true;
         mark("rope q, k + quantize k, v (one launch)");
     } else {
         cudaGetLastError();
@@ -281,7 +283,7 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
             mark("quantize k, v to q8_0");
         }
     }
-    check(attn::launch_attention_simple(im.q, kk, vv, im.attn, hq, hkv, c.M, c.M, c.D, c.attn_scale, 0, 1, c.kv_q8_0 ? 0 : 1, stream));
+    check(attn::launch_attention_simple(im.q, kk, vv, im.attn, hq, hkv, c.M, c.M, c.D, c.attn_scale, 0, 1, kv_as_fp16 ? 1 : 0, stream));
     launches_ += (uint32_t)(attn::last_attention_launches() - 1);
     mark("attention");
     // 2. O projection + first residual
