@@ -492,5 +492,7 @@ uint64_t b200_bridge_kernel_launches(void) { return g.launches; }
 void* b200_bridge_stream(void) { return (void*)g.stream; }
 void b200_bridge_force_generic(int on) { g.force_generic = on; }
 void b200_bridge_enable_small_kernel(int on) { qg::set_small_kernel_enabled(on); }
+void b200_bridge_enable_pair_kernel(int on) { qg::set_pair_kernel_enabled(on != 0); }
+int b200_bridge_last_launch_pair(void) { return qg::last_launch_pairs(); }
 
 }  // extern "C"

@@ -128,6 +128,69 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                  : "memory");
 }
 
+// ---- CTA pairs (cta_group::2): one MMA spans the tensor cores of two SMs ------------------------------------------
+// The two CTAs of a cluster of two hold 128 rows of A each and half of B's rows each; the accumulator of CTA r (rows
+// 128 r .. 128 r + 127 of the 256-row result) sits in that CTA's tensor memory.  One thread of the even-ranked CTA issues
+// the MMAs; operand descriptors name the same shared-memory offsets in both CTAs.  Per SM the MMA then reads its A rows and
+// only half of B from shared memory, which is what takes the shared-memory pipe off the critical path.
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {   // every thread of every CTA of the cluster
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {  // one warp of each CTA of the pair
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_pair_f16_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// the barrier at this shared-memory offset in both CTAs of the pair gets one arrival once every MMA issued so far by this
+// thread has finished
+__device__ __forceinline__ void umma_pair_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+}
+// Arrival on the barrier at this offset in CTA `rank` of the cluster.  Plain form (release at CTA scope), as for a local
+// barrier: what the arrival publishes are shared-memory stores that fence.proxy.async has already handed to the async
+// proxy, which is the proxy the other CTA's MMA reads them through.  (With .release.cluster the arriving unpack thread
+// stalled about a thousand cycles per stage, which made the pair slower than two single CTAs.)
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t rank) {
+    uint32_t ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(bar)), "r"(rank));
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(ra) : "memory");
+}
+// bounded wait on a local barrier that the other CTA of the cluster arrives on too (acquire at cluster scope)
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, int* err_word, int code) {
+    long long t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((spin & 1023u) == 1023u) {
+            if (*abort_flag) return false;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1u;
+                if (err_word) atomicCAS(err_word, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
 // 32 lanes x 16 consecutive fp32 columns -> 16 registers per thread (lane i of the warp reads
 // TMEM lane (taddr.lane + i)).  Warp w of a CTA may only touch lanes 32*(w%4) .. +31.
 __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {

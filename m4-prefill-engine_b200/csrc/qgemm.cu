@@ -30,6 +30,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -71,6 +72,7 @@ constexpr int MAX_RAW_STAGES = 6;   // packed-weight ring depth is chosen per la
 constexpr int SMEM_BYTES = 226 * 1024;  // dynamic shared memory of every launch
 constexpr int STAGES = 3;       // ring of unpacked weight tiles (one 64-element K step each)
 constexpr int MAX_B_STAGES = 4;  // ring of activation tiles: deeper, so a tile is requested three steps before its MMA
+constexpr int MAX_A_STAGES = 6, PAIR_MAX_B_STAGES = 6;   // CTA-pair launches: deeper rings of smaller stages (see qgemm_kernel)
 constexpr int A_TILE_BYTES = W_TILE * 128;
 constexpr int TMEM_COLS = 512;
 constexpr int ACC_STRIDE = 256; // tensor-memory columns per accumulator buffer
@@ -110,6 +112,7 @@ struct Params {
     uint32_t T;                  // tokens per tile (multiple of 16)
     uint32_t n_tok_tiles, n_w_tiles, k_splits, kchunks;   // kchunks: 256-element chunks per split
     uint32_t raw_stages, b_stage_bytes, b_stages;         // ring depth of packed weights; bytes of one activation stage (T*128); activation ring depth
+    uint32_t a_stages;                                    // ring depth of unpacked weight tiles (STAGES; more for CTA pairs)
     __half* Y;
     const __half* residual;
     float* partial_out;
@@ -138,9 +141,9 @@ struct Params {
 };
 
 // Packed-weight stages that fit beside the operand ring for a given activation-tile height.
-template <int FMT> inline long raw_stages_fit(uint32_t T, long xchg_bytes, uint32_t b_stages) {
+template <int FMT> inline long raw_stages_fit(uint32_t T, long xchg_bytes, uint32_t b_stages, uint32_t a_stages = STAGES) {
     const long avail = (long)SMEM_BYTES - 1024 /*alignment slack*/ - 512 /*barriers*/ - xchg_bytes -
-                       (long)STAGES * A_TILE_BYTES - (long)b_stages * T * 128;
+                       (long)a_stages * A_TILE_BYTES - (long)b_stages * T * 128;
     return avail / ((long)cdc::Codec<FMT>::ROW_BYTES * W_TILE);
 }
 // Activation ring depth: four stages when two packed-weight stages still fit beside them, else three.
@@ -446,12 +449,23 @@ __device__ __forceinline__ void row_epilogue_kv(const Params& p, uint8_t* stage,
 }
 
 // RESID: the launch adds a residual in the epilogue (its prefetch ring costs registers the plain launch should not pay for)
-template <int FMT, bool RESID>
+// PAIR: the launch runs as clusters of two CTAs whose tensor cores work on one 256-row MMA (cta_group::2).  CTA r of a
+// pair unpacks its own weight tile (rows of tile 2 i + r) into its own shared memory and loads tokens 128 r .. 128 r + 127
+// of the 256-token tile; the even CTA's MMA warp issues 256 x 256 x 16 MMAs that read A from both CTAs and each half of B
+// from the CTA that holds it, and every CTA finds the accumulator of its own 128 rows in its own tensor memory, so the
+// epilogue is that of the single-CTA kernel.  Per SM and 64-element step the MMAs then read 32 KB of shared memory instead
+// of 48 KB and TMA writes 16 KB instead of 32 KB -- with one CTA per MMA the shared-memory pipe, not the tensor pipe, bounds
+// the step (measured: tensor-core operand reads plus unpack stores and loads keep it busy 98 % of the active cycles).
+//   "full" barriers of the operand rings and the accumulator's "empty" barriers live in the even CTA: the odd CTA's unpack
+//   and epilogue warps arrive there remotely, and a relay warp forwards the completion of the odd CTA's activation loads;
+//   "empty" / accumulator-"full" arrivals are tcgen05.commit multicasts to the barrier at the same offset in both CTAs.
+template <int FMT, bool RESID, bool PAIR>
 __global__ void __launch_bounds__(Cfg<FMT>::THREADS, 1)
 qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW0,
              const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmW2, const Params p) {
     using C = Cfg<FMT>;
     using Cd = cdc::Codec<FMT>;
+    static_assert(!PAIR || (C::EPI_WARP0 > 14 && C::DQ_WARPS == 12), "the pair kernel uses the idle warp 14 as its relay");
     constexpr int ROW_BYTES = Cd::ROW_BYTES;
     constexpr int RAW_TILE_BYTES = ROW_BYTES * W_TILE;
 
@@ -461,7 +475,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     const uint32_t pad = (1024u - (ptx::smem_u32(smem_dyn) & 1023u)) & 1023u;
     uint8_t* sB = smem_dyn + pad;
     uint8_t* sA = sB + p.b_stages * p.b_stage_bytes;
-    uint8_t* sRaw = sA + STAGES * A_TILE_BYTES;
+    uint8_t* sRaw = sA + p.a_stages * A_TILE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + p.raw_stages * RAW_TILE_BYTES);
     uint64_t* raw_full = bars;
     uint64_t* raw_empty = raw_full + MAX_RAW_STAGES;
@@ -470,10 +484,10 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     // before its MMA for the load latency to stay off the critical path when the inputs are not L2-resident
     // (with a shared three-deep ring the request could only go out two steps ahead).
     uint64_t* a_full = raw_empty + MAX_RAW_STAGES;      // unpacked weight tile published (one arrival per unpack warp)
-    uint64_t* a_empty = a_full + STAGES;                // ... consumed (one tcgen05.commit)
-    uint64_t* b_full = a_empty + STAGES;                // activation tile landed (producer's arrival + TMA byte count)
-    uint64_t* b_empty = b_full + MAX_B_STAGES;          // ... consumed (one tcgen05.commit)
-    uint64_t* tm_full = b_empty + MAX_B_STAGES;
+    uint64_t* a_empty = a_full + MAX_A_STAGES;          // ... consumed (one tcgen05.commit)
+    uint64_t* b_full = a_empty + MAX_A_STAGES;          // activation tile landed (producer's arrival + TMA byte count)
+    uint64_t* b_empty = b_full + PAIR_MAX_B_STAGES;     // ... consumed (one tcgen05.commit)
+    uint64_t* tm_full = b_empty + PAIR_MAX_B_STAGES;
     uint64_t* tm_empty = tm_full + 2;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tm_empty + 2);
     volatile uint32_t* abort_flag = tmem_holder + 1;
@@ -481,24 +495,40 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
     float4* xchg = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(bars) + 512);   // epilogue exchange area (16-byte aligned)
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t total_tiles = p.n_w_tiles * p.n_tok_tiles * p.k_splits;
+    const uint32_t pair_rank = PAIR ? ptx::cluster_ctarank() : 0u;     // 0: the CTA whose MMA warp issues for the pair
+    // work items: output tiles (x K splits), or for a pair launch pairs of weight tiles that share a token tile
+    const uint32_t total_tiles = PAIR ? (p.n_w_tiles / 2u) * p.n_tok_tiles : p.n_w_tiles * p.n_tok_tiles * p.k_splits;
+    const uint32_t first_tile = PAIR ? (blockIdx.x >> 1) : blockIdx.x, tile_stride = PAIR ? (gridDim.x >> 1) : gridDim.x;
+    auto tile_of = [&](uint32_t idx) {
+        if (!PAIR) return decode_tile(idx, p);
+        Tile t;
+        const uint32_t n_wp = p.n_w_tiles / 2u;
+        t.ks = 0u; t.wt = 2u * (idx % n_wp) + pair_rank; t.tt = idx / n_wp;
+        if (p.tt_shift) { t.tt += p.tt_shift; if (t.tt >= p.n_tok_tiles) t.tt -= p.n_tok_tiles; }
+        t.id = t.tt * p.n_w_tiles + t.wt;
+        return t;
+    };
     const uint32_t ksteps = p.kchunks * (uint32_t)C::SUBS;
+    const uint32_t b_rows = PAIR ? p.T / 2u : p.T;                      // token rows of the activation tile this CTA loads
 
     if (threadIdx.x == 0) {
+        // pair launch: the even CTA's "full" barriers also count the odd CTA's arrivals (unpack warps, relay, epilogue warps)
+        const uint32_t both = (PAIR && pair_rank == 0u) ? 2u : 1u;
         for (int i = 0; i < MAX_RAW_STAGES; i++) { ptx::mbar_init(&raw_full[i], 1); ptx::mbar_init(&raw_empty[i], C::DQ_THREADS / 32); }
-        for (int i = 0; i < STAGES; i++) { ptx::mbar_init(&a_full[i], C::FILL_THREADS / 32); ptx::mbar_init(&a_empty[i], 1); }
-        for (int i = 0; i < MAX_B_STAGES; i++) { ptx::mbar_init(&b_full[i], 1); ptx::mbar_init(&b_empty[i], 1); }
-        for (int i = 0; i < 2; i++) { ptx::mbar_init(&tm_full[i], 1); ptx::mbar_init(&tm_empty[i], 4); }
+        for (int i = 0; i < MAX_A_STAGES; i++) { ptx::mbar_init(&a_full[i], both * (C::FILL_THREADS / 32)); ptx::mbar_init(&a_empty[i], 1); }
+        for (int i = 0; i < PAIR_MAX_B_STAGES; i++) { ptx::mbar_init(&b_full[i], both); ptx::mbar_init(&b_empty[i], 1); }
+        for (int i = 0; i < 2; i++) { ptx::mbar_init(&tm_full[i], 1); ptx::mbar_init(&tm_empty[i], both * 4u); }
         *abort_flag = 0u;
         *last_flag = 0u;
         ptx::fence_barrier_init();
     }
     if (warp == 2) {
-        ptx::tmem_alloc(tmem_holder, TMEM_COLS);
-        ptx::tmem_relinquish();
+        if (PAIR) { ptx::tmem_alloc_pair(tmem_holder, TMEM_COLS); ptx::tmem_relinquish_pair(); }
+        else { ptx::tmem_alloc(tmem_holder, TMEM_COLS); ptx::tmem_relinquish(); }
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if (PAIR) ptx::cluster_sync_all();        // both CTAs' barriers are initialised before either arrives on the other's
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
     // Everything above touched only this CTA's shared and tensor memory; global memory (inputs another kernel may
@@ -523,8 +553,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         uint32_t rs = 0, rph = 0, wtr = 0;
         (void)wtr;
         bool ok = true;
-        for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
-            const Tile t = decode_tile(idx, p);
+        for (uint32_t idx = first_tile; ok && idx < total_tiles; idx += tile_stride) {
+            const Tile t = tile_of(idx);
             for (uint32_t kc = 0; kc < p.kchunks; kc++) {
                 ok = __all_sync(0xffffffffu, ptx::mbar_wait<64>(&raw_empty[rs], rph ^ 1u, abort_flag, p.err, 101));
                 if (!ok) break;
@@ -557,34 +587,48 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         uint32_t bs = 0, bph = 0, xtr = 0;
         (void)xtr;
         bool ok = true;
-        for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
-            const Tile t = decode_tile(idx, p);
+        for (uint32_t idx = first_tile; ok && idx < total_tiles; idx += tile_stride) {
+            const Tile t = tile_of(idx);
             const uint32_t k0 = t.ks * p.kchunks * (uint32_t)C::CHUNK;
             for (uint32_t ks = 0; ks < ksteps; ks++) {
                 ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&b_empty[bs], bph ^ 1u, abort_flag, p.err, 102));
                 if (!ok) break;
                 if (lane == 0) {
                     QTR(1, xtr, 0);
-                    ptx::mbar_arrive_expect_tx(&b_full[bs], p.T * 128u);
-                    ptx::tma_load_2d(sB + bs * p.b_stage_bytes, &tmX, &b_full[bs], (int)(k0 + ks * KSTEP), (int)(t.tt * p.T));
+                    ptx::mbar_arrive_expect_tx(&b_full[bs], b_rows * 128u);
+                    ptx::tma_load_2d(sB + bs * p.b_stage_bytes, &tmX, &b_full[bs], (int)(k0 + ks * KSTEP), (int)(t.tt * p.T + pair_rank * b_rows));
                     QTR(1, xtr, 1); xtr++;
                 }
                 __syncwarp();
                 if (++bs == p.b_stages) { bs = 0; bph ^= 1u; }
             }
         }
-    } else if (warp == 2) {
+    } else if (PAIR && pair_rank == 1u && warp == 14u) {
+        // ---------------- relay (odd CTA): activation tile landed here -> one arrival on the even CTA's barrier ----------------
+        uint32_t bs = 0, bph = 0;
+        bool ok = true;
+        for (uint32_t idx = first_tile; ok && idx < total_tiles; idx += tile_stride) {
+            for (uint32_t ks = 0; ks < ksteps; ks++) {
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait(&b_full[bs], bph, abort_flag, p.err, 109));
+                if (!ok) break;
+                if (lane == 0) ptx::mbar_arrive_cluster(&b_full[bs], 0u);
+                __syncwarp();
+                if (++bs == p.b_stages) { bs = 0; bph ^= 1u; }
+            }
+        }
+    } else if (warp == 2 && (!PAIR || pair_rank == 0u)) {
         // ---------------- MMA issuer ----------------
-        const uint32_t idesc = ptx::umma_idesc_f16(W_TILE, p.T);
+        const uint32_t idesc = ptx::umma_idesc_f16(PAIR ? 2 * W_TILE : W_TILE, p.T);
         // operand descriptors differ between stages only in the 14-bit start-address field
         const uint64_t desc_hi = ptx::umma_desc_k_sw128(0u);
         const uint32_t a_lo0 = (ptx::smem_u32(sA) & 0x3FFFFu) >> 4, b_lo0 = (ptx::smem_u32(sB) & 0x3FFFFu) >> 4;
         uint32_t st = 0, sph = 0, bst = 0, bsph = 0, it = 0, mtr = 0;
         (void)mtr;
         bool ok = true;
-        for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x, it++) {
+        for (uint32_t idx = first_tile; ok && idx < total_tiles; idx += tile_stride, it++) {
             const uint32_t buf = it & 1u;
-            ok = __all_sync(0xffffffffu, ptx::mbar_wait(&tm_empty[buf], ((it >> 1) & 1u) ^ 1u, abort_flag, p.err, 103));
+            ok = __all_sync(0xffffffffu, PAIR ? ptx::mbar_wait_cluster(&tm_empty[buf], ((it >> 1) & 1u) ^ 1u, abort_flag, p.err, 103)
+                                                   : ptx::mbar_wait(&tm_empty[buf], ((it >> 1) & 1u) ^ 1u, abort_flag, p.err, 103));
             if (!ok) break;
             ptx::tc_fence_after_sync();
             if (lane == 0) QTRC(2, 200u + it, 0);
@@ -593,26 +637,39 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                 // (no tcgen05 fence here: the stage was written by TMA and by generic stores that were
                 // followed by fence.proxy.async; the mbarrier acquire orders them before the MMA's reads)
                 // (the vote keeps the warp converged for elect.sync even if a wait gives up)
-                ok = __all_sync(0xffffffffu, ptx::mbar_wait(&a_full[st], sph, abort_flag, p.err, 104) &&
-                                                 ptx::mbar_wait(&b_full[bst], bsph, abort_flag, p.err, 105));
+                if (PAIR) ok = __all_sync(0xffffffffu, ptx::mbar_wait_cluster(&a_full[st], sph, abort_flag, p.err, 104) &&
+                                                           ptx::mbar_wait_cluster(&b_full[bst], bsph, abort_flag, p.err, 105));
+                else ok = __all_sync(0xffffffffu, ptx::mbar_wait(&a_full[st], sph, abort_flag, p.err, 104) &&
+                                                      ptx::mbar_wait(&b_full[bst], bsph, abort_flag, p.err, 105));
                 if (!ok) break;
                 if (ptx::elect_one()) {
                     QTR(2, mtr, 2);
                     const uint64_t bdesc = desc_hi | (uint64_t)(b_lo0 + bst * (p.b_stage_bytes >> 4));
                     const uint64_t adesc = desc_hi | (uint64_t)(a_lo0 + st * (A_TILE_BYTES >> 4));
                     const uint32_t dcol = tmem_base + buf * ACC_STRIDE;
+                    if (PAIR) {
 #pragma unroll
-                    for (int kk = 0; kk < KSTEP / 16; kk++)
-                        ptx::umma_f16_ss(dcol, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | (uint32_t)kk) != 0u);
-                    ptx::umma_commit(&a_empty[st]);
-                    ptx::umma_commit(&b_empty[bst]);
+                        for (int kk = 0; kk < KSTEP / 16; kk++)
+                            ptx::umma_pair_f16_ss(dcol, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | (uint32_t)kk) != 0u);
+                        ptx::umma_pair_commit(&a_empty[st]);
+                        ptx::umma_pair_commit(&b_empty[bst]);
+                    } else {
+#pragma unroll
+                        for (int kk = 0; kk < KSTEP / 16; kk++)
+                            ptx::umma_f16_ss(dcol, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | (uint32_t)kk) != 0u);
+                        ptx::umma_commit(&a_empty[st]);
+                        ptx::umma_commit(&b_empty[bst]);
+                    }
                     QTR(2, mtr, 3); mtr++;
                 }
                 __syncwarp();
-                if (++st == STAGES) { st = 0; sph ^= 1u; }
+                if (++st == p.a_stages) { st = 0; sph ^= 1u; }
                 if (++bst == p.b_stages) { bst = 0; bsph ^= 1u; }
             }
-            if (ok && ptx::elect_one()) { ptx::umma_commit(&tm_full[buf]); QTRC(2, 200u + it, 1); }   // same lane as the MMAs
+            if (ok && ptx::elect_one()) {      // same lane as the MMAs
+                if (PAIR) ptx::umma_pair_commit(&tm_full[buf]); else ptx::umma_commit(&tm_full[buf]);
+                QTRC(2, 200u + it, 1);
+            }
             __syncwarp();
         }
     } else if (pre_epi && wq != 2u && uw < (uint32_t)C::DQ_WARPS) {
@@ -626,10 +683,11 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         const uint32_t mrow_in_tile = p.swiglu ? (row & 63u) : row;
         const uint32_t row_off = (row >> 3) * 1024 + (row & 7) * 128, xr = row & 7;
         uint32_t rs = 0, rph = 0, kn = 0;                     // kn: running 64-element step of this CTA
-        uint32_t km = 0, own_ph = 0;                          // (kn / 4) % STAGES; phase of the group's own operand stage
+        uint32_t km = 0, own_ph = 0;                          // (kn / 4) % STAGES; phase of the group's next operand stage
+        uint32_t own_st = grp;                                // ... and that stage: the group's steps g, g + 3, ... use stages (g + 3 j) % a_stages
         bool ok = true;
-        for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
-            const Tile t = decode_tile(idx, p);
+        for (uint32_t idx = first_tile; ok && idx < total_tiles; idx += tile_stride) {
+            const Tile t = tile_of(idx);
             // META_WORDS / 2 words of scales and as many of biases per chunk: one group per 64 elements (4 words)
             // or per 32 elements (8 words); the bias plane follows the scale plane
             constexpr int MW = Cd::META_WORDS > 0 ? Cd::META_WORDS : 4;
@@ -684,7 +742,11 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                         Cd::dequant64(r, s, o, meta);
                         if (row == 0) QTR(4 + grp, kn + s, 0);
                         uint32_t as, aph;
-                        if (G == STAGES) { as = grp; aph = own_ph; own_ph ^= 1u; }     // the group's own stage, phase toggles per use
+                        if (G == STAGES) {      // three stages: always the group's own; deeper rings (CTA pairs): every third stage in turn
+                            as = own_st; aph = own_ph;
+                            own_st += (uint32_t)STAGES;
+                            if (own_st >= p.a_stages) { own_st -= p.a_stages; own_ph ^= 1u; }
+                        }
                         else { const uint32_t step = kn + s; as = step % STAGES; aph = (step / STAGES) & 1u; }
                         ok = __all_sync(0xffffffffu, ok && ptx::mbar_wait<32>(&a_empty[as], aph ^ 1u, abort_flag, p.err, 107));
                         if (row == 0) QTR(4 + grp, kn + s, 1);
@@ -695,7 +757,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
                                 *reinterpret_cast<uint4*>(dst + ((c ^ xr) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
                             ptx::fence_proxy_async_smem();
                             __syncwarp();                      // every lane's stores are fenced; one arrival per warp
-                            if (lane == 0) ptx::mbar_arrive(&a_full[as]);
+                            if (lane == 0) { if (PAIR && pair_rank == 1u) ptx::mbar_arrive_cluster(&a_full[as], 0u); else ptx::mbar_arrive(&a_full[as]); }
                             if (row == 0) QTR(4 + grp, kn + s, 2);
                         }
                     }
@@ -723,7 +785,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         // owner -- and adds its counts to the rank-wide counters; the warp that completes an owner's count (tiles x 4
         // epilogue warps) raises this rank's arrival flag on that owner.  Counting per warp needs no barrier among the
         // epilogue warps, so a warp that gave up on a wait cannot strand the others.
-        uint32_t* sc_cnt = reinterpret_cast<uint32_t*>(bars) + 64 + q * 8;      // bytes 256..383 of the barrier block
+        uint32_t* sc_cnt = reinterpret_cast<uint32_t*>(bars) + 96 + q * 8;      // bytes 384..511 of the barrier block
         if (p.scatter.world && lane < 8u) sc_cnt[lane] = 0u;
         __syncwarp();
         bool sc_ok = true;
@@ -743,8 +805,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             }
             __syncwarp();
         };
-        for (uint32_t idx = blockIdx.x; idx < total_tiles; idx += gridDim.x, it++) {
-            const Tile t = decode_tile(idx, p);
+        for (uint32_t idx = first_tile; idx < total_tiles; idx += tile_stride, it++) {
+            const Tile t = tile_of(idx);
             const uint32_t buf = it & 1u;
             if (p.residual && p.k_splits == 1u) {
                 // The epilogue warps idle through the tile's main loop: use that time to pull the residual tile
@@ -923,7 +985,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&tm_empty[buf]);
+            if (lane == 0) { if (PAIR && pair_rank == 1u) ptx::mbar_arrive_cluster(&tm_empty[buf], 0u); else ptx::mbar_arrive(&tm_empty[buf]); }
             if (et == 0) QTRC(6, it, 1);
             if (p.k_splits > 1) {
                 // count this partial tile in; the CTA that completes the count adds the partial tiles after the
@@ -950,9 +1012,12 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         while (clock64() - t0 < 4000000LL) { }
         __syncthreads();
     }
+    // pair launch: neither CTA may leave (or free tensor memory) while the other's MMAs, commits or arrivals can still
+    // reach it; every thread of both CTAs gets here on every path, also after a wait has given up
+    if (PAIR) ptx::cluster_sync_all();
     if (warp == 2) {
         ptx::tc_fence_after_sync();
-        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+        if (PAIR) ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS); else ptx::tmem_dealloc(tmem_base, TMEM_COLS);
     }
     if (p.k_splits > 1 && *last_flag && !*abort_flag) {
         // Split-K fix-up by the whole CTA: the partial tiles of this output tile are complete (this CTA's arrival
@@ -1188,6 +1253,10 @@ Plan make_plan(const GemmArgs& a) {
     return pl;
 }
 
+// CTA pairs need the idle warp 14 as their relay: the codecs with three unpack groups (twelve unpack warps) have it; the two
+// with two groups are bound by their unpack arithmetic and would gain nothing.
+template <int FMT> constexpr bool pair_capable() { return Cfg<FMT>::DQ_WARPS == 12 && Cfg<FMT>::EPI_WARP0 > 14; }
+
 // The dynamic shared-memory attribute is per device: set once for every device a launch (or prepare_device) sees.
 template <int FMT>
 cudaError_t set_kernel_attributes() {
@@ -1197,10 +1266,40 @@ cudaError_t set_kernel_attributes() {
     cudaGetDevice(&dev);
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && (done_mask >> dev) & 1u) return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(qgemm_kernel<FMT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(qgemm_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(qgemm_kernel<FMT, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(qgemm_kernel<FMT, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if constexpr (pair_capable<FMT>()) {
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(qgemm_kernel<FMT, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(qgemm_kernel<FMT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    }
     if (e == cudaSuccess && dev >= 0 && dev < 64) done_mask |= 1ull << dev;
     return e;
+}
+
+bool g_pair_enabled = true;      // testing hook: off keeps every launch on one CTA per MMA
+int g_last_pair = 0;             // CTA pairs of the last launch (0: it ran with one CTA per MMA)
+
+// Clusters of two CTAs (one CTA per SM) that can be resident at once: the pair launch's grid.  Asked of the runtime once
+// per format; half the SM count where the query fails.
+template <int FMT> int max_pairs() {
+    static int n = 0;
+    if (n == 0) {
+        if constexpr (pair_capable<FMT>()) {
+            cudaLaunchConfig_t cfg;
+            memset(&cfg, 0, sizeof(cfg));
+            cfg.gridDim = dim3(2 * (unsigned)sm_count()); cfg.blockDim = dim3(Cfg<FMT>::THREADS); cfg.dynamicSmemBytes = SMEM_BYTES;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+            cfg.attrs = at; cfg.numAttrs = 1;
+            int c = 0;
+            if (cudaOccupancyMaxActiveClusters(&c, qgemm_kernel<FMT, false, true>, &cfg) == cudaSuccess && c > 0) n = c;
+            else { cudaGetLastError(); n = sm_count() / 2; }
+        } else n = sm_count() / 2;
+        if (n > sm_count() / 2) n = sm_count() / 2;
+        if (n < 1) n = 1;
+    }
+    return n;
 }
 
 template <int FMT>
@@ -1209,8 +1308,14 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     const Plan pl = make_plan(a);
     const int rb = cdc::Codec<FMT>::ROW_BYTES;
     const uint64_t w_row_bytes = (uint64_t)(a.K / C::CHUNK) * rb;
+    // CTA pairs (cta_group::2): whole 256-token tiles, no K split, weight tiles in pairs.  Not for SwiGLU launches: their
+    // epilogue (two accumulators per output, a SiLU each) takes about as long as a tile's main loop, so a faster main loop
+    // gains nothing and waiting for both CTAs' epilogues costs a little (measured 405-440 us against 390 us at the 8B shape).
+    const bool pair = pair_capable<FMT>() && g_pair_enabled && pl.k_splits == 1 && pl.T == 256u && pl.n_w_tiles % 2u == 0u && !a.W1;
+    const uint32_t t_cta = pair ? pl.T / 2u : pl.T;             // token rows of the activation tile one CTA loads
+    g_last_pair = pair ? 1 : 0;
     CUtensorMap tmX, tmW0, tmW1, tmW2;
-    if (!make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.X, a.K, a.M, (uint64_t)a.K * 2, KSTEP, pl.T,
+    if (!make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.X, a.K, a.M, (uint64_t)a.K * 2, KSTEP, t_cta,
                      CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
     const CUtensorMapSwizzle wsw = cdc::Codec<FMT>::RAW_SWIZZLE_128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;
@@ -1269,8 +1374,31 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     for (int gi = 0; gi < 3; gi++) p.grp_post[gi] = (uint32_t)gi <= a.n_extra ? a.post[gi] : 0u;
     p.row_epi = row_ok ? 1u : 0u;
     const long xchg_bytes = a.W1 ? XCHG_BYTES : (row_ok ? ((partial_f32 || a.residual) ? XCHG_BYTES_F32 : XCHG_BYTES) : 0);
-    p.raw_stages = raw_stages_for<FMT>(pl.T, xchg_bytes); p.b_stage_bytes = pl.T * 128u;
-    p.b_stages = b_stages_for<FMT>(pl.T, xchg_bytes);
+    p.b_stage_bytes = t_cta * 128u;
+    p.a_stages = STAGES;
+    if (pair) {
+        // A stage is handed over between the two CTAs of a pair (remote arrival, multicast commit), which adds latency to
+        // every turn of a ring, and an activation stage is only 16 KB: deeper rings, as far as two packed stages still fit
+        // beside them.  Measured at the 8B shapes (Q4_0, M = 2048): 6 activation + 4 weight stages 54.0 / 171 us
+        // (K = 4096 / 14336), 6 + 5: 54.9 / 183, 4 + 4: 55.1 / 178, 4 + 3: 55.6 / 190; one CTA per MMA: 59.5 / 194.
+        static const uint32_t choices[][2] = {{6, 4}, {5, 4}, {4, 4}, {4, 3}};
+        p.b_stages = 4; p.a_stages = 3;
+        for (const auto& c : choices)
+            if (raw_stages_fit<FMT>(t_cta, xchg_bytes, c[0], c[1]) >= 2) { p.b_stages = c[0]; p.a_stages = c[1]; break; }
+        // tuning aid: B200_PAIR_STAGES="<activation stages>,<weight stages>" overrides the choice where it fits
+        static const char* ov = getenv("B200_PAIR_STAGES");
+        if (ov) {
+            unsigned ob = 0, oa = 0;
+            if (sscanf(ov, "%u,%u", &ob, &oa) == 2 && ob >= 2 && ob <= (unsigned)PAIR_MAX_B_STAGES && oa >= 3 && oa <= (unsigned)MAX_A_STAGES &&
+                raw_stages_fit<FMT>(t_cta, xchg_bytes, ob, oa) >= 1) { p.b_stages = ob; p.a_stages = oa; }
+        }
+        long n = raw_stages_fit<FMT>(t_cta, xchg_bytes, p.b_stages, p.a_stages);
+        p.raw_stages = (uint32_t)(n < 1 ? 1 : (n > MAX_RAW_STAGES ? MAX_RAW_STAGES : n));
+        if (raw_stages_fit<FMT>(t_cta, xchg_bytes, p.b_stages, p.a_stages) < 1) return cudaErrorInvalidValue;
+    } else {
+        p.raw_stages = raw_stages_for<FMT>(t_cta, xchg_bytes);
+        p.b_stages = b_stages_for<FMT>(t_cta, xchg_bytes);
+    }
     p.Y = (__half*)a.Y; p.residual = (const __half*)a.residual; p.partial_out = a.partial_out;
     p.scatter = a.scatter;
     p.groups = 1u + a.n_extra;
@@ -1309,13 +1437,27 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(C::THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
+    if constexpr (pair_capable<FMT>()) {
+        if (pair) {
+            // one cluster of two CTAs per pair of SMs; a pair walks pairs of weight tiles that share a token tile
+            const uint32_t pair_tiles = (pl.n_w_tiles / 2u) * pl.n_tok_tiles;
+            const uint32_t pairs = pair_tiles < (uint32_t)max_pairs<FMT>() ? pair_tiles : (uint32_t)max_pairs<FMT>();
+            cfg.gridDim = dim3(2u * pairs);
+            g_last_pair = (int)pairs;
+            attr[1].id = cudaLaunchAttributeClusterDimension;
+            attr[1].val.clusterDim.x = 2; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
+            cfg.numAttrs = 2;
+            if (a.residual) return cudaLaunchKernelEx(&cfg, qgemm_kernel<FMT, true, true>, tmX, tmW0, tmW1, tmW2, p);
+            return cudaLaunchKernelEx(&cfg, qgemm_kernel<FMT, false, true>, tmX, tmW0, tmW1, tmW2, p);
+        }
+    }
     // (the split-K fix-up adds the residual outside the epilogue loop: only unsplit residual launches need the RESID build)
-    if (a.residual && pl.k_splits == 1) return cudaLaunchKernelEx(&cfg, qgemm_kernel<FMT, true>, tmX, tmW0, tmW1, tmW2, p);
-    return cudaLaunchKernelEx(&cfg, qgemm_kernel<FMT, false>, tmX, tmW0, tmW1, tmW2, p);
+    if (a.residual && pl.k_splits == 1) return cudaLaunchKernelEx(&cfg, qgemm_kernel<FMT, true, false>, tmX, tmW0, tmW1, tmW2, p);
+    return cudaLaunchKernelEx(&cfg, qgemm_kernel<FMT, false, false>, tmX, tmW0, tmW1, tmW2, p);
 }
 
 cudaError_t dispatch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t s) {
@@ -1389,5 +1531,7 @@ cudaError_t launch(const GemmArgs& a, const Workspace& ws, cudaStream_t stream) 
 }
 
 int last_launch_count() { return g_last_launches; }
+void set_pair_kernel_enabled(bool on) { g_pair_enabled = on; }
+int last_launch_pairs() { return g_last_pair; }
 
 }  // namespace qg

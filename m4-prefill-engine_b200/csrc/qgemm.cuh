@@ -75,5 +75,7 @@ void set_small_kernel_enabled(int mode);     // testing hook: 0 routes those sha
                                              // 2 takes every shape the kernel can compute (any number of token tiles)
 // Number of kernels the last launch() enqueued (1, or 2 with the generic tail) -- for launch accounting.
 int last_launch_count();
+void set_pair_kernel_enabled(bool on);        // testing hook: off keeps every launch of the persistent kernel on one CTA per MMA
+int last_launch_pairs();                      // CTA pairs (cta_group::2) of the last persistent-kernel launch, 0 if it ran without
 
 }  // namespace qg
