@@ -343,6 +343,38 @@ def test_8b_projection_m2048(bridge, fmt):
     assert np.array_equal(Yp.view(np.uint16), Y[perm].view(np.uint16))
 
 
+@pytest.mark.parametrize("fmt", [o.Q4_0, o.MLX_4BIT_PLANAR, o.TERNARY_ROW, o.PRISM_Q2_0])
+def test_cta_pair_launch_is_bit_identical(bridge, fmt):
+    """Launches with whole 256-token tiles, no K split and an even number of weight tiles run as CTA pairs (one 256-row MMA
+    over two SMs, operands handed over between the two CTAs): the same products in the same order as with one CTA per MMA,
+    so the outputs must agree bit for bit -- plain, with a fused residual, head-major, and with a ragged last token tile."""
+    L = bridge.lib
+    M, K, N, D = 1000, 1024, 1536, 128          # 4 token tiles (the last one ragged) x 12 weight tiles
+    X, W = o.baseline_inputs(fmt, M, K, N, 21)
+    R = (np.random.default_rng(3).standard_normal((M, N)) * 0.5).astype(np.float16)
+    outs = {}
+    for pair in (1, 0):
+        L.b200_bridge_enable_pair_kernel(pair)
+        try:
+            a = run_gemm(bridge, fmt, X, W, N, ex=True)
+            used = L.b200_bridge_last_launch_pair()
+            b = run_gemm(bridge, fmt, X, W, N, residual=R)
+            c = run_gemm(bridge, fmt, X, W, N, layout=1, H=N // D, D=D)
+        finally:
+            L.b200_bridge_enable_pair_kernel(1)
+        assert (used > 0) == bool(pair)
+        outs[pair] = (a, b, c)
+    for x, y in zip(outs[0], outs[1]):
+        assert np.array_equal(x.view(np.uint16), y.view(np.uint16))
+    gold = o.gemm_f64(fmt, X, W, N)
+    check(outs[1][0], gold, f"CTA pairs fmt {fmt} M={M}", dev_gold=device_weight_gold(fmt, X, W, N))
+    check(outs[1][1], gold + R.astype(np.float64), f"CTA pairs fmt {fmt} M={M} + residual")
+    # an odd number of weight tiles keeps one CTA per MMA
+    X2, W2 = o.baseline_inputs(fmt, 512, K, 384, 22)
+    check(run_gemm(bridge, fmt, X2, W2, 384, ex=True), o.gemm_f64(fmt, X2, W2, 384), f"fmt {fmt} 3 weight tiles")
+    assert L.b200_bridge_last_launch_pair() == 0
+
+
 @pytest.mark.parametrize("fmt", ALL_CODECS)
 def test_few_token_kernels_agree(bridge, fmt):
     """The cluster kernel (weights unpacked into tensor memory, K split over a thread-block cluster, partial tiles summed by
