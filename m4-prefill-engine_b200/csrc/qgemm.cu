@@ -1308,10 +1308,10 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     const Plan pl = make_plan(a);
     const int rb = cdc::Codec<FMT>::ROW_BYTES;
     const uint64_t w_row_bytes = (uint64_t)(a.K / C::CHUNK) * rb;
-    // CTA pairs (cta_group::2): whole 256-token tiles, no K split, weight tiles in pairs.  Not for SwiGLU launches: their
+    // CTA pairs (cta_group::2): token tiles that halve into whole 16-row groups, no K split, weight tiles in pairs.  Not for SwiGLU launches: their
     // epilogue (two accumulators per output, a SiLU each) takes about as long as a tile's main loop, so a faster main loop
     // gains nothing and waiting for both CTAs' epilogues costs a little (measured 405-440 us against 390 us at the 8B shape).
-    const bool pair = pair_capable<FMT>() && g_pair_enabled && pl.k_splits == 1 && pl.T == 256u && pl.n_w_tiles % 2u == 0u && !a.W1;
+    const bool pair = pair_capable<FMT>() && g_pair_enabled && pl.k_splits == 1 && pl.T >= 128u && pl.T % 32u == 0u && pl.n_w_tiles % 2u == 0u && !a.W1;
     const uint32_t t_cta = pair ? pl.T / 2u : pl.T;             // token rows of the activation tile one CTA loads
     g_last_pair = pair ? 1 : 0;
     CUtensorMap tmX, tmW0, tmW1, tmW2;

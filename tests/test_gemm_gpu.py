@@ -345,11 +345,11 @@ def test_8b_projection_m2048(bridge, fmt):
 
 @pytest.mark.parametrize("fmt", [o.Q4_0, o.MLX_4BIT_PLANAR, o.TERNARY_ROW, o.PRISM_Q2_0])
 def test_cta_pair_launch_is_bit_identical(bridge, fmt):
-    """Launches with whole 256-token tiles, no K split and an even number of weight tiles run as CTA pairs (one 256-row MMA
+    """Launches with token tiles of 128 to 256 rows, no K split and an even number of weight tiles run as CTA pairs (one 256-row MMA
     over two SMs, operands handed over between the two CTAs): the same products in the same order as with one CTA per MMA,
     so the outputs must agree bit for bit -- plain, with a fused residual, head-major, and with a ragged last token tile."""
     L = bridge.lib
-    M, K, N, D = 1000, 1024, 1536, 128          # 4 token tiles (the last one ragged) x 12 weight tiles
+    M, K, N, D = 2000, 1024, 1536, 128          # 8 token tiles (the last one ragged) x 12 weight tiles: above the SM count, no K split
     X, W = o.baseline_inputs(fmt, M, K, N, 21)
     R = (np.random.default_rng(3).standard_normal((M, N)) * 0.5).astype(np.float16)
     outs = {}
@@ -369,9 +369,12 @@ def test_cta_pair_launch_is_bit_identical(bridge, fmt):
     gold = o.gemm_f64(fmt, X, W, N)
     check(outs[1][0], gold, f"CTA pairs fmt {fmt} M={M}", dev_gold=device_weight_gold(fmt, X, W, N))
     check(outs[1][1], gold + R.astype(np.float64), f"CTA pairs fmt {fmt} M={M} + residual")
-    # an odd number of weight tiles keeps one CTA per MMA
-    X2, W2 = o.baseline_inputs(fmt, 512, K, 384, 22)
-    check(run_gemm(bridge, fmt, X2, W2, 384, ex=True), o.gemm_f64(fmt, X2, W2, 384), f"fmt {fmt} 3 weight tiles")
+    # narrower token tiles (7 of 224 rows) pair up as well; an odd number of weight tiles keeps one CTA per MMA
+    X2, W2 = o.baseline_inputs(fmt, 1560, K, 2048, 22)
+    check(run_gemm(bridge, fmt, X2, W2, 2048, ex=True), o.gemm_f64(fmt, X2, W2, 2048), f"CTA pairs fmt {fmt} M=1560")
+    assert L.b200_bridge_last_launch_pair() > 0
+    X3, W3 = o.baseline_inputs(fmt, 2048, K, 2432, 23)
+    check(run_gemm(bridge, fmt, X3, W3, 2432, ex=True), o.gemm_f64(fmt, X3, W3, 2432), f"fmt {fmt} 19 weight tiles")
     assert L.b200_bridge_last_launch_pair() == 0
 
 
