@@ -59,7 +59,8 @@ FORMATS = {"q4_0": 0, "mlx_4bit": 1, "q4_k": 2, "ternary_1_58": 3, "var_rate_aff
 FMT_NAME = {v: k for k, v in FORMATS.items()}
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, only for the (format, M) pairs that have a committed
 # ncu summary (K = N = 4096); every other row reports traffic null
-NCU_TRAFFIC = {("q4_0", 2048): (26.4e6, "profiles/qgemm_q4_0_m2048.md"), ("q4_0", 33): (9.78e6, "profiles/qgemm_q4_0_m33.md")}
+NCU_TRAFFIC = {("q4_0", 2048): (26.3e6, "profiles/qgemm_q4_0_m2048.md"), ("q4_0", 33): (9.78e6, "profiles/qgemm_small_q4_0_m33.md"),
+               ("var_rate_affine", 2048): (27.4e6, "profiles/qgemm_var_rate_m2048.md")}
 LAYER = dict(M=2048, K=4096, H=32, Hkv=8, D=128, F=14336)
 TOL = 1.0 / 128.0
 
