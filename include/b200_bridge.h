@@ -148,7 +148,7 @@ void b200_bridge_force_generic(int on);
 void b200_bridge_enable_small_kernel(int on);
 /* Testing hook: 0 keeps the persistent projection kernel on one CTA per MMA; != 0 restores the default, CTA pairs
  * (tcgen05 cta_group::2: one 256-row MMA over two SMs) wherever a launch has token tiles of 128 to 256 rows (a multiple of
- * 32), no K split, an even number of weight tiles and no SwiGLU epilogue.  b200_bridge_last_launch_pair returns the number of CTA pairs of the last such launch (0: none). */
+ * 32), no K split and an even number of weight tiles.  b200_bridge_last_launch_pair returns the number of CTA pairs of the last such launch (0: none). */
 void b200_bridge_enable_pair_kernel(int on);
 int b200_bridge_last_launch_pair(void);
 /* Up to three projections of the same activations in one launch (the Q, K and V projections of a layer): Y[i] =

@@ -1277,6 +1277,7 @@ cudaError_t set_kernel_attributes() {
 }
 
 bool g_pair_enabled = true;      // testing hook: off keeps every launch on one CTA per MMA
+bool pair_swiglu() { static const char* e = getenv("B200_PAIR_SWIGLU"); return !(e && e[0] == '0'); }   // tuning aid: B200_PAIR_SWIGLU=0 keeps SwiGLU launches on one CTA per MMA
 int g_last_pair = 0;             // CTA pairs of the last launch (0: it ran with one CTA per MMA)
 
 // Clusters of two CTAs (one CTA per SM) that can be resident at once: the pair launch's grid.  Asked of the runtime once
@@ -1308,10 +1309,9 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     const Plan pl = make_plan(a);
     const int rb = cdc::Codec<FMT>::ROW_BYTES;
     const uint64_t w_row_bytes = (uint64_t)(a.K / C::CHUNK) * rb;
-    // CTA pairs (cta_group::2): token tiles that halve into whole 16-row groups, no K split, weight tiles in pairs.  Not for SwiGLU launches: their
-    // epilogue (two accumulators per output, a SiLU each) takes about as long as a tile's main loop, so a faster main loop
-    // gains nothing and waiting for both CTAs' epilogues costs a little (measured 405-440 us against 390 us at the 8B shape).
-    const bool pair = pair_capable<FMT>() && g_pair_enabled && pl.k_splits == 1 && pl.T >= 128u && pl.T % 32u == 0u && pl.n_w_tiles % 2u == 0u && !a.W1;
+    // CTA pairs (cta_group::2): token tiles that halve into whole 16-row groups, no K split, weight tiles in pairs.
+    // (SwiGLU launches included: 352-372 us against 380-392 us at the 8B shape, the layer 0.75 ms against 0.80 ms.)
+    const bool pair = pair_capable<FMT>() && g_pair_enabled && pl.k_splits == 1 && pl.T >= 128u && pl.T % 32u == 0u && pl.n_w_tiles % 2u == 0u && (!a.W1 || pair_swiglu());
     const uint32_t t_cta = pair ? pl.T / 2u : pl.T;             // token rows of the activation tile one CTA loads
     g_last_pair = pair ? 1 : 0;
     CUtensorMap tmX, tmW0, tmW1, tmW2;
