@@ -244,7 +244,7 @@ template <> struct Codec<QUANT_TERNARY_1_58> : CodecDefaults {
 // ---- EXL3-style codebook, 144 B / 256 (quant_router_kernels.metal:368-411; gold :342-389) ---------
 template <> struct Codec<QUANT_EXL3> : CodecDefaults {
     static constexpr int ROW_BYTES = 144;
-    static constexpr int GROUPS = 2;      // unpack warp groups per matrix in the projection kernel
+    static constexpr int GROUPS = 2;      // unpack warp groups per matrix in the projection kernel (three, capped at 96 registers, measured slower: 176 against 157 us)
     static constexpr int HDR_WORDS = 9;   // d, bias, sub-scales, residual scales, two 8-entry codebooks
     CDC_HD static constexpr int sub_lo(int s) { return 12 + 6 * s; }
     CDC_HD static constexpr int sub_hi(int s) { return 18 + 6 * s; }
@@ -281,7 +281,7 @@ template <> struct Codec<QUANT_EXL3> : CodecDefaults {
 // ---- variable-rate affine, 160 B / 256 (quant_router_kernels.metal:265-365; gold :214-311) ---------
 template <> struct Codec<QUANT_VAR_RATE_AFFINE> : CodecDefaults {
     static constexpr int ROW_BYTES = 160;
-    static constexpr int GROUPS = 2;      // unpack warp groups per matrix in the projection kernel
+    static constexpr int GROUPS = 3;      // unpack warp groups per matrix in the projection kernel (fits 96 registers without spilling: 111-120 us against 134-140 us with two)
     static constexpr int HDR_WORDS = 7;   // d, bias, sub-scales, sub-biases, mode bytes
     // payload runs start at bytes 32 + {0,12,24,40,56,72,88,108}; any run may be read as five words
     CDC_HD static constexpr int sub_lo(int s) { return s == 0 ? 8 : (s == 1 ? 14 : (s == 2 ? 22 : 30)); }
