@@ -114,14 +114,6 @@ CDC_HD void nib_pairs(uint32_t sp, uint32_t& lo, uint32_t& hi) {
     hi = (sp & 0x00F000F0u) | H2_64;
 }
 
-// 8-entry fp16 table in L[0..3] (entry e in half e&1 of word e>>1), looked up for two indices at once
-CDC_HD uint32_t lut8_pair(const uint32_t* L, uint32_t q0, uint32_t q1) {
-    uint32_t sel = 0x1010u + 0x22u * (q0 & 3u) + 0x2200u * (q1 & 3u);
-    uint32_t wa = prmt(L[0], L[1], sel), wb = prmt(L[2], L[3], sel);
-    uint32_t m = ((q0 & 4u) ? 0x0000FFFFu : 0u) | ((q1 & 4u) ? 0xFFFF0000u : 0u);
-    return (wa & ~m) | (wb & m);
-}
-
 // Traits every codec may override: META_WORDS 32-bit words of per-chunk metadata that live outside the packed
 // row (fetched from global memory by the unpack thread), ROW_SCALE when the weights are unpacked to exact small
 // integers and one fp16 scale per output row is applied to the fp32 accumulator instead.
@@ -244,7 +236,7 @@ template <> struct Codec<QUANT_TERNARY_1_58> : CodecDefaults {
 // ---- EXL3-style codebook, 144 B / 256 (quant_router_kernels.metal:368-411; gold :342-389) ---------
 template <> struct Codec<QUANT_EXL3> : CodecDefaults {
     static constexpr int ROW_BYTES = 144;
-    static constexpr int GROUPS = 2;      // unpack warp groups per matrix in the projection kernel (three, capped at 96 registers, measured slower: 176 against 157 us)
+    static constexpr int GROUPS = 3;      // unpack warp groups per matrix in the projection kernel
     static constexpr int HDR_WORDS = 9;   // d, bias, sub-scales, residual scales, two 8-entry codebooks
     CDC_HD static constexpr int sub_lo(int s) { return 12 + 6 * s; }
     CDC_HD static constexpr int sub_hi(int s) { return 18 + 6 * s; }
@@ -267,13 +259,24 @@ template <> struct Codec<QUANT_EXL3> : CodecDefaults {
             const uint32_t w0 = r[w], w1 = r[w + 1], w2 = r[w + 2];
             const uint32_t v[4] = {w0 & 0xFFFFFFu, ((w0 >> 24) | (w1 << 8)) & 0xFFFFFFu,
                                    ((w1 >> 16) | (w2 << 16)) & 0xFFFFFFu, w2 >> 8};
+            // The eight table entries as two byte tables (low bytes, high bytes): one byte permute then looks up four
+            // 3-bit codes at once (its selector nibbles are the codes), two more interleave the bytes back into fp16 pairs.
+            const uint32_t lo_a = prmt(L[0], L[1], 0x6420u), lo_b = prmt(L[2], L[3], 0x6420u);
+            const uint32_t hi_a = prmt(L[0], L[1], 0x7531u), hi_b = prmt(L[2], L[3], 0x7531u);
 #pragma unroll
-            for (int g = 0; g < 4; g++)
+            for (int g = 0; g < 4; g++) {
+                // eight 3-bit codes -> eight nibbles: 12-bit halves apart, then 6-bit pairs, then single codes
+                uint32_t x = (v[g] & 0xFFFu) | ((v[g] & 0xFFF000u) << 4);
+                x = (x & 0x003F003Fu) | ((x & 0x0FC00FC0u) << 2);
+                x = (x & 0x07070707u) | ((x & 0x38383838u) << 1);
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    uint32_t t = v[g] >> (6 * i);
-                    out[16 * bi + 4 * g + i] = lut8_pair(L, t & 7u, (t >> 3) & 7u);
+                for (int h = 0; h < 2; h++) {
+                    const uint32_t sel = h ? (x >> 16) : x;           // codes 4h .. 4h + 3
+                    const uint32_t lo4 = prmt(lo_a, lo_b, sel), hi4 = prmt(hi_a, hi_b, sel);
+                    out[16 * bi + 4 * g + 2 * h] = prmt(lo4, hi4, 0x5140u);
+                    out[16 * bi + 4 * g + 2 * h + 1] = prmt(lo4, hi4, 0x7362u);
                 }
+            }
         }
     }
 };
@@ -333,14 +336,21 @@ template <> struct Codec<QUANT_VAR_RATE_AFFINE> : CodecDefaults {
                     pk[8 + p] = h2fma(h2sub(hi, H2_72), sc2, bs2);
                 }
             }
-            // destination permutation: 0 identity; 1 even sources first, then odd; 2 reversed
+            // destination permutation: 0 identity; 1 even sources first, then odd; 2 reversed.  Branches, not selects: the
+            // rows of a warp usually share the mode byte, and even when they do not, the three arms together cost less than
+            // computing all three results for every output.
+            if (perm == 1u) {
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-                uint32_t ident = pk[i];
-                uint32_t deint = (i < 8) ? prmt(pk[2 * i], pk[2 * i + 1], 0x5410u)
-                                         : prmt(pk[2 * (i - 8)], pk[2 * (i - 8) + 1], 0x7632u);
-                uint32_t rev = prmt(pk[15 - i], 0u, 0x1032u);
-                out[16 * bi + i] = (perm == 1u) ? deint : ((perm == 2u) ? rev : ident);
+                for (int i = 0; i < 8; i++) {
+                    out[16 * bi + i] = prmt(pk[2 * i], pk[2 * i + 1], 0x5410u);
+                    out[16 * bi + 8 + i] = prmt(pk[2 * i], pk[2 * i + 1], 0x7632u);
+                }
+            } else if (perm == 2u) {
+#pragma unroll
+                for (int i = 0; i < 16; i++) out[16 * bi + i] = prmt(pk[15 - i], 0u, 0x1032u);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; i++) out[16 * bi + i] = pk[i];
             }
         }
     }
