@@ -1072,8 +1072,10 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bar_s) + 128);   // [2 parities][2 halves][128 rows]
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t pb = gridDim.x - 1 - blockIdx.x;      // latest position blocks (longest) first
-    const uint32_t hk = blockIdx.y;
+    // CTAs start in the order of their linear index (x fastest): kv heads along x, position blocks along y, latest block
+    // (most key tiles) first, so the long CTAs of every head start before any short one and the short ones fill the tail
+    const uint32_t pb = gridDim.y - 1 - blockIdx.y;
+    const uint32_t hk = blockIdx.x;
     const uint32_t p0 = pb * BP;
     const uint32_t last_pos = min(p.pos0 + min(p0 + BP, p.M) - 1, p.Mkv - 1);
     const uint32_t n_ktiles = last_pos / TC_BK + 1;
@@ -1363,7 +1365,7 @@ template <int G> cudaError_t launch_tma(const Params& p, cudaStream_t stream) {
     if (!make_kv_map(&tmK, Kf, p.Hkv, p.Mkv, TC_BK, 1) || !make_kv_map(&tmV, Vf, p.Hkv, p.Mkv, TC_BK, 1) ||
         !make_kv_map(&tmQ, p.Q, p.Hq, p.M, BP, G))
         return cudaErrorInvalidValue;
-    dim3 grid((p.M + BP - 1) / BP, p.Hkv);
+    dim3 grid(p.Hkv, (p.M + BP - 1) / BP);
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T2_SMEM);
