@@ -89,20 +89,24 @@ __device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-template <int W, int HI>
-__device__ __forceinline__ void ld_words(const uint8_t* rowp, uint32_t* r) {
+// words [W, HI) of a packed row; SW: the row was staged with the 128-byte TMA swizzle (16-byte chunk index ^ row % 8, the
+// planar layouts' 128-byte rows) and is read in whole chunks
+template <int W, int HI, bool SW = false>
+__device__ __forceinline__ void ld_words(const uint8_t* rowp, uint32_t* r, uint32_t xr = 0u) {
     if constexpr (W < HI) {
         if constexpr (W % 4 == 0 && W + 4 <= HI) {
-            const uint4 v = *reinterpret_cast<const uint4*>(rowp + W * 4);
+            const uint4 v = *reinterpret_cast<const uint4*>(rowp + (SW ? ((uint32_t)(W / 4) ^ xr) << 4 : (uint32_t)W * 4u));
             r[W] = v.x; r[W + 1] = v.y; r[W + 2] = v.z; r[W + 3] = v.w;
-            ld_words<W + 4, HI>(rowp, r);
+            ld_words<W + 4, HI, SW>(rowp, r, xr);
         } else if constexpr (W % 2 == 0 && W + 2 <= HI) {
+            static_assert(!SW, "swizzled rows are read in 16-byte chunks");
             const uint2 v = *reinterpret_cast<const uint2*>(rowp + W * 4);
             r[W] = v.x; r[W + 1] = v.y;
-            ld_words<W + 2, HI>(rowp, r);
+            ld_words<W + 2, HI, SW>(rowp, r, xr);
         } else {
+            static_assert(!SW, "swizzled rows are read in 16-byte chunks");
             r[W] = *reinterpret_cast<const uint32_t*>(rowp + W * 4);
-            ld_words<W + 1, HI>(rowp, r);
+            ld_words<W + 1, HI, SW>(rowp, r, xr);
         }
     }
 }
@@ -117,7 +121,8 @@ qgemm_small_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     constexpr int ROW_BYTES = Cd::ROW_BYTES;
     constexpr int RAW_TILE_BYTES = ROW_BYTES * W_TILE;
     constexpr int SUBS = Cd::CHUNK / KSTEP;
-    static_assert(!Cd::RAW_SWIZZLE_128 && Cd::META_WORDS == 0, "planar layouts with side planes stay on the persistent kernel");
+    constexpr bool SW = Cd::RAW_SWIZZLE_128;
+    constexpr int MW = Cd::META_WORDS > 0 ? Cd::META_WORDS : 4;      // scale / bias words per chunk of the planar layouts
 
     extern __shared__ uint8_t smem_dyn[];
     ptx::launch_dependents();     // the next kernel in the stream may set itself up while this grid runs
@@ -237,19 +242,41 @@ qgemm_small_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         uint32_t rs = 0, rph = 0;
         bool ok = true;
         for (uint32_t kc = 0; ok && kc < p.kchunks; kc++) {
+            // planar layouts: this chunk's scales and biases come straight from their planes in global memory, requested
+            // before the wait for the packed bytes
+            uint32_t meta[MW] = {};
+            if (Cd::META_WORDS != 0) {
+                const uint32_t n = wt * W_TILE + row;
+                if (n < p.N) {
+                    const uint32_t groups = (p.K / 256u) * MW;
+                    const uint8_t* mp = p.meta0 + ((size_t)n * groups + (size_t)(ks * p.kchunks + kc) * MW) * 2;
+                    const uint8_t* bp = mp + (size_t)p.N * groups * 2;
+                    if (MW == 4) {
+                        const uint2 sc = __ldg(reinterpret_cast<const uint2*>(mp));
+                        const uint2 bi = __ldg(reinterpret_cast<const uint2*>(bp));
+                        meta[0] = sc.x; meta[1] = sc.y; meta[2] = bi.x; meta[3] = bi.y;
+                    } else {
+                        const uint4 sc = __ldg(reinterpret_cast<const uint4*>(mp));
+                        const uint4 bi = __ldg(reinterpret_cast<const uint4*>(bp));
+                        meta[0] = sc.x; meta[1] = sc.y; meta[2] = sc.z; meta[3] = sc.w;
+                        meta[MW - 4] = bi.x; meta[MW - 3] = bi.y; meta[MW - 2] = bi.z; meta[MW - 1] = bi.w;
+                    }
+                }
+            }
             ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&raw_full[rs], rph, abort_flag, p.err, 115));
             if (!ok) break;
             if (threadIdx.x == 0) QST(3, kc);
             uint32_t r[ROW_BYTES / 4];
             const uint8_t* rowp = sRaw + rs * RAW_TILE_BYTES + row * ROW_BYTES;
-            ld_words<0, Cd::HDR_WORDS>(rowp, r);
+            const uint32_t xr = row & 7u;
+            ld_words<0, Cd::HDR_WORDS, SW>(rowp, r, xr);
             auto sub_tile = [&](auto S) {
                 constexpr int s = decltype(S)::value;
                 // step of this CTA, its stage of the A ring and the parity of that stage's use
                 const uint32_t step = kc * (uint32_t)SUBS + (uint32_t)s, as = step % A_STAGES, aph = (step / A_STAGES) & 1u;
                 uint32_t o[32];
-                ld_words<Cd::sub_lo(s), Cd::sub_hi(s)>(rowp, r);
-                Cd::dequant64(r, s, o, nullptr);
+                ld_words<Cd::sub_lo(s), Cd::sub_hi(s), SW>(rowp, r, xr);
+                Cd::dequant64(r, s, o, meta);
                 ok = __all_sync(0xffffffffu, ok && ptx::mbar_wait<32>(&a_empty[as], aph ^ 1u, abort_flag, p.err, 116));
                 if (ok) {
                     ptx::tc_fence_after_sync();                      // the MMAs that read this stage have completed
@@ -442,7 +469,7 @@ template <int FMT> cudaError_t launch_fmt(const GemmArgs& a, const Workspace& ws
         return cudaErrorInvalidValue;
     constexpr int EB = Cd::TMA_ELEM_BYTES;
     if (!make_map(&tmW, EB == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, a.W0, w_row_bytes / EB, a.N, w_row_bytes,
-                  Cd::ROW_BYTES / EB, W_TILE, CU_TENSOR_MAP_SWIZZLE_NONE))
+                  Cd::ROW_BYTES / EB, W_TILE, Cd::RAW_SWIZZLE_128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorInvalidValue;
     Params p;
     p.M = a.M; p.N = a.N; p.K = a.K; p.T = pl.T;
@@ -501,9 +528,9 @@ bool small_path_ok(const GemmArgs& a) {
     uint32_t chunk = 256;
     switch (a.format) {
         case QUANT_Q4_0: case QUANT_MLX_4BIT: case QUANT_Q4_K: case QUANT_TERNARY_1_58: case QUANT_VAR_RATE_AFFINE: case QUANT_EXL3:
-        case QUANT_TERNARY_ROW: break;
+        case QUANT_TERNARY_ROW: case QUANT_MLX_4BIT_G64: case QUANT_MLX_4BIT_PLANAR: break;
         case QUANT_PRISM_Q2_0: chunk = 1024; break;
-        default: return false;          // the planar group-64 layout reads side planes per chunk: persistent kernel
+        default: return false;
     }
     if (a.K % chunk != 0) return false;
     // worthwhile where the persistent kernel would leave SMs idle: fewer output tiles (at its tile height) than SMs
@@ -525,6 +552,8 @@ bool small_path_ok(const GemmArgs& a) {
         case QUANT_VAR_RATE_AFFINE: { constexpr int F = QUANT_VAR_RATE_AFFINE; return EXPR; } \
         case QUANT_EXL3: { constexpr int F = QUANT_EXL3; return EXPR; }                    \
         case QUANT_TERNARY_ROW: { constexpr int F = QUANT_TERNARY_ROW; return EXPR; }      \
+        case QUANT_MLX_4BIT_G64: { constexpr int F = QUANT_MLX_4BIT_G64; return EXPR; }    \
+        case QUANT_MLX_4BIT_PLANAR: { constexpr int F = QUANT_MLX_4BIT_PLANAR; return EXPR; } \
         case QUANT_PRISM_Q2_0: { constexpr int F = QUANT_PRISM_Q2_0; return EXPR; }        \
         default: break;                                                                    \
     }
