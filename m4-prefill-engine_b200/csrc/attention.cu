@@ -635,6 +635,22 @@ __device__ __forceinline__ float ex2(float x) {        // 2^x, one MUFU instruct
     return y;
 }
 
+// 2^x for x <= 8 without the special-function unit: x = n + f with n the nearest integer (read off the low mantissa bits of
+// x + 1.5 * 2^23) and |f| <= 1/2, 2^f as a degree-5 polynomial (relative error 3e-6, far below the fp16 rounding of the
+// probabilities it produces), n added to the exponent field.  Inputs below -120 (masked scores are -inf) give 2^-120.
+__device__ __forceinline__ float ex2_poly(float x) {
+    x = fmaxf(x, -120.0f);
+    const float r = x + 12582912.0f;
+    const float f = x - (r - 12582912.0f);
+    float p = 1.3333558146e-3f;
+    p = fmaf(p, f, 9.6181291076e-3f);
+    p = fmaf(p, f, 5.5504108665e-2f);
+    p = fmaf(p, f, 2.4022650696e-1f);
+    p = fmaf(p, f, 6.9314718056e-1f);
+    p = fmaf(p, f, 1.0f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
+}
+
 // byte offset of fp16 element (row, col) inside a K-major swizzled tile of two 64-column atoms
 __device__ __forceinline__ uint32_t tc_off(uint32_t row, uint32_t col) {
     return (col >> 6) * TC_ATOM + (row >> 3) * 1024u + (row & 7u) * 128u + ((((col & 63u) >> 3) ^ (row & 7u)) << 4) + (col & 7u) * 2u;
@@ -1200,16 +1216,23 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             xm[half_id * 128u + row] = mx;
             ptx::bar_sync(1 + (int)(warp & 3u), 64);        // this warp and its partner
             mx = fmaxf(fmaxf(mx, xm[(half_id ^ 1u) * 128u + row]), m_run);
-            const float corr = ex2(m_run - mx);
-            m_run = mx;
+            // The reference maximum of a row moves only when the tile's maximum exceeds it by more than 2^8: probabilities
+            // are then 2^(s - m_run) <= 256 instead of <= 1, which fp16 P and the fp32 sums hold just as well, the final
+            // division by the row sum removes the common factor, and O has to be rescaled in tensor memory only when that
+            // happens (after the first tile: hardly ever) instead of whenever any of a warp's 32 rows sees a new maximum
+            // (almost every tile).  Both threads of a row take the same decision (same m_run, same mx).
+            float corr = 1.0f;
+            if (mx > m_run + 8.0f) { corr = ex2(m_run - mx); m_run = mx; }
             ATR(1);
             uint32_t pk[32];
             float rs = 0.0f;
 #pragma unroll
             for (int j = 0; j < 64; j += 2) {
-                // masked scores are -inf: fma gives -inf, ex2 gives 0
-                const float e0 = ex2(fmaf(sc[j], p.scale_log2e, -mx));
-                const float e1 = ex2(fmaf(sc[j + 1], p.scale_log2e, -mx));
+                // masked scores are -inf: fma gives -inf, ex2 gives 0.  One exponential in four is evaluated as a polynomial
+                // on the FMA pipe: the SM's 16 ex2 per clock bound this loop (one in two made it issue-bound: 70 us against 62).
+                const float x0 = fmaf(sc[j], p.scale_log2e, -m_run), x1 = fmaf(sc[j + 1], p.scale_log2e, -m_run);
+                const float e0 = ex2(x0);
+                const float e1 = (j & 2) ? ex2_poly(x1) : ex2(x1);
                 rs += e0 + e1;
                 pk[j >> 1] = pack_h2(e0, e1);
             }

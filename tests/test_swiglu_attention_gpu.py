@@ -162,8 +162,9 @@ def test_attention_tensor_memory_kernel_long(bridge):
     assert np.abs(b.astype(np.float64) - gold.astype(np.float64)).max() <= TOL
     assert np.abs(a.astype(np.float32) - b.astype(np.float32)).max() <= 2e-3
     # the kernel that unpacks the Q8_0 tiles itself, with V transposed in shared memory (K-major operand, hook 2) and in
-    # its natural [key][d] form (MN-major operand, hook 3), against the default (cache dequantised once, tiles through
-    # TMA): the same products in the same order
+    # its natural [key][d] form (MN-major operand, hook 3): the same products in the same order.  The default (cache
+    # dequantised once, tiles through TMA) moves a row's reference maximum only for jumps above 2^8 and evaluates part of
+    # the exponentials as a polynomial, so it agrees with them to rounding, not bit for bit.
     outs = {}
     for hook in (2, 3):
         bridge.lib.b200_bridge_force_legacy_attention(hook)
@@ -172,7 +173,7 @@ def test_attention_tensor_memory_kernel_long(bridge):
         finally:
             bridge.lib.b200_bridge_force_legacy_attention(0)
     assert np.array_equal(outs[2].view(np.uint16), outs[3].view(np.uint16))
-    assert np.array_equal(a.view(np.uint16), outs[3].view(np.uint16))
+    assert np.abs(a.astype(np.float32) - outs[3].astype(np.float32)).max() <= 2e-3
     assert bridge.device_error() == 0
 
 
