@@ -403,7 +403,9 @@ def roofline_of(fmt_name: str, m: int, k: int, n: int, flops: float, algo_bytes:
     common = {"traffic": traffic, "traffic_source": tsrc, "algorithmic_flops_per_launch": flops, "algorithmic_bytes_per_launch": algo_bytes}
     if m > 256:
         return {"bound": "tensor", "achieved": tfl, "peak": burst, "unit": "TFLOP/s", "frac": tfl / burst,
-                "peak_source": f"{src}: dense bf16/fp16 cuBLAS burst (sustained {sustained})", "hbm_frac": gbs / hbm, **common}
+                "peak_source": f"{src}: dense bf16/fp16 cuBLAS burst (sustained {sustained})",
+                # the timed blocks are back-to-back launches under the power cap, the condition the sustained figure was taken in
+                "frac_of_sustained": (tfl / sustained) if sustained else None, "hbm_frac": gbs / hbm, **common}
     return {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
             "peak_source": f"{src}: device copy bandwidth", "tensor_frac": tfl / burst, **common}
 

@@ -194,6 +194,22 @@ def test_shards_reassemble_exactly(pkg):
         assert np.abs(part - full).max() < 1e-9
 
 
+def test_planar_shards_reassemble_exactly(pkg):
+    """Column split of the planar layouts (every plane keeps the rank's rows; the group-32 MLX layout pads its planes to
+    16 bytes, also where a shard's plane sizes are not multiples of 16)."""
+    from m4_prefill_engine_b200.layer import shard_rows_any
+    M = 5
+    for fmt, K, N, tp in ((o.MLX_4BIT_G64, 512, 96, 4), (o.TERNARY_ROW, 512, 96, 4), (o.MLX_4BIT_PLANAR, 512, 96, 4),
+                          (o.MLX_4BIT_PLANAR, 96, 6, 2), (o.PRISM_Q2_0, 512, 96, 4)):
+        X, W = o.baseline_inputs(fmt, M, K, N, 31) if fmt != o.PRISM_Q2_0 else (o.RefLcg(3).activations(M, K), o.RefLcg(3).weights(fmt, K, N))
+        full = o.gemm_f64(fmt, X, W, N)
+        shards = [shard_rows_any(W, fmt, K, N, r, tp) for r in range(tp)]
+        for sh in shards:
+            assert sh.size == o.weight_bytes(fmt, K, N // tp)
+        cols = np.concatenate([o.gemm_f64(fmt, X, sh, N // tp) for sh in shards], axis=1)
+        assert np.array_equal(cols, full)
+
+
 GLOO_WORKER = r'''
 import os, sys, numpy as np, torch, torch.distributed as dist
 sys.path.insert(0, sys.argv[1])
