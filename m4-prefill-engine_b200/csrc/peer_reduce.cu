@@ -269,6 +269,7 @@ cudaError_t wait_rows(const Exchange& x, int* err, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
+long long wait_limit_cycles() { return g_wait_limit_cycles; }
 void set_wait_limit_ms(unsigned ms) { g_wait_limit_cycles = ms ? (long long)ms * 2000000LL : DEFAULT_WAIT_LIMIT_CYCLES; }
 
 }  // namespace peer

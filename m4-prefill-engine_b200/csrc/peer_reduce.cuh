@@ -30,5 +30,6 @@ cudaError_t wait_rows(const Exchange& x, int* err, cudaStream_t stream);
 
 // Bound of the flag waits in milliseconds at about 2 GHz (0 = the default of ten seconds).
 void set_wait_limit_ms(unsigned ms);
+long long wait_limit_cycles();       // the bound of every flag wait, in clock64 ticks
 
 }  // namespace peer

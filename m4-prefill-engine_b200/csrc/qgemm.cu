@@ -125,6 +125,7 @@ struct Params {
     uint32_t groups, grp_tiles[3], grp_N[3];
     __half* grp_Y[3];
     GemmArgs::Scatter scatter;   // fused reduce-scatter of fp32 partial sums to peer ranks (world == 0: off)
+    GemmArgs::WaitRows wait_rows; // activations other ranks are still writing (flags == nullptr: off)
     uint32_t tt_shift;           // rotation of the token-tile order (fused reduce-scatter only, else 0)
     uint32_t tiles_per_owner;    // output tiles whose token rows belong to one rank (fused reduce-scatter only)
     uint32_t swiglu;             // 1: tiles are 64 gate rows (matrix 0) + their 64 up rows (matrix 1); output = silu(g) * u
@@ -587,9 +588,35 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CU
         uint32_t bs = 0, bph = 0, xtr = 0;
         (void)xtr;
         bool ok = true;
+        uint32_t rows_seen = 0;               // bit o: owner o's rows are known to be there
         for (uint32_t idx = first_tile; ok && idx < total_tiles; idx += tile_stride) {
             const Tile t = tile_of(idx);
             const uint32_t k0 = t.ks * p.kchunks * (uint32_t)C::CHUNK;
+            if (p.wait_rows.flags) {
+                // rows this CTA is about to load: wait until their owners have written them (system-scope acquire, then the
+                // proxy fence that orders the TMA reads behind it)
+                const uint32_t r0 = t.tt * p.T + pair_rank * b_rows, r1 = min(r0 + b_rows, p.M) - 1u;
+                for (uint32_t o = r0 / p.wait_rows.rows; ok && o <= r1 / p.wait_rows.rows; o++) {
+                    if ((rows_seen >> o) & 1u) continue;
+                    const long long t0 = clock64();
+                    for (;;) {
+                        uint32_t v;
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait_rows.flags + o) : "memory");
+                        if ((int32_t)(v - p.wait_rows.epoch) >= 0) break;
+                        if (*abort_flag || clock64() - t0 > p.wait_rows.limit_cycles) {
+                            *abort_flag = 1u;
+                            if (p.err) atomicCAS(p.err, 0, 110);
+                            ok = false;
+                            break;
+                        }
+                        __nanosleep(100);
+                    }
+                    rows_seen |= 1u << o;
+                }
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
             for (uint32_t ks = 0; ks < ksteps; ks++) {
                 ok = __all_sync(0xffffffffu, ptx::mbar_wait<32>(&b_empty[bs], bph ^ 1u, abort_flag, p.err, 102));
                 if (!ok) break;
@@ -1401,6 +1428,8 @@ cudaError_t launch_fast(const GemmArgs& a, const Workspace& ws, cudaStream_t str
     }
     p.Y = (__half*)a.Y; p.residual = (const __half*)a.residual; p.partial_out = a.partial_out;
     p.scatter = a.scatter;
+    p.wait_rows = a.wait_rows;
+    if (a.wait_rows.flags && (pl.k_splits != 1 || a.wait_rows.rows == 0 || a.M > 32u * a.wait_rows.rows)) return cudaErrorInvalidValue;
     p.groups = 1u + a.n_extra;
     p.grp_tiles[0] = (a.N + W_TILE - 1) / W_TILE; p.grp_N[0] = a.N; p.grp_Y[0] = (__half*)a.Y;
     for (uint32_t e = 0; e < 2u; e++) {
@@ -1516,6 +1545,7 @@ size_t workspace_floats(const GemmArgs& a) {
 
 cudaError_t launch(const GemmArgs& a, const Workspace& ws, cudaStream_t stream) {
     g_last_launches = 1;
+    if (a.wait_rows.flags) return fast_path_ok(a) ? dispatch_fast(a, ws, stream) : cudaErrorInvalidValue;   // only the persistent kernel waits for rows
     if (gemv_path_ok(a)) return launch_gemv(a, stream);
     if (small_path_ok(a)) return launch_small(a, ws, stream);
     if (fast_path_ok(a)) return dispatch_fast(a, ws, stream);

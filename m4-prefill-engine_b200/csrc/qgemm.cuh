@@ -45,6 +45,15 @@ struct GemmArgs {
         uint32_t fp16;                   // != 0: partial sums travel as fp16 (recv[o] then holds fp16 [world][rows][N]), else fp32
         uint32_t* done_counter;          // 16 device-local words, zero between launches (words 4..11: one tile counter per owner)
     } scatter;
+    // Activations that other ranks are still writing (the rows an owner-side reduction broadcasts): token rows
+    // [o * rows, (o + 1) * rows) may be read once flags[o] has reached `epoch`.  The warp that loads a token tile polls the
+    // flags of the owners the tile covers first (bounded; error code 110), so the launch needs no separate wait kernel in
+    // front of it and starts on the rows that are already there.  flags == nullptr: off.  Persistent kernel, no K split.
+    struct WaitRows {
+        const uint32_t* flags;           // this rank's "rows written" flags, one word per owner
+        uint32_t rows, epoch;
+        long long limit_cycles;          // give up after this many clock64 ticks
+    } wait_rows;
 };
 
 struct Workspace {            // split-K scratch, owned by the caller

@@ -291,8 +291,10 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
     // row-split projection with the reduction fused in: scatter in the epilogue, owner reduces and broadcasts
     // `norm_w` != nullptr: the owner normalises its rows before writing them to every rank and keeps the plain rows
     // (the next block's residual) in `keep`.
+    // `defer_wait`: the kernel that consumes the broadcast rows waits for them itself, tile by tile (the gate/up projection's
+    // activation loads), instead of a wait kernel in front of it
     auto reduced_gemm = [&](const void* X, const void* W, uint32_t Kin, const void* residual, int which_out, const void* norm_w,
-                            void* keep, const char* what) {
+                            void* keep, const char* what, bool defer_wait) {
         if (status_) return;
         peer::Exchange& x = *im.px;
         x.epoch++;
@@ -306,6 +308,7 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
         mark(what);
         check(peer::reduce_broadcast(x, which_out, residual, c.M, c.K, im.err, stream, norm_w, c.rms_eps, keep));
         mark(norm_w ? "owner: sum + residual + rmsnorm -> all ranks" : "owner: sum + residual -> all ranks");
+        if (defer_wait) return;
         check(peer::wait_rows(x, im.err, stream));
         mark("wait for all ranks' rows");
     };
@@ -325,7 +328,7 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
         mark("o projection + residual");
     } else if (im.px) {
         reduced_gemm(im.attn, W_o, hq * c.D, X_in, 0, px_norm ? im.norm2 : nullptr, px_norm ? im.x_mid : nullptr,
-                     "o projection, partial rows scattered to their owners");
+                     "o projection, partial rows scattered to their owners", /*defer_wait=*/px_norm);
         if (!px_norm) x_mid = im.px->out[0][im.px->rank];
     } else {
         gemm(im.gemm_binding, im.attn, W_o, nullptr, nullptr, c.K, hq * c.D, 0, nullptr, im.partial);
@@ -338,7 +341,25 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
     if (fuse_add_norm) { check(lops::rmsnorm_add(im.xn, X_in, im.norm2, im.x_mid, im.xn, c.M, c.K, c.rms_eps, stream)); x_mlp = im.xn; mark("residual + rmsnorm 2"); }
     else if (px_norm) x_mlp = im.px->out[0][im.px->rank];
     else if (c.rms_eps > 0.0f) { check(lops::rmsnorm(x_mid, im.norm2, im.xn, c.M, c.K, c.rms_eps, stream)); x_mlp = im.xn; mark("rmsnorm 2"); }
-    gemm(im.gemm_binding, x_mlp, W_gate, W_up, im.act, f, c.K, 0, nullptr, nullptr);
+    bool mlp_done = false;
+    if (px_norm && !status_) {
+        // the normalised rows are still arriving from their owners: the projection waits for each token tile's rows itself
+        peer::Exchange& x = *im.px;
+        qg::GemmArgs a; memset(&a, 0, sizeof(a));
+        a.format = im.gemm_binding.format; a.X = x_mlp; a.W0 = W_gate; a.W1 = W_up; a.Y = im.act; a.M = c.M; a.N = f; a.K = c.K;
+        a.layout = im.gemm_binding.layout; a.D = c.D;
+        a.wait_rows.flags = x.flags[x.rank] + 8; a.wait_rows.rows = c.M / x.world; a.wait_rows.epoch = x.epoch;
+        a.wait_rows.limit_cycles = peer::wait_limit_cycles();
+        if (qg::launch(a, ws, stream) == cudaSuccess) {
+            launches_ += (uint32_t)qg::last_launch_count();
+            mlp_done = true;
+        } else {
+            cudaGetLastError();
+            check(peer::wait_rows(x, im.err, stream));
+            mark("wait for all ranks' rows");
+        }
+    }
+    if (!mlp_done) gemm(im.gemm_binding, x_mlp, W_gate, W_up, im.act, f, c.K, 0, nullptr, nullptr);
     mark("gate/up SwiGLU");
     // The MLP block's residual rides in the down projection's epilogue (row-wise: the residual row is read with the same
     // 16-byte-granular accesses the output row is written with).  B200_LAYER_SPLIT_ADD=1 selects the older arrangement, a
@@ -355,7 +376,7 @@ void TransformerLayerCoordinator::forward(cudaStream_t stream, const void* X_in,
         mark("down projection + residual");
     } else if (im.px) {
         // (x_mid: this rank's rows are all the owner's reduction reads)
-        reduced_gemm(im.act, W_down, f, x_mid, 1, nullptr, nullptr, "down projection, partial rows scattered to their owners");
+        reduced_gemm(im.act, W_down, f, x_mid, 1, nullptr, nullptr, "down projection, partial rows scattered to their owners", false);
         // the result sits in this rank's copy of the second result buffer; a caller that hands that very buffer in as
         // X_out (the layers of a model do) needs no copy
         if (!status_ && X_out != im.px->out[1][im.px->rank]) {
