@@ -141,8 +141,8 @@ def cpu_baseline(fmt: int, budget_s: float = 12.0) -> dict:
     import oracle as o
     cores = cpu_threads()
     use_ref = o.ref_lib() is not None and fmt in (0, 1, 2, 3, 4, 5)
-    t = cpu_slab(fmt, 4, use_ref)                       # calibrate on 4 token rows
-    rows = int(max(4, min(M, 4 * budget_s / max(t, 1e-3))))
+    t = cpu_slab(fmt, 64, use_ref)                      # calibrate on 64 token rows (enough rows to keep every thread busy)
+    rows = int(max(4, min(M, 64 * budget_s / max(t, 1e-3))))
     rows -= rows % 4
     t = cpu_slab(fmt, rows, use_ref)
     return {"value": 2.0 * rows * N * K / t / 1e12, "unit": "TFLOP/s", "cores": cores,
