@@ -663,7 +663,7 @@ def run_ours(args) -> None:
         # serving loop that batches DEPTH requests per synchronize): the bridge uploads step i+1 while step i computes
         # and downloads.  Every step's X is copied host -> device and every step's Y device -> host inside the timed
         # region.  `serial` repeats the measurement with a synchronize after every dispatch.
-        DEPTH = 4
+        DEPTH = 8
         Xh, Wh = case.Xh, case.Wh[0]
         Xp = [torch.from_numpy(Xh if i == 0 else Xh.copy()).pin_memory() for i in range(DEPTH)]
         Yp = [torch.zeros(M, N, dtype=torch.float16).pin_memory() for _ in range(DEPTH)]
