@@ -123,8 +123,10 @@ int b200_bridge_gemm_scratch_static(void* X_ptr, size_t X_bytes, void* W_ptr, si
 int b200_bridge_register_weights(const void* host_ptr, size_t bytes);
 int b200_bridge_unregister_weights(const void* host_ptr);
 
-/* 0 if no kernel has reported a fault since init; otherwise the first code reported (codes
- * 101..199: a bounded wait inside a GEMM kernel ran out). */
+/* 0 if no kernel has reported a fault since init; otherwise the first code reported: a bounded wait ran out inside a
+ * projection kernel (101..110; 109 the CTA-pair relay, 110 rows another rank had not written), the few-token projection
+ * kernel (111..117), an attention kernel (201..204, 210..217) or the peer exchange (301, 302); 401: a token id outside the
+ * embedding table. */
 int b200_bridge_device_error(void);
 const char* b200_bridge_last_error_string(void);
 
