@@ -12,6 +12,7 @@
 // a read outside the mapping.  Multi-byte fields are read byte by byte as little-endian, so the host's byte order does
 // not matter.
 #pragma once
+#ifdef __cplusplus
 #include <cstddef>
 #include <cstdint>
 #include <map>
@@ -158,7 +159,14 @@ private:
 
 }  // namespace b200_llm
 
+#else   /* C callers see the C entry points below only */
+#include <stddef.h>
+#include <stdint.h>
+#endif
+
+#ifdef __cplusplus
 extern "C" {
+#endif
 /* C surface over GgufFile / GgufLayerStreamer for the Python side (no counterpart in the reference's C ABI: its loader is
  * reached from Objective-C++ only).  Handles are opaque; strings are NUL-terminated UTF-8. */
 void* b200_gguf_open(const char* path);
@@ -191,4 +199,6 @@ int b200_gguf_streamer_is_resident(void* streamer, int layer);
 const void* b200_gguf_streamer_tensor(void* streamer, const char* name);
 uint64_t b200_gguf_streamer_stat(void* streamer, int what);   /* 0 current, 1 peak, 2 total, 3 shared bytes, 4 number of layers */
 int b200_gguf_parse_layer_index(const char* tensor_name);
+#ifdef __cplusplus
 }
+#endif

@@ -8,6 +8,7 @@
 // CUDA launcher takes, which is how the layer coordinator binds its projections
 // (models/transformer_layer.mm:38-47 does the same through Metal pipeline names).
 #pragma once
+#ifdef __cplusplus
 #include <cstddef>
 #include <cstdint>
 #include <functional>
@@ -73,7 +74,15 @@ struct CodecRegistrationHelper {
 namespace metal_llm = b200_llm;   // the reference's namespace name, for code written against it
 
 // C view of the registry for bindings and tests.
+
+#else   /* C callers see the C entry points below only */
+#include <stddef.h>
+#include <stdint.h>
+#endif
+
+#ifdef __cplusplus
 extern "C" {
+#endif
 int b200_registry_count(void);
 int b200_registry_format_at(int index);
 int b200_registry_describe(int format, char* name_out, size_t name_cap, uint32_t* block_size, size_t* struct_size,
@@ -86,4 +95,6 @@ int b200_registry_resolve_kernel(const char* kernel_name, int* format, int* layo
 /* registers (or replaces) a descriptor at run time; returns 0 */
 int b200_registry_register(int format, const char* name, uint32_t block_size, size_t struct_size, double bits_per_weight,
                            const char* gemm_kernel, const char* head_kernel);
+#ifdef __cplusplus
 }
+#endif

@@ -14,6 +14,7 @@
 // reference's Python block has (src/engine/model.py:181-270): RMSNorm, grouped-query attention,
 // rotary embedding; plus the Q8_0 KV cache of its benches and tensor parallelism.
 #pragma once
+#ifdef __cplusplus
 #include <cstddef>
 #include <cstdint>
 
@@ -100,7 +101,14 @@ private:
 
 }  // namespace b200_llm
 
+#else   /* C callers see the C entry points below only */
+#include <stddef.h>
+#include <stdint.h>
+#endif
+
+#ifdef __cplusplus
 extern "C" {
+#endif
 typedef struct {
     uint32_t M, K, H, D, N_mlp;
     float attn_scale;
@@ -167,4 +175,6 @@ void b200_peer_set_wait_limit_ms(unsigned ms);
 /* Partial-sum type of the three primitive entry points above: 0 fp32 (default), != 0 fp16 (the receive buffers then hold
  * fp16 [world][M / world][N]). */
 void b200_peer_set_partial_fp16(int on);
+#ifdef __cplusplus
 }
+#endif

@@ -12,6 +12,7 @@
 // TransformerLayerCoordinator::forward, lm_head holds this rank's rows of the vocabulary (logits come out column-
 // split, no collective), the embedding table is replicated.
 #pragma once
+#ifdef __cplusplus
 #include <cstddef>
 #include <cstdint>
 
@@ -66,7 +67,15 @@ private:
 
 }  // namespace b200_llm
 
+#else   /* C callers see the C entry points below only */
+#include <stddef.h>
+#include <stdint.h>
+#include "transformer_layer.h"
+#endif
+
+#ifdef __cplusplus
 extern "C" {
+#endif
 typedef struct {
     b200_layer_config layer;
     uint32_t num_layers, vocab_size;
@@ -90,4 +99,6 @@ int b200_model_set_allreduce(void* model, void (*fn)(void* ctx, void* buf, size_
  * logits (fp16 [M][vocab_rows]) and hidden (fp16 [M][K]) may be host or device pointers or NULL. */
 int b200_model_forward(void* model, const int32_t* tokens, uint32_t n_tokens, void* logits, void* hidden);
 uint32_t b200_model_kernels_per_forward(void* model);
+#ifdef __cplusplus
 }
+#endif

@@ -34,6 +34,17 @@ def test_library_exports_every_declared_symbol(lib_path):
     assert not missing, f"declared in include/*.h but not exported: {missing}"
 
 
+def test_public_headers_compile_as_c(tmp_path):
+    """The C entry points are declared for C callers too: every header under include/ that declares one compiles as C11
+    (the C++ classes that mirror the reference's own headers are hidden from a C compiler)."""
+    inc = Path(__file__).resolve().parent.parent / "include"
+    for h in ("b200_bridge.h", "transformer_layer.h", "transformer_model.h", "gguf_loader.h", "quant_registry.h"):
+        src = tmp_path / (h + ".c")
+        src.write_text(f'#include "{h}"\nint main(void) {{ return 0; }}\n')
+        r = subprocess.run(["gcc", "-std=c11", "-Wall", "-Werror", "-I", str(inc), "-fsyntax-only", str(src)], capture_output=True, text=True)
+        assert r.returncode == 0, f"{h}: {r.stderr[:400]}"
+
+
 def test_no_compute_without_init(lib_path, pkg):
     lib = pkg.bridge.bind(ctypes.CDLL(str(lib_path)))
     if lib.m4_bridge_is_initialized():
