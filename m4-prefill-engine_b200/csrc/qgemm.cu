@@ -1280,8 +1280,8 @@ Plan make_plan(const GemmArgs& a) {
     return pl;
 }
 
-// CTA pairs need the idle warp 14 as their relay: the codecs with three unpack groups (twelve unpack warps) have it; the two
-// with two groups are bound by their unpack arithmetic and would gain nothing.
+// CTA pairs need the idle warp 14 as their relay: a codec with three unpack groups (twelve unpack warps) has it -- every
+// codec as of now; one with two groups would stay on one CTA per MMA.
 template <int FMT> constexpr bool pair_capable() { return Cfg<FMT>::DQ_WARPS == 12 && Cfg<FMT>::EPI_WARP0 > 14; }
 
 // The dynamic shared-memory attribute is per device: set once for every device a launch (or prepare_device) sees.
